@@ -111,24 +111,24 @@ class Net:
         except Exception:
             pass
 
-    def op(self, type: str, bottoms: Iterable[str], tops: Iterable[str], name: str | None = None,
+    def op(self, op_type: str, bottoms: Iterable[str], tops: Iterable[str], /, op_name: str | None = None,
            **args) -> "Net":
         bottoms, tops = list(bottoms), list(tops)
         names, kinds, counts, values, strings = encode_args(args)
         n = len(names)
         rc = self.L.net_add_op(
-            self.h, type.encode(), (name or "%s_%d" % (type.lower(), self._n_ops)).encode(),
+            self.h, op_type.encode(), (op_name or "%s_%d" % (op_type.lower(), self._n_ops)).encode(),
             len(bottoms), _cstr_array(bottoms), len(tops), _cstr_array(tops), n, _cstr_array(names),
             (C.c_int * max(n, 1))(*kinds), (C.c_int * max(n, 1))(*counts),
             (C.c_double * max(len(values), 1))(*values), _cstr_array(strings))
-        self.L.check(rc, "net_add_op(%s)" % type)
+        self.L.check(rc, "net_add_op(%s)" % op_type)
         self._n_ops += 1
         return self
 
     def input(self, shapes: Mapping[str, Sequence[int]]) -> "Net":
         """The ``Input`` operator: one top per input blob, its shape in a v_i argument named
         after the blob (shadow/backends/native/native.cpp:174-180)."""
-        return self.op("Input", [], list(shapes), name="input",
+        return self.op("Input", [], list(shapes), op_name="input",
                        **{k: [int(d) for d in v] for k, v in shapes.items()})
 
     def weight(self, name: str, array: np.ndarray) -> "Net":

@@ -1,0 +1,212 @@
+"""Shared parity-case table: one description of (operator, arguments, seeded inputs) that the
+golden-fixture generator, the oracle tests and the GPU parity tests all iterate over.
+
+A case is a dict: ``name``, ``op`` (operator type string), ``args`` (operator arguments, the
+reference's names), ``inputs`` (list of float32 arrays: the operator's bottoms in order).
+Input tensors are seeded ``numpy.random.Generator(PCG64(seed))`` draws cast to float32.
+"""
+from __future__ import annotations
+
+import numpy as np
+
+from oracle import oracle as orc
+
+SPECIALS = np.array(
+    [0.0, -0.0, 1.0, -1.0, np.nan, np.inf, -np.inf, 3.4028235e38, -3.4028235e38, 1.17549435e-38,
+     1e-45, -1e-45, 0.5, -0.5, 2.0, 3.0, -3.0, 6.0, 6.5, -7.25, 88.0, -88.0, 104.0, -104.0,
+     0.33333334, 1e-3, 16.0, 1e10, -1e10, 9.5, 2.5, -2.5], dtype=np.float32)
+
+
+def rng(seed: int) -> np.random.Generator:
+    return np.random.Generator(np.random.PCG64(seed))
+
+
+def uniform(seed, shape, lo=-1.0, hi=1.0):
+    return rng(seed).uniform(lo, hi, size=shape).astype(np.float32)
+
+
+def normal(seed, shape, mean=0.0, std=1.0):
+    return rng(seed).normal(mean, std, size=shape).astype(np.float32)
+
+
+def _case(name, op, args, inputs):
+    return {"name": name, "op": op, "args": args, "inputs": [np.ascontiguousarray(x, np.float32) for x in inputs]}
+
+
+def special_pairs():
+    """Every ordered pair of special values, as two flat arrays."""
+    a, b = np.meshgrid(SPECIALS, SPECIALS, indexing="ij")
+    return a.ravel().copy(), b.ravel().copy()
+
+
+def small_cases():
+    """Cases the C oracle finishes in well under a second each; covers every operation code of
+    the six operators, ragged sizes, every broadcast position, rank padding, edge values."""
+    cs = []
+    # ---- Binary: same shape, scalar, broadcast --------------------------------------------
+    for opname, code in orc.BINARY.items():
+        lo = 0.1 if opname == "Pow" else -2.0
+        a = uniform(100 + code, (3, 5, 7, 11), lo, 2.0)
+        b = uniform(200 + code, (3, 5, 7, 11), lo, 2.0)
+        cs.append(_case("binary_same_%s" % opname, "Binary", {"operation": code}, [a, b]))
+        cs.append(_case("binary_scalar_%s" % opname, "Binary",
+                        {"operation": code, "scalar": float(np.float32(0.7))}, [a]))
+        cs.append(_case("binary_bcast_chan_%s" % opname, "Binary", {"operation": code},
+                        [a, uniform(300 + code, (1, 5, 1, 1), lo, 2.0)]))
+    sa, sb = special_pairs()
+    for opname in ("Add", "Sub", "Mul", "Div", "Max", "Min"):
+        cs.append(_case("binary_special_%s" % opname, "Binary", {"operation": orc.BINARY[opname]}, [sa, sb]))
+    for sc in (0.0, -0.0, float("nan"), float("inf")):
+        for opname in ("Max", "Min", "Mul"):
+            cs.append(_case("binary_scalar_special_%s_%r" % (opname, sc), "Binary",
+                            {"operation": orc.BINARY[opname], "scalar": sc}, [SPECIALS]))
+    bshapes = [
+        ((4, 6, 5, 7), (1, 6, 1, 1)), ((4, 6, 5, 7), (4, 1, 1, 1)), ((4, 6, 5, 7), (1, 1, 1, 7)),
+        ((4, 6, 5, 7), (1, 1, 5, 1)), ((4, 6, 5, 7), (1, 6, 5, 7)), ((4, 6, 5, 7), (4, 6, 1, 1)),
+        ((4, 1, 5, 7), (1, 6, 1, 7)), ((1, 6, 1, 7), (4, 1, 5, 1)), ((4, 6, 5, 7), (7,)),
+        ((5, 7), (4, 6, 5, 7)), ((4, 6, 5, 7), (1,)), ((1,), (3, 2)), ((2, 3, 4, 5, 6), (1, 3, 1, 5, 1)),
+        ((2, 1, 3, 1, 2, 1, 3, 1), (1, 2, 1, 3, 1, 2, 1, 3)), ((33, 1), (1, 129)), ((8, 1, 64), (1, 3, 64)),
+        ((2, 3, 36), (2, 1, 36)), ((6, 1, 1), (1, 1, 9)),
+    ]
+    for i, (s1, s2) in enumerate(bshapes):
+        for opname in ("Add", "Mul", "Max", "Sub"):
+            cs.append(_case("binary_bcast%02d_%s" % (i, opname), "Binary", {"operation": orc.BINARY[opname]},
+                            [uniform(400 + i, s1), normal(500 + i, s2)]))
+    # ---- Unary ------------------------------------------------------------------------------
+    for opname, code in orc.UNARY.items():
+        if opname in ("Sqrt", "Log"):
+            x = uniform(600 + code, (1031,), 0.01, 10.0)
+        elif opname in ("Asin", "Acos"):
+            x = uniform(600 + code, (1031,), -1.0, 1.0)
+        else:
+            x = uniform(600 + code, (1031,), -10.0, 10.0)
+        cs.append(_case("unary_%s" % opname, "Unary", {"operation": code}, [x]))
+    for opname in ("Abs", "Square", "Sqrt", "Floor", "Ceil", "Neg", "Reciprocal"):
+        cs.append(_case("unary_special_%s" % opname, "Unary", {"operation": orc.UNARY[opname]}, [SPECIALS]))
+    for n in (1, 2, 3, 4, 5, 7, 8, 9, 31, 255, 256, 257, 1023, 4099):
+        cs.append(_case("unary_ragged_%d" % n, "Unary", {"operation": orc.UNARY["Neg"]}, [uniform(700 + n, (n,))]))
+    # ---- Activate ---------------------------------------------------------------------------
+    for opname, code in orc.ACTIVATE.items():
+        x = normal(800 + code, (2, 6, 5, 9), 0.0, 2.0)
+        if opname == "PRelu":
+            cs.append(_case("activate_prelu_chan", "Activate", {"type": 0}, [x, normal(850, (6,))]))
+            cs.append(_case("activate_prelu_shared", "Activate", {"type": 0}, [x, normal(851, (1,))]))
+            cs.append(_case("activate_prelu_2d", "Activate", {"type": 0},
+                            [normal(852, (7, 5)), normal(853, (5,))]))
+        else:
+            cs.append(_case("activate_%s" % opname, "Activate", {"type": code, "slope": float(np.float32(0.1))}, [x]))
+    for opname in ("Relu", "Leaky", "Relu6", "HardSwish"):
+        cs.append(_case("activate_special_%s" % opname, "Activate",
+                        {"type": orc.ACTIVATE[opname], "slope": float(np.float32(0.25))}, [SPECIALS]))
+    # ---- Scale ------------------------------------------------------------------------------
+    x = normal(900, (3, 8, 5, 7))
+    g, bt = normal(901, (8,), 1.0, 0.1), normal(902, (8,), 0.0, 0.1)
+    cs.append(_case("scale_blob_sb", "Scale", {"axis": 1, "has_scale": True, "has_bias": True}, [x, g, bt]))
+    cs.append(_case("scale_blob_s", "Scale", {"axis": 1, "has_scale": True}, [x, g]))
+    cs.append(_case("scale_blob_b", "Scale", {"axis": 1, "has_bias": True}, [x, bt]))
+    cs.append(_case("scale_blob_2axes", "Scale", {"axis": 1, "has_scale": True, "has_bias": True},
+                    [x, normal(903, (8, 5)), normal(904, (8, 5))]))
+    cs.append(_case("scale_blob_axis0", "Scale", {"axis": 0, "has_scale": True, "has_bias": True},
+                    [x, normal(905, (3,)), normal(906, (3,))]))
+    cs.append(_case("scale_blob_last", "Scale", {"axis": 3, "has_scale": True, "has_bias": True},
+                    [x, normal(907, (7,)), normal(908, (7,))]))
+    cs.append(_case("scale_value_sb", "Scale", {"axis": 1, "scale_value": [float(v) for v in g],
+                                                 "bias_value": [float(v) for v in bt]}, [x]))
+    cs.append(_case("scale_value_s1", "Scale", {"axis": 1, "scale_value": [1.5]}, [x]))
+    cs.append(_case("scale_value_b1", "Scale", {"axis": 2, "bias_value": [-0.25]}, [x]))
+    # the unfused multiply-add known answer: 0.3333333f*0.1f + (-0.033333331f) == +0 exactly
+    cs.append(_case("scale_unfused_kat", "Scale", {"axis": 1, "has_scale": True, "has_bias": True},
+                    [np.full((1, 1, 1, 4), 0.3333333, np.float32), np.array([0.1], np.float32),
+                     np.array([-0.033333331], np.float32)]))
+    # ---- Reduce -----------------------------------------------------------------------------
+    xr = normal(1000, (4, 6, 5, 7))
+    xp = uniform(1001, (4, 6, 5, 7), 0.9, 1.1)
+    axes_sets = [[2, 3], [1], [0, 2, 3], [0], [3], [0, 1, 2, 3], [], [1, 2], [0, 3], [1, 3], [0, 1], [0, 2]]
+    for opname, code in orc.REDUCE.items():
+        for ai, axes in enumerate(axes_sets):
+            for keep in (True, False):
+                cs.append(_case("reduce_%s_ax%d_k%d" % (opname, ai, int(keep)), "Reduce",
+                                {"operation": code, "axes": axes, "keep_dims": keep},
+                                [xp if opname == "Prod" else xr]))
+    cs.append(_case("reduce_long_row", "Reduce", {"operation": 1, "axes": [1], "keep_dims": True}, [normal(1002, (3, 5000))]))
+    cs.append(_case("reduce_long_col", "Reduce", {"operation": 1, "axes": [0], "keep_dims": True}, [normal(1003, (3000, 5))]))
+    cs.append(_case("reduce_1d_all", "Reduce", {"operation": 4, "axes": [], "keep_dims": False}, [normal(1004, (10007,))]))
+    cs.append(_case("reduce_unsorted_axes", "Reduce", {"operation": 1, "axes": [3, 1], "keep_dims": True}, [xr]))
+    nanrow = normal(1005, (4, 33))
+    nanrow[1, 5] = np.nan
+    nanrow[2, :] = -np.inf
+    cs.append(_case("reduce_max_nan", "Reduce", {"operation": 2, "axes": [1], "keep_dims": True}, [nanrow]))
+    cs.append(_case("reduce_min_nan", "Reduce", {"operation": 3, "axes": [1], "keep_dims": True}, [nanrow]))
+    cs.append(_case("reduce_one_elem", "Reduce", {"operation": 6, "axes": [], "keep_dims": True}, [np.array([[-3.0]], np.float32)]))
+    # ---- Softmax ----------------------------------------------------------------------------
+    cs.append(_case("softmax_rows", "Softmax", {"axis": 1}, [normal(1100, (37, 129), 0.0, 3.0)]))
+    cs.append(_case("softmax_rows_neg_axis", "Softmax", {"axis": -1}, [normal(1101, (5, 3, 64), 0.0, 3.0)]))
+    cs.append(_case("softmax_strided", "Softmax", {"axis": 1}, [normal(1102, (3, 50, 7, 7))]))
+    cs.append(_case("softmax_axis0", "Softmax", {"axis": 0}, [normal(1103, (19, 23))]))
+    cs.append(_case("softmax_mid", "Softmax", {"axis": 2}, [normal(1104, (2, 3, 11, 5))]))
+    cs.append(_case("softmax_dim1", "Softmax", {"axis": 1}, [normal(1105, (7, 1, 3))]))
+    cs.append(_case("softmax_long_row", "Softmax", {"axis": 1}, [normal(1106, (2, 20011), 0.0, 3.0)]))
+    cs.append(_case("softmax_huge_logits", "Softmax", {"axis": 1}, [normal(1107, (4, 300), 0.0, 200.0)]))
+    return cs
+
+
+def run_port(case) -> np.ndarray:
+    """Evaluate a case with the C restatement + Python front-end rules."""
+    op, a, x = case["op"], dict(case["args"]), case["inputs"]
+    if op == "Binary":
+        if "scalar" in a:
+            return orc.binary_scalar(x[0], a["scalar"], a["operation"])
+        return orc.binary(x[0], x[1], a["operation"])
+    if op == "Unary":
+        return orc.unary(x[0], a["operation"])
+    if op == "Activate":
+        t = a.get("type", 1)
+        return orc.activate(x[0], t, a.get("slope", 0.1), x[1] if t == 0 else None)
+    if op == "Scale":
+        axis = a.get("axis", 1)
+        hs, hb = a.get("has_scale", False), a.get("has_bias", False)
+        if hs and hb:
+            return orc.scale(x[0], axis, x[1], x[2])
+        if hs:
+            return orc.scale(x[0], axis, x[1], None)
+        if hb:
+            return orc.scale(x[0], axis, None, x[1])
+        dim = x[0].shape[axis]
+        sv, bv = list(a.get("scale_value", [])), list(a.get("bias_value", []))
+        sv = sv * dim if len(sv) == 1 else sv
+        bv = bv * dim if len(bv) == 1 else bv
+        return orc.scale(x[0], axis, np.array(sv, np.float32) if sv else None,
+                         np.array(bv, np.float32) if bv else None)
+    if op == "Reduce":
+        return orc.reduce(x[0], a.get("operation", 0), a.get("axes", []), a.get("keep_dims", True))
+    if op == "Softmax":
+        return orc.softmax(x[0], a.get("axis", 1))
+    raise KeyError(op)
+
+
+def run_net(library, case, backend="Native", device_id=0):
+    """Evaluate a case through the Network API of `library` (reference build or product)."""
+    from shadow_b200.netapi import Net
+    names = ["in%d" % i for i in range(len(case["inputs"]))]
+    net = Net(library, case["name"])
+    net.input({n: (x.shape if x.ndim else (1,)) for n, x in zip(names, case["inputs"])})
+    net.op(case["op"], names, ["out"], **case["args"])
+    net.load(backend, device_id=device_id, out_blobs=["out"])
+    net.forward(dict(zip(names, case["inputs"])))
+    return net.blob("out")
+
+
+def tolerance_class(case) -> str:
+    """'exact', 'ulp2' or 'rel' (relative error <= 1e-5*log2(n))."""
+    op, a = case["op"], case["args"]
+    if op == "Binary":
+        return "ulp2" if a["operation"] == 4 else "exact"
+    if op == "Unary":
+        return "ulp2" if a["operation"] in (3, 4, 5, 6, 7, 8, 9, 10) else "exact"
+    if op == "Activate":
+        return "ulp2" if a.get("type", 1) in (3, 4, 5, 8) else "exact"
+    if op == "Scale":
+        return "exact"
+    if op == "Reduce":
+        return "exact" if a.get("operation", 0) in (2, 3) else "rel"
+    return "rel"
