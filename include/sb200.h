@@ -1,0 +1,154 @@
+/*
+ * sb200 - C ABI of the B200 (sm_100a) tensor-operator kernels.
+ *
+ * These are the entry points a Shadow kernel class (`<Op>GPU(Default)` in the kernel registry,
+ * shadow/core/kernel.hpp:31-35) calls instead of the reference's `Blas::` / `Vision::` device
+ * functions.  Each declaration names the reference interface it replaces.
+ *
+ * Conventions
+ *  - every pointer is a DEVICE pointer to dense row-major float32 data unless it is documented
+ *    as a host array (shapes, axes);
+ *  - `stream` is a cudaStream_t passed as void* (Context::stream(), shadow/core/context.cu:69-72);
+ *    work is enqueued asynchronously on it and the call returns without synchronising;
+ *  - the caller's CUDA device must be current (the reference does cudaSetDevice in
+ *    Context::switch_device before running operators, shadow/core/context.cu:63);
+ *  - nothing here allocates or frees device memory; kernels that need scratch take a
+ *    caller-provided buffer (Workspace::GrowTempBuffer / CreateTempBlob,
+ *    shadow/core/workspace.cpp:83-123) whose size a *_scratch_bytes query returns;
+ *  - in-place operation (y == x) is allowed for the elementwise entry points, as in the
+ *    reference (Vision::Activate(out, out, ...), shadow/operators/kernels/conv.hpp:129), and
+ *    forbidden for reduce (shadow/operators/reduce_op.cpp:27); softmax also accepts y == x;
+ *  - return value: SB200_OK or an error code; bad arguments are rejected before any launch.
+ *    Launch errors are read with cudaGetLastError (the reference uses cudaPeekAtLastError in
+ *    CUDA_CHECK, shadow/core/external.hpp:39-43); asynchronous faults surface at the caller's
+ *    next synchronisation, as in the reference.
+ *  - element counts are 64-bit; a single call handles up to 2^40 elements.
+ */
+#ifndef SB200_H_
+#define SB200_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+  SB200_OK = 0,
+  SB200_ERR_BAD_ARGUMENT = 1, /* null pointer, negative size, unknown operation code, bad axis */
+  SB200_ERR_UNSUPPORTED = 2,  /* geometry outside what the kernels cover (more than 8 collapsed axes) */
+  SB200_ERR_CUDA = 3,         /* a CUDA runtime call or a launch failed; see sb200_last_cuda_error */
+  SB200_ERR_SCRATCH = 4       /* scratch buffer missing, misaligned or too small */
+};
+
+#define SB200_MAX_AXES 16 /* raw axes accepted; at most 8 remain after collapsing */
+
+const char* sb200_status_string(int status);
+/* Text of the CUDA error behind the calling thread's last SB200_ERR_CUDA ("" if none). */
+const char* sb200_last_cuda_error(void);
+/* Multiprocessor count of the current device (grid sizing uses it); -1 on error. */
+int sb200_device_sm_count(void);
+/* Number of kernels this library has launched so far in the calling process. */
+long long sb200_launch_count(void);
+
+/* Operation codes are the reference's own enums. */
+enum { SB200_ADD = 0, SB200_SUB = 1, SB200_MUL = 2, SB200_DIV = 3, SB200_POW = 4, SB200_MAX = 5, SB200_MIN = 6 };
+enum {
+  SB200_ABS = 0, SB200_SQUARE = 1, SB200_SQRT = 2, SB200_LOG = 3, SB200_EXP = 4, SB200_SIN = 5,
+  SB200_COS = 6, SB200_TAN = 7, SB200_ASIN = 8, SB200_ACOS = 9, SB200_ATAN = 10, SB200_FLOOR = 11,
+  SB200_CEIL = 12, SB200_NEG = 13, SB200_RECIPROCAL = 14
+};
+enum {
+  SB200_PRELU = 0, SB200_RELU = 1, SB200_LEAKY = 2, SB200_SIGMOID = 3, SB200_SOFTPLUS = 4,
+  SB200_TANH = 5, SB200_RELU6 = 6, SB200_HARDSWISH = 7, SB200_GELU = 8
+};
+enum {
+  SB200_RED_PROD = 0, SB200_RED_SUM = 1, SB200_RED_MAX = 2, SB200_RED_MIN = 3, SB200_RED_AVG = 4,
+  SB200_RED_L1 = 5, SB200_RED_L2 = 6
+};
+
+/* y[i] = val.  Replaces Blas::Set<kGPU,float>(n, val, y, offy, ctx)
+ * (shadow/core/blas.hpp:10-11, shadow/core/blas.cu:11-21). */
+int sb200_fill(float* y, int64_t n, float val, void* stream);
+
+/* y[i] = f(x[i]), f by SB200_ABS..SB200_RECIPROCAL.  Replaces the fifteen
+ * Blas::{Abs..Reciprocal}<kGPU,float>(n, a, offa, y, offy, ctx)
+ * (shadow/core/blas.hpp:31-49, shadow/core/blas.cu:77-108), called from
+ * UnaryKernelDefault::Run (shadow/operators/kernels/unary.hpp:35-97). */
+int sb200_unary(const float* x, float* y, int64_t n, int operation, void* stream);
+
+/* y[i] = act(x[i]) for SB200_RELU..SB200_GELU.  Replaces
+ * Vision::Activate<kGPU,float>(in, out, count, type, slope, ctx)
+ * (shadow/operators/kernels/activate.hpp:10-12, activate.cu:7-45). */
+int sb200_activate(const float* x, float* y, int64_t n, int type, float slope, void* stream);
+
+/* PReLU over x viewed as [outer, channels, dim]: y = x > 0 ? x : x * slope[c], c = channel index,
+ * or slope[0] when channel_shared.  Replaces Vision::PRelu<kGPU,float>(in, out, in_shape,
+ * channel_shared, slope, ctx) (shadow/operators/kernels/activate.hpp:14-16, activate.cu:47-71);
+ * outer = shape[0], channels = shape[1], dim = product of shape[2:]. */
+int sb200_prelu(const float* x, float* y, int64_t outer, int64_t channels, int64_t dim,
+                const float* slope, int channel_shared, void* stream);
+
+/* y[i] = a[i] op alpha.  Replaces Blas::{Add..Min}<kGPU,float>(n, a, offa, float alpha, y, offy, ctx)
+ * (shadow/core/blas.hpp:13-28, shadow/core/blas.cu:50-75). */
+int sb200_binary_scalar(const float* a, float alpha, float* y, int64_t n, int operation, void* stream);
+
+/* y[i] = a[i] op b[i].  Replaces Blas::{Add..Min}<kGPU,float>(n, a, offa, b, offb, y, offy, ctx)
+ * (shadow/core/blas.hpp:13-28, shadow/core/blas.cu:23-48). */
+int sb200_binary(const float* a, const float* b, float* y, int64_t n, int operation, void* stream);
+
+/* N-d broadcast binary.  a_shape, b_shape, out_shape are HOST arrays of num_axes ints (already
+ * rank-aligned: each input dim equals the output dim or is 1).  Replaces
+ * Vision::BroadcastBinary<kGPU,float>(in, in_shape, scalar, scalar_shape, operation, num_axes, count,
+ * out_shape, out, ctx) (shadow/operators/kernels/binary.hpp:11-15, binary.cu:7-64), which takes
+ * the three shapes as DEVICE arrays uploaded per call (binary.hpp:84-92); here they are collapsed
+ * on the host into strides passed by value, so no temp buffer and no upload is needed. */
+int sb200_binary_broadcast(const float* a, const int* a_shape, const float* b, const int* b_shape,
+                           const int* out_shape, int num_axes, float* y, int operation, void* stream);
+
+/* y[i] = x[i] * scale[c] + bias[c] with c = (i / inner_num) % scale_num; multiply and add are
+ * rounded separately (not fused), as the reference CPU build does.  scale == NULL gives
+ * y = x + bias[c], bias == NULL gives y = x * scale[c].  Replaces Vision::ScaleBias / Scale / Bias
+ * <kGPU,float>(in, count, scale, bias, scale_num, inner_num, out, ctx)
+ * (shadow/operators/kernels/scale.hpp:10-25, scale.cu:7-69). */
+int sb200_scale_bias(const float* x, float* y, int64_t n, const float* scale, const float* bias,
+                     int64_t scale_num, int64_t inner_num, void* stream);
+
+/* Reduce x (HOST shape in_shape[num_axes]) over the HOST list `axes` (non-negative, distinct,
+ * n_axes >= 1) with SB200_RED_*; y receives one float per kept position, row-major over the
+ * kept axes.  Prod/Sum/Avg/L1/L2 accumulate in double, Max/Min in float starting from
+ * -FLT_MAX/+FLT_MAX with NaNs skipped, as shadow/operators/kernels/reduce.cpp:9-65.
+ * Replaces ReduceKernelDefault::Run's table building plus
+ * Vision::Reduce<kGPU,float>(in, list, offset, num_list, operation, count, out, ctx)
+ * (shadow/operators/kernels/reduce.hpp:10-13,41-90, reduce.cu:7-85): the reference uploads an
+ * int offset list with one entry per reduced element on every call; here the geometry is
+ * collapsed on the host and no index table exists.
+ * `scratch` (256-byte aligned, sb200_reduce_scratch_bytes() bytes, may be NULL when that is 0)
+ * holds cross-block partials; its previous contents are ignored. */
+int64_t sb200_reduce_scratch_bytes(const int* in_shape, int num_axes, const int* axes, int n_axes,
+                                   int operation);
+int sb200_reduce(const float* x, const int* in_shape, int num_axes, const int* axes, int n_axes,
+                 int operation, float* y, void* scratch, int64_t scratch_bytes, void* stream);
+
+/* Two-step form for a tensor sharded over several GPUs on an axis that is being reduced: step 1
+ * writes one DOUBLE partial per kept position (sum for Sum/Avg/L1, sum of squares for L2, product
+ * for Prod, max/min value for Max/Min) so the caller can combine the shards' partials (sum, product,
+ * max or min across ranks); step 2 turns combined partials into the float result:
+ * cast (Sum, Prod, L1, Max, Min), divide by total_reduced_count then cast (Avg),
+ * sqrtf((float)p) (L2).  No counterpart in the reference, which is single-device. */
+int sb200_reduce_partial(const float* x, const int* in_shape, int num_axes, const int* axes,
+                         int n_axes, int operation, double* partial, void* scratch,
+                         int64_t scratch_bytes, void* stream);
+int sb200_reduce_finalize(const double* partial, float* y, int64_t count, int operation,
+                          int64_t total_reduced_count, void* stream);
+
+/* Softmax over the middle axis of x viewed as [outer, dim, inner]: max, exp(x - max), sum,
+ * divide, all in float.  Replaces Vision::Softmax<kGPU,float>(in, outer, dim, inner, val, out, ctx)
+ * (shadow/operators/kernels/softmax.hpp:10-12, softmax.cu:9-70); the reference's `val` scratch of
+ * outer*inner floats and its four launches are not needed. */
+int sb200_softmax(const float* x, float* y, int64_t outer, int64_t dim, int64_t inner, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* SB200_H_ */

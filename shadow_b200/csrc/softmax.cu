@@ -1,0 +1,232 @@
+// Softmax over the middle axis of x viewed as [outer, dim, inner].
+//
+// The reference makes four launches and six passes over memory (max, exp, sum, divide) with a
+// workspace of outer*inner floats.  Here the tensor is read once and written once, no scratch:
+//   inner == 1 (rows): a row lives in the registers of TPR threads (TPR = 32..1024, up to 8 float4
+//       per thread, so rows up to 32768 floats): one 128-bit read, warp-shuffle / shared-memory
+//       max and sum, one 128-bit write.  Longer rows use a block-per-row kernel that re-reads the
+//       row (from L2) for the second and third step.
+//   inner > 1 (strided): lanes run along `inner` (contiguous), the rows of the block walk `dim`;
+//       the [dim, 32] tile is staged in shared memory when it fits (up to 50 K floats), so global
+//       memory is still read once; otherwise the tile is re-read.
+// Arithmetic as the reference: float max, expf(x - max), float sum (tree order instead of the
+// reference's left-to-right order), IEEE division.  Algorithmic bytes: 8 per element.
+#include <float.h>
+
+#include "common.cuh"
+#include "math.cuh"
+
+namespace sb200 {
+namespace {
+
+// Reduce `v` over the TPR consecutive threads that share a row.  `red` is shared scratch with one
+// slot per warp of the block.  Every thread of the row gets the result.
+template <int TPR, typename Op>
+__device__ __forceinline__ float row_reduce(float v, Op op, float identity, float* red) {
+  if (TPR <= 32) {
+#pragma unroll
+    for (int o = TPR / 2; o > 0; o >>= 1) v = op(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+  } else {
+    constexpr int WPR = TPR / 32;  // warps per row
+    v = warp_reduce(v, op);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    const int first = (warp / WPR) * WPR;
+    float r = (lane < WPR) ? red[first + lane] : identity;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) r = op(r, __shfl_xor_sync(0xffffffffu, r, o));
+    return r;
+  }
+}
+
+// Rows in registers.  VEC: units are float4 (dim % 4 == 0, aligned), else single floats.
+// Each thread owns NV units: unit index = lane_in_row + i*TPR.
+template <int TPR, int NV, bool VEC, int BLOCK>
+__global__ void __launch_bounds__(BLOCK)
+softmax_rows_kernel(const float* x, float* y, int64_t rows, int units_per_row) {
+  constexpr int RPB = BLOCK / TPR;  // rows per block
+  constexpr int W = VEC ? 4 : 1;
+  __shared__ float red[BLOCK / 32];
+  const int t = threadIdx.x % TPR;
+  const int64_t row = static_cast<int64_t>(blockIdx.x) * RPB + threadIdx.x / TPR;
+  const bool live = row < rows;   // dead rows still take part in the barriers
+  const int64_t row_off = row * static_cast<int64_t>(units_per_row) * W;
+  float v[NV][W];
+  float m = -FLT_MAX;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int u = t + i * TPR;
+    if (live && u < units_per_row) {
+      if (VEC) {
+        float4 q = ld_stream(reinterpret_cast<const float4*>(x + row_off) + u);
+        v[i][0] = q.x; v[i][W > 1 ? 1 : 0] = q.y; v[i][W > 2 ? 2 : 0] = q.z; v[i][W > 3 ? 3 : 0] = q.w;
+      } else {
+        v[i][0] = ld_stream(x + row_off + u);
+      }
+#pragma unroll
+      for (int e = 0; e < W; ++e) m = std_max(v[i][e], m);
+    }
+  }
+  m = row_reduce<TPR>(m, OpMaxF(), -FLT_MAX, red);
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int u = t + i * TPR;
+    if (live && u < units_per_row) {
+#pragma unroll
+      for (int e = 0; e < W; ++e) {
+        v[i][e] = expf(__fsub_rn(v[i][e], m));
+        sum = __fadd_rn(sum, v[i][e]);
+      }
+    }
+  }
+  sum = row_reduce<TPR>(sum, OpAddF(), 0.f, red);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int u = t + i * TPR;
+    if (live && u < units_per_row) {
+      if (VEC) {
+        float4 q = make_float4(__fdiv_rn(v[i][0], sum), __fdiv_rn(v[i][W > 1 ? 1 : 0], sum),
+                               __fdiv_rn(v[i][W > 2 ? 2 : 0], sum), __fdiv_rn(v[i][W > 3 ? 3 : 0], sum));
+        st_stream(reinterpret_cast<float4*>(y + row_off) + u, q);
+      } else {
+        st_stream(y + row_off + u, __fdiv_rn(v[i][0], sum));
+      }
+    }
+  }
+}
+
+// Any row length: one block per row (grid-strided), three passes over the row.
+__global__ void __launch_bounds__(256)
+softmax_long_rows_kernel(const float* x, float* y, int64_t rows, int64_t dim) {
+  __shared__ float red[32];
+  for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
+    const float* xr = x + row * dim;
+    float* yr = y + row * dim;
+    float m = -FLT_MAX;
+    for (int64_t i = threadIdx.x; i < dim; i += 256) m = std_max(xr[i], m);
+    m = block_reduce(m, OpMaxF(), -FLT_MAX, red);
+    float sum = 0.f;
+    for (int64_t i = threadIdx.x; i < dim; i += 256) sum = __fadd_rn(sum, expf(__fsub_rn(xr[i], m)));
+    sum = block_reduce(sum, OpAddF(), 0.f, red);
+    for (int64_t i = threadIdx.x; i < dim; i += 256) yr[i] = __fdiv_rn(expf(__fsub_rn(xr[i], m)), sum);
+    __syncthreads();
+  }
+}
+
+// Strided: blockIdx.x = n * nbx + bx; block = 32 lanes along inner x TY rows along dim.
+constexpr int kTX = 32, kTY = 8;
+
+template <bool STAGE>
+__global__ void __launch_bounds__(kTX * kTY)
+softmax_strided_kernel(const float* x, float* y, int64_t dim, int64_t inner, int64_t nbx) {
+  extern __shared__ float tile[];   // [dim][32] when STAGE
+  __shared__ float red[kTY][kTX];
+  const int tx = threadIdx.x % kTX, ty = threadIdx.x / kTX;
+  const int64_t n = blockIdx.x / nbx, bx = blockIdx.x - n * nbx;
+  const int64_t s = bx * kTX + tx;
+  const bool live = s < inner;
+  const float* xp = x + n * dim * inner + s;
+  float* yp = y + n * dim * inner + s;
+  float m = -FLT_MAX;
+  if (live) {
+    for (int64_t c = ty; c < dim; c += kTY) {
+      float v = ld_stream(xp + c * inner);
+      if (STAGE) tile[c * kTX + tx] = v;
+      m = std_max(v, m);
+    }
+  }
+  red[ty][tx] = m;
+  __syncthreads();
+  m = red[0][tx];
+#pragma unroll
+  for (int r = 1; r < kTY; ++r) m = std_max(red[r][tx], m);
+  __syncthreads();
+  float sum = 0.f;
+  if (live) {
+    for (int64_t c = ty; c < dim; c += kTY) {
+      float v = STAGE ? tile[c * kTX + tx] : xp[c * inner];
+      float e = expf(__fsub_rn(v, m));
+      if (STAGE) tile[c * kTX + tx] = e;
+      sum = __fadd_rn(sum, e);
+    }
+  }
+  red[ty][tx] = sum;
+  __syncthreads();
+  sum = red[0][tx];
+#pragma unroll
+  for (int r = 1; r < kTY; ++r) sum = __fadd_rn(sum, red[r][tx]);
+  if (live) {
+    for (int64_t c = ty; c < dim; c += kTY) {
+      float e = STAGE ? tile[c * kTX + tx] : expf(__fsub_rn(xp[c * inner], m));
+      st_stream(yp + c * inner, __fdiv_rn(e, sum));
+    }
+  }
+}
+
+template <int TPR, int NV, bool VEC>
+void launch_rows(const float* x, float* y, int64_t rows, int units, cudaStream_t s) {
+  constexpr int BLOCK = TPR < 256 ? 256 : TPR;
+  constexpr int RPB = BLOCK / TPR;
+  const int64_t blocks = (rows + RPB - 1) / RPB;
+  softmax_rows_kernel<TPR, NV, VEC, BLOCK><<<static_cast<unsigned>(blocks), BLOCK, 0, s>>>(x, y, rows, units);
+}
+
+template <bool VEC>
+bool pick_rows(const float* x, float* y, int64_t rows, int units, cudaStream_t s) {
+  // smallest TPR whose per-thread unit count fits; NV rounded up to 1, 2, 4 or 8
+#define SB200_TRY(TPR, NV) \
+  if (units <= TPR * NV) { launch_rows<TPR, NV, VEC>(x, y, rows, units, s); return true; }
+  SB200_TRY(32, 1) SB200_TRY(32, 2) SB200_TRY(32, 4)
+  SB200_TRY(64, 4) SB200_TRY(128, 4) SB200_TRY(256, 4) SB200_TRY(512, 4) SB200_TRY(1024, 4)
+  SB200_TRY(1024, 8)
+#undef SB200_TRY
+  return false;
+}
+
+}  // namespace
+}  // namespace sb200
+
+using namespace sb200;
+
+extern "C" int sb200_softmax(const float* x, float* y, int64_t outer, int64_t dim, int64_t inner,
+                             void* stream) {
+  if (outer < 0 || dim < 1 || inner < 1) return SB200_ERR_BAD_ARGUMENT;
+  if (outer == 0) return SB200_OK;
+  if (x == nullptr || y == nullptr) return SB200_ERR_BAD_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 3u) return SB200_ERR_BAD_ARGUMENT;
+  if (outer * dim > (1ll << 40) / inner) return SB200_ERR_UNSUPPORTED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  if (inner == 1) {
+    const int64_t rows = outer;
+    if (rows >= (1ll << 31)) return SB200_ERR_UNSUPPORTED;
+    bool done = false;
+    if (dim % 4 == 0 && aligned16(x) && aligned16(y) && dim / 4 <= 1024 * 8)
+      done = pick_rows<true>(x, y, rows, static_cast<int>(dim / 4), s);
+    else if (dim <= 1024 * 8)
+      done = pick_rows<false>(x, y, rows, static_cast<int>(dim), s);
+    if (!done) {
+      const unsigned grid = stream_grid(rows, 8);
+      softmax_long_rows_kernel<<<grid, 256, 0, s>>>(x, y, rows, dim);
+    }
+    return after_launch("sb200_softmax");
+  }
+  const int64_t nbx = (inner + kTX - 1) / kTX;
+  if (outer * nbx >= (1ll << 31)) return SB200_ERR_UNSUPPORTED;
+  const unsigned grid = static_cast<unsigned>(outer * nbx);
+  const size_t tile_bytes = static_cast<size_t>(dim) * kTX * sizeof(float);
+  if (tile_bytes <= 200 * 1024) {
+    if (tile_bytes > 40 * 1024) {
+      cudaError_t err = cudaFuncSetAttribute(softmax_strided_kernel<true>,
+                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+      if (err != cudaSuccess) return cuda_failure(err, "sb200_softmax(cudaFuncSetAttribute)");
+    }
+    softmax_strided_kernel<true><<<grid, kTX * kTY, tile_bytes, s>>>(x, y, dim, inner, nbx);
+  } else {
+    softmax_strided_kernel<false><<<grid, kTX * kTY, 0, s>>>(x, y, dim, inner, nbx);
+  }
+  return after_launch("sb200_softmax");
+}

@@ -1,0 +1,189 @@
+"""Operator-level calls on CUDA tensors that are already resident in HBM.
+
+Each function applies the shape rule of the reference operator front-end
+(shadow/operators/{binary,unary,activate,scale,reduce,softmax}_op.cpp) and then makes exactly the
+C-ABI call(s) of ``include/sb200.h`` on the tensor's device pointers and the current torch stream.
+torch is used only for device memory and streams; all arithmetic happens in ``libsb200.so``.
+Inputs must be contiguous float32 CUDA tensors; there is no CPU path.
+"""
+from __future__ import annotations
+
+from typing import Optional, Sequence
+
+import torch
+
+from . import capi
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _chk(t: torch.Tensor, name: str) -> torch.Tensor:
+    if not (t.is_cuda and t.dtype == torch.float32 and t.is_contiguous()):
+        raise ValueError("%s must be a contiguous float32 CUDA tensor" % name)
+    return t
+
+
+def fill(y: torch.Tensor, val: float) -> torch.Tensor:
+    _chk(y, "y")
+    capi.check(capi.lib().sb200_fill(y.data_ptr(), y.numel(), val, _stream()), "sb200_fill")
+    return y
+
+
+def unary(x: torch.Tensor, operation: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _chk(x, "x")
+    y = torch.empty_like(x) if out is None else _chk(out, "out")
+    capi.check(capi.lib().sb200_unary(x.data_ptr(), y.data_ptr(), x.numel(), operation, _stream()), "sb200_unary")
+    return y
+
+
+def activate(x: torch.Tensor, type: int = 1, slope: float = 0.1, slope_blob: Optional[torch.Tensor] = None,
+             out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _chk(x, "x")
+    y = torch.empty_like(x) if out is None else _chk(out, "out")
+    if type == 0:
+        s = _chk(slope_blob, "slope_blob")
+        if x.dim() < 2:
+            raise ValueError("PRelu needs >= 2 axes")
+        shared = s.numel() == 1
+        if not shared and s.numel() != x.shape[1]:
+            raise ValueError("PRelu slope count must be 1 or channels")
+        dim = 1
+        for d in x.shape[2:]:
+            dim *= d
+        capi.check(capi.lib().sb200_prelu(x.data_ptr(), y.data_ptr(), x.shape[0], x.shape[1], dim,
+                                          s.data_ptr(), int(shared), _stream()), "sb200_prelu")
+    else:
+        capi.check(capi.lib().sb200_activate(x.data_ptr(), y.data_ptr(), x.numel(), type, slope, _stream()),
+                   "sb200_activate")
+    return y
+
+
+def binary_scalar(a: torch.Tensor, scalar: float, operation: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _chk(a, "a")
+    y = torch.empty_like(a) if out is None else _chk(out, "out")
+    capi.check(capi.lib().sb200_binary_scalar(a.data_ptr(), scalar, y.data_ptr(), a.numel(), operation, _stream()),
+               "sb200_binary_scalar")
+    return y
+
+
+def broadcast_shapes(sa: Sequence[int], sb: Sequence[int]):
+    sa, sb = list(sa), list(sb)
+    nd = max(len(sa), len(sb))
+    pa, pb = [1] * (nd - len(sa)) + sa, [1] * (nd - len(sb)) + sb
+    out = []
+    for da, db in zip(pa, pb):
+        if not (da == db or da == 1 or db == 1):
+            raise ValueError("shapes %s and %s do not broadcast" % (sa, sb))
+        out.append(max(da, db))
+    return pa, pb, out
+
+
+def binary(a: torch.Tensor, b: torch.Tensor, operation: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _chk(a, "a"), _chk(b, "b")
+    if tuple(a.shape) == tuple(b.shape):
+        y = torch.empty_like(a) if out is None else _chk(out, "out")
+        capi.check(capi.lib().sb200_binary(a.data_ptr(), b.data_ptr(), y.data_ptr(), a.numel(), operation,
+                                           _stream()), "sb200_binary")
+        return y
+    pa, pb, po = broadcast_shapes(a.shape, b.shape)
+    y = torch.empty(po, dtype=torch.float32, device=a.device) if out is None else _chk(out, "out")
+    capi.check(capi.lib().sb200_binary_broadcast(a.data_ptr(), capi.ints(pa), b.data_ptr(), capi.ints(pb),
+                                                 capi.ints(po), len(po), y.data_ptr(), operation, _stream()),
+               "sb200_binary_broadcast")
+    return y
+
+
+def scale(x: torch.Tensor, axis: int = 1, scale: Optional[torch.Tensor] = None,
+          bias: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _chk(x, "x")
+    ref = scale if scale is not None else bias
+    if ref is None:
+        raise ValueError("scale or bias required")
+    if scale is not None and bias is not None and tuple(scale.shape) != tuple(bias.shape):
+        raise ValueError("scale and bias shapes differ")
+    inner = 1
+    for d in x.shape[axis + ref.dim():]:
+        inner *= d
+    y = torch.empty_like(x) if out is None else _chk(out, "out")
+    capi.check(capi.lib().sb200_scale_bias(
+        x.data_ptr(), y.data_ptr(), x.numel(), scale.data_ptr() if scale is not None else None,
+        bias.data_ptr() if bias is not None else None, ref.numel(), inner, _stream()), "sb200_scale_bias")
+    return y
+
+
+class ReduceScratch:
+    """Grow-only device scratch, the analogue of Workspace::GrowTempBuffer for Python callers."""
+
+    def __init__(self):
+        self.buf: Optional[torch.Tensor] = None
+
+    def get(self, nbytes: int, device) -> int:
+        if nbytes <= 0:
+            return 0
+        if self.buf is None or self.buf.numel() < nbytes or self.buf.device != device:
+            self.buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        return self.buf.data_ptr()
+
+
+_scratch = ReduceScratch()
+
+
+def reduce(x: torch.Tensor, operation: int = 0, axes: Sequence[int] = (), keep_dims: bool = True,
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _chk(x, "x")
+    axes = list(axes) if len(axes) else list(range(x.dim()))
+    out_shape = list(x.shape)
+    for ax in axes:
+        out_shape[ax] = 1
+    y = torch.empty(out_shape, dtype=torch.float32, device=x.device) if out is None else _chk(out, "out")
+    shape_c, axes_c = capi.ints(x.shape), capi.ints(axes)
+    nbytes = capi.lib().sb200_reduce_scratch_bytes(shape_c, x.dim(), axes_c, len(axes), operation)
+    if nbytes < 0:
+        raise capi.Sb200Error(1, "sb200_reduce_scratch_bytes")
+    capi.check(capi.lib().sb200_reduce(x.data_ptr(), shape_c, x.dim(), axes_c, len(axes), operation, y.data_ptr(),
+                                       _scratch.get(nbytes, x.device), nbytes, _stream()), "sb200_reduce")
+    if not keep_dims:
+        y = y.reshape([d for n, d in enumerate(out_shape) if n not in axes])
+    return y
+
+
+def reduce_partial(x: torch.Tensor, operation: int, axes: Sequence[int]) -> torch.Tensor:
+    """Double partial per kept position (see sb200_reduce_partial); shape = x.shape with reduced dims 1."""
+    _chk(x, "x")
+    axes = list(axes) if len(axes) else list(range(x.dim()))
+    out_shape = list(x.shape)
+    for ax in axes:
+        out_shape[ax] = 1
+    part = torch.empty(out_shape, dtype=torch.float64, device=x.device)
+    shape_c, axes_c = capi.ints(x.shape), capi.ints(axes)
+    nbytes = capi.lib().sb200_reduce_scratch_bytes(shape_c, x.dim(), axes_c, len(axes), operation)
+    capi.check(capi.lib().sb200_reduce_partial(x.data_ptr(), shape_c, x.dim(), axes_c, len(axes), operation,
+                                               part.data_ptr(), _scratch.get(nbytes, x.device), nbytes, _stream()),
+               "sb200_reduce_partial")
+    return part
+
+
+def reduce_finalize(part: torch.Tensor, operation: int, total_reduced_count: int) -> torch.Tensor:
+    y = torch.empty(part.shape, dtype=torch.float32, device=part.device)
+    capi.check(capi.lib().sb200_reduce_finalize(part.data_ptr(), y.data_ptr(), part.numel(), operation,
+                                                total_reduced_count, _stream()), "sb200_reduce_finalize")
+    return y
+
+
+def softmax(x: torch.Tensor, axis: int = 1, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    _chk(x, "x")
+    if not -x.dim() <= axis < x.dim():
+        raise ValueError("axis out of range")
+    axis %= x.dim()
+    outer = 1
+    for d in x.shape[:axis]:
+        outer *= d
+    inner = 1
+    for d in x.shape[axis + 1:]:
+        inner *= d
+    y = torch.empty_like(x) if out is None else _chk(out, "out")
+    capi.check(capi.lib().sb200_softmax(x.data_ptr(), y.data_ptr(), outer, x.shape[axis], inner, _stream()),
+               "sb200_softmax")
+    return y

@@ -210,3 +210,74 @@ def tolerance_class(case) -> str:
     if op == "Reduce":
         return "exact" if a.get("operation", 0) in (2, 3) else "rel"
     return "rel"
+
+
+def run_cuda(case, device="cuda:0"):
+    """Evaluate a case through the kernel C ABI (shadow_b200.functional) on device tensors."""
+    import torch
+    from shadow_b200 import functional as F
+    op, a = case["op"], dict(case["args"])
+    x = [torch.from_numpy(np.ascontiguousarray(v)).to(device) for v in case["inputs"]]
+    if op == "Binary":
+        y = F.binary_scalar(x[0], a["scalar"], a["operation"]) if "scalar" in a else F.binary(x[0], x[1], a["operation"])
+    elif op == "Unary":
+        y = F.unary(x[0], a["operation"])
+    elif op == "Activate":
+        t = a.get("type", 1)
+        y = F.activate(x[0], t, a.get("slope", 0.1), x[1] if t == 0 else None)
+    elif op == "Scale":
+        axis = a.get("axis", 1)
+        hs, hb = a.get("has_scale", False), a.get("has_bias", False)
+        if hs and hb:
+            y = F.scale(x[0], axis, x[1], x[2])
+        elif hs:
+            y = F.scale(x[0], axis, x[1], None)
+        elif hb:
+            y = F.scale(x[0], axis, None, x[1])
+        else:
+            dim = x[0].shape[axis]
+            sv, bv = list(a.get("scale_value", [])), list(a.get("bias_value", []))
+            sv = sv * dim if len(sv) == 1 else sv
+            bv = bv * dim if len(bv) == 1 else bv
+            dev = lambda v: torch.tensor(v, dtype=torch.float32, device=device) if v else None  # noqa: E731
+            y = F.scale(x[0], axis, dev(sv), dev(bv))
+    elif op == "Reduce":
+        y = F.reduce(x[0], a.get("operation", 0), a.get("axes", []), a.get("keep_dims", True))
+    elif op == "Softmax":
+        y = F.softmax(x[0], a.get("axis", 1))
+    else:
+        raise KeyError(op)
+    torch.cuda.synchronize()
+    return y.cpu().numpy()
+
+
+def reduced_length(case) -> int:
+    x = case["inputs"][0]
+    if case["op"] == "Softmax":
+        return int(x.shape[case["args"].get("axis", 1)])
+    axes = case["args"].get("axes", []) or list(range(x.ndim))
+    return int(np.prod([x.shape[a] for a in axes]))
+
+
+def assert_parity(case, got: np.ndarray, want: np.ndarray):
+    """The parity bar: bit-exact / <= 2 ulp / relative error <= 1e-5*log2(n)."""
+    assert tuple(got.shape) == tuple(want.shape), (got.shape, want.shape)
+    cls = tolerance_class(case)
+    if cls == "exact":
+        assert orc.bit_equal(got, want), "%s: not bit-exact, max ulp %d at %d mismatches" % (
+            case["name"], int(orc.ulp_distance(got, want).max()), int((got.view(np.uint32) != want.view(np.uint32)).sum()))
+    elif cls == "ulp2":
+        d = orc.ulp_distance(got, want)
+        assert int(d.max()) <= 2, "%s: max ulp %d" % (case["name"], int(d.max()))
+    else:
+        n = max(reduced_length(case), 2)
+        tol = 1e-5 * np.log2(n)
+        g, w = got.astype(np.float64).ravel(), want.astype(np.float64).ravel()
+        both_nan = np.isnan(g) & np.isnan(w)
+        same_inf = np.isinf(g) & np.isinf(w) & (np.sign(g) == np.sign(w))
+        ok = both_nan | same_inf
+        err = np.abs(g - w)
+        denom = np.abs(w)
+        rel = np.where(ok, 0.0, np.where(denom > 0, err / np.maximum(denom, 1e-300), err))
+        # outputs that are exactly 0 in the reference (underflowed softmax terms) must be ~0 here
+        assert float(np.nanmax(rel)) <= tol, "%s: rel err %.3g > %.3g" % (case["name"], float(np.nanmax(rel)), tol)

@@ -1,0 +1,69 @@
+"""The C-ABI library loads and exports every symbol include/sb200.h declares; argument checks
+that happen before any launch.  Needs no GPU (no compute call is made)."""
+import os
+import re
+
+import pytest
+
+from shadow_b200 import build as sbuild
+from shadow_b200 import capi
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    sbuild.build_kernels()
+    return capi.lib()
+
+
+def declared_functions(header):
+    text = open(os.path.join(ROOT, "include", header)).read()
+    text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+    return sorted(set(re.findall(r"\b(sb200_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_every_declared_symbol_is_exported(lib):
+    names = declared_functions("sb200.h")
+    assert len(names) >= 17
+    for name in names:
+        assert hasattr(lib, name), name
+    assert sorted(capi.EXPORTED) == names
+
+
+def test_status_strings(lib):
+    assert capi.status_string(0) == "ok"
+    assert "argument" in capi.status_string(1)
+    assert "unknown" in capi.status_string(99)
+
+
+def test_bad_arguments_are_rejected_before_launch(lib):
+    before = capi.launch_count()
+    assert lib.sb200_unary(None, None, 16, 0, None) == 1
+    assert lib.sb200_unary(None, None, -1, 0, None) == 1
+    assert lib.sb200_unary(256, 512, 16, 99, None) == 1            # unknown operation code
+    assert lib.sb200_activate(256, 512, 16, 0, 0.1, None) == 1      # PReLU goes through sb200_prelu
+    assert lib.sb200_binary(256, None, 512, 16, 0, None) == 1
+    assert lib.sb200_binary_scalar(256, 1.0, 512, 16, 7, None) == 1
+    assert lib.sb200_scale_bias(256, 512, 16, None, None, 4, 4, None) == 1
+    assert lib.sb200_scale_bias(256, 512, 16, 1024, None, 0, 4, None) == 1
+    assert lib.sb200_softmax(256, 512, 4, 0, 1, None) == 1
+    assert lib.sb200_prelu(256, 512, 2, 3, 4, None, 0, None) == 1
+    shp, bad = capi.ints([2, 3]), capi.ints([2, 4])
+    assert lib.sb200_binary_broadcast(256, shp, 512, bad, shp, 2, 1024, 0, None) == 1   # 4 vs 3
+    assert lib.sb200_reduce(256, shp, 2, capi.ints([2]), 1, 1, 512, None, 0, None) == 1  # axis out of range
+    assert lib.sb200_reduce(256, shp, 2, capi.ints([1, 1]), 2, 1, 512, None, 0, None) == 1  # duplicate axis
+    assert lib.sb200_reduce(256, shp, 2, capi.ints([1]), 1, 9, 512, None, 0, None) == 1  # unknown op
+    assert lib.sb200_unary(258, 512, 16, 0, None) == 1              # not 4-byte aligned
+    assert capi.launch_count() == before
+    # zero-size calls succeed without launching
+    assert lib.sb200_unary(None, None, 0, 0, None) == 0
+    assert lib.sb200_fill(None, 0, 1.0, None) == 0
+    assert capi.launch_count() == before
+
+
+def test_missing_library_fails_loudly(monkeypatch):
+    monkeypatch.setattr(capi, "_lib", None)
+    monkeypatch.setattr(capi, "LIB_PATH", "/nonexistent/libsb200.so")
+    with pytest.raises(ImportError):
+        capi.lib()
