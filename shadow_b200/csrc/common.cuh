@@ -28,6 +28,13 @@ int sm_count();
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
+// Grid with one block per tile of `tile` units (at least one block so that edge work still runs).
+inline unsigned tile_grid(int64_t units, int64_t tile) {
+  int64_t blocks = (units + tile - 1) / tile;
+  if (blocks < 1) blocks = 1;
+  return static_cast<unsigned>(blocks);   // callers bound sizes at 2^40 elements: < 2^31 blocks
+}
+
 // Grid for a block-stride streaming kernel: as many blocks as there are tiles, capped at
 // `waves` resident blocks per SM times the SM count so the grid is a whole multiple of the SMs.
 inline unsigned stream_grid(int64_t tiles, int blocks_per_sm) {

@@ -32,6 +32,7 @@ namespace {
 constexpr int kMaxDims = 8;
 constexpr int kThreads = 256;
 constexpr int kUnroll = 4;
+constexpr int kChunkTiles = 8;   // tiles (kThreads*kUnroll units) per block in the split kernels
 
 // ---- per-operation arithmetic --------------------------------------------------------------------
 template <int OP>
@@ -134,6 +135,56 @@ redA_warp_kernel(const float* __restrict__ x, float* y, double* part, const __gr
     }
     acc = warp_reduce(acc, typename R::Merge());
     if (lane == 0) emit<OP, TO_PART>(acc, y, part, k, 0, g.K, g.count);
+  }
+}
+
+// Short rows (R0 == 1, at most 256 units per row): a block owns `rows_per_block` consecutive rows,
+// i.e. one contiguous chunk of up to 7*256 units.  Phase 1 loads the chunk with 7 independent
+// 128-bit loads per thread (coalesced, no per-row structure) and leaves one partial per unit in
+// shared memory; phase 2 gives every row to 8 lanes that combine its partials in a fixed order.
+constexpr int kRowsPerThread = 7;
+constexpr int kRowsUnits = kRowsPerThread * kThreads;
+
+template <int OP, bool VEC, bool TO_PART>
+__global__ void __launch_bounds__(kThreads)
+redA_rows_kernel(const float* __restrict__ x, float* y, double* part, int64_t K, int r1u,
+                 int rows_per_block, double count) {
+  using R = RedOp<OP>;
+  using Acc = typename R::Acc;
+  __shared__ Acc partial[kRowsUnits];
+  const int t = threadIdx.x;
+  const int64_t row0 = static_cast<int64_t>(blockIdx.x) * rows_per_block;
+  const int rows = static_cast<int>((K - row0) < rows_per_block ? (K - row0) : rows_per_block);
+  const int n_units = rows * r1u;
+  const float* base = x + row0 * r1u * (VEC ? 4 : 1);
+  float4 v4[kRowsPerThread];
+  float v1[kRowsPerThread];
+#pragma unroll
+  for (int i = 0; i < kRowsPerThread; ++i) {
+    const int idx = i * kThreads + t;
+    if (idx < n_units) {
+      if (VEC) v4[i] = ld_stream(reinterpret_cast<const float4*>(base) + idx);
+      else v1[i] = ld_stream(base + idx);
+    }
+  }
+#pragma unroll
+  for (int i = 0; i < kRowsPerThread; ++i) {
+    const int idx = i * kThreads + t;
+    if (idx < n_units) partial[idx] = VEC ? step4<OP>(R::init(), v4[i]) : R::step(R::init(), v1[i]);
+  }
+  __syncthreads();
+  const int lane8 = t & 7, group = (t >> 3) & 3, warp = t >> 5;
+  for (int rb = warp * 4; rb < rows; rb += (kThreads / 32) * 4) {   // warp-uniform trip count
+    const int r = rb + group;
+    Acc a = R::init();
+    if (r < rows) {
+      const Acc* p = partial + r * r1u;
+      for (int j = lane8; j < r1u; j += 8) a = R::merge(a, p[j]);
+    }
+    a = R::merge(a, __shfl_xor_sync(0xffffffffu, a, 4));
+    a = R::merge(a, __shfl_xor_sync(0xffffffffu, a, 2));
+    a = R::merge(a, __shfl_xor_sync(0xffffffffu, a, 1));
+    if (r < rows && lane8 == 0) emit<OP, TO_PART>(a, y, part, row0 + r, 0, K, count);
   }
 }
 
@@ -295,20 +346,23 @@ redG_kernel(const float* __restrict__ x, float* y, double* part, const __grid_co
 }
 
 // ---- finishing kernel: combine `splits` double partials per output, in split order ----------------
-// LANES = 1: one thread per output; LANES = 32: one warp per output (many splits, few outputs).
+// LANES = 1: one thread per output; 32: one warp per output; 256: one block per output (many
+// splits, few outputs, e.g. a full-tensor reduction).
 template <int OP, int LANES, bool TO_PART>
 __global__ void __launch_bounds__(kThreads)
 red_finish_kernel(const double* __restrict__ in, int64_t splits, int64_t n_out, float* y, double* part,
                   double count) {
   using R = RedOp<OP>;
   using Acc = typename R::Acc;
+  __shared__ Acc smem[32];
   const int64_t gid = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
   const int64_t o = gid / LANES;
   const int lane = static_cast<int>(gid % LANES);
-  if (o >= n_out) return;   // whole warps leave together when LANES == 32
+  if (o >= n_out) return;   // whole warps (LANES == 32) / whole blocks (256) leave together
   Acc acc = R::init();
   for (int64_t s = lane; s < splits; s += LANES) acc = R::merge(acc, static_cast<Acc>(in[s * n_out + o]));
   if (LANES == 32) acc = warp_reduce(acc, typename R::Merge());
+  if (LANES == 256) acc = block_reduce(acc, typename R::Merge(), R::init(), smem);
   if (lane == 0) emit<OP, TO_PART>(acc, y, part, o, 0, n_out, count);
 }
 
@@ -319,6 +373,8 @@ struct Plan {
   Family family;
   bool vec;
   bool a_warp;        // family A: warp-per-output kernel
+  bool a_rows;        // family A: staged short-rows kernel
+  int rows_per_block;
   int tx;             // family B
   int64_t splits;
   int64_t n_out, n_red;
@@ -352,7 +408,7 @@ int make_plan(const int* in_shape, int num_axes, const int* axes, int n_axes, co
   }
   if (nd > kMaxDims) return SB200_ERR_UNSUPPORTED;
   P->n_out = n_out, P->n_red = n_red, P->splits = 1, P->scratch_bytes = 0, P->vec = false;
-  P->a_warp = false, P->tx = 32;
+  P->a_warp = false, P->a_rows = false, P->rows_per_block = 1, P->tx = 32;
   const double count = static_cast<double>(n_red);
   const int64_t target_blocks = static_cast<int64_t>(sm_count()) * 8;
 
@@ -388,20 +444,28 @@ int make_plan(const int* in_shape, int num_axes, const int* axes, int n_axes, co
     g.row_elems = R1, g.r0_stride = K * R1;
     g.n_units = R0 * r1u;
     g.count = count;
-    if (g.n_units < 2048 && r1u < (1ll << 32)) {
+    if (R0 == 1 && r1u <= 256) {
+      P->a_rows = true;
+      P->rows_per_block = static_cast<int>(kRowsUnits / r1u);
+      g.R1u = static_cast<uint32_t>(r1u);
+      g.div_r1u = FastDiv32(g.R1u);
+      g.chunk_units = g.n_units;
+    } else if (g.n_units < 2048 && r1u < (1ll << 32)) {
       P->a_warp = true;
       g.R1u = static_cast<uint32_t>(r1u);
       g.div_r1u = FastDiv32(g.R1u);
       g.chunk_units = g.n_units;
     } else {
-      int64_t splits = 1;
-      if (K < target_blocks) {
+      // Many small blocks stream better than few long-running ones (see elementwise.cu): aim at
+      // kChunkTiles tiles per block, but never fewer blocks than fill the machine.
+      int64_t splits = (g.n_units + kThreads * kUnroll * kChunkTiles - 1) / (kThreads * kUnroll * kChunkTiles);
+      if (K * splits < target_blocks) {
         splits = (target_blocks + K - 1) / K;
         const int64_t max_by_work = (g.n_units + kThreads * kUnroll * 2 - 1) / (kThreads * kUnroll * 2);
         if (splits > max_by_work) splits = max_by_work;
-        if (splits > 65535) splits = 65535;
-        if (splits < 1) splits = 1;
       }
+      if (splits > 65535) splits = 65535;
+      if (splits < 1) splits = 1;
       int64_t chunk = (g.n_units + splits - 1) / splits;
       const int64_t tile = kThreads * kUnroll;
       chunk = (chunk + tile - 1) / tile * tile;
@@ -427,14 +491,14 @@ int make_plan(const int* in_shape, int num_axes, const int* axes, int n_axes, co
     g.nbx = (g.K1u + best_tx - 1) / best_tx;
     const int ty = kThreads / best_tx;
     const int64_t blocks = g.nbx * K0;
-    int64_t splits = 1;
-    if (blocks < target_blocks) {
+    int64_t splits = (Rm + ty * kUnroll * kChunkTiles - 1) / (ty * kUnroll * kChunkTiles);
+    if (blocks * splits < target_blocks) {
       splits = (target_blocks + blocks - 1) / blocks;
       const int64_t max_by_work = (Rm + ty * kUnroll - 1) / (ty * kUnroll);
       if (splits > max_by_work) splits = max_by_work;
-      if (splits > 65535) splits = 65535;
-      if (splits < 1) splits = 1;
     }
+    if (splits > 65535) splits = 65535;
+    if (splits < 1) splits = 1;
     int64_t chunk = (Rm + splits - 1) / splits;
     splits = (Rm + chunk - 1) / chunk;
     g.r_chunk = chunk;
@@ -458,7 +522,12 @@ int make_plan(const int* in_shape, int num_axes, const int* axes, int n_axes, co
 template <int OP, bool TO_PART>
 void launch_stage1(const Plan& P, const float* x, float* y, double* part, cudaStream_t s) {
   if (P.family == kFamA) {
-    if (P.a_warp) {
+    if (P.a_rows) {
+      const unsigned grid = tile_grid(P.a.K, P.rows_per_block);
+      const int r1u = static_cast<int>(P.a.R1u);
+      if (P.vec) redA_rows_kernel<OP, true, TO_PART><<<grid, kThreads, 0, s>>>(x, y, part, P.a.K, r1u, P.rows_per_block, P.a.count);
+      else redA_rows_kernel<OP, false, TO_PART><<<grid, kThreads, 0, s>>>(x, y, part, P.a.K, r1u, P.rows_per_block, P.a.count);
+    } else if (P.a_warp) {
       const int64_t blocks = (P.a.K * 32 + kThreads - 1) / kThreads;
       const unsigned grid = stream_grid(blocks, 8);
       if (P.vec) redA_warp_kernel<OP, true, TO_PART><<<grid, kThreads, 0, s>>>(x, y, part, P.a);
@@ -486,7 +555,9 @@ void launch_stage1(const Plan& P, const float* x, float* y, double* part, cudaSt
 template <int OP, bool TO_PART>
 void launch_finish(const double* in, int64_t splits, int64_t n_out, float* y, double* part, double count,
                    cudaStream_t s) {
-  if (splits > 8) {
+  if (splits > 256) {
+    red_finish_kernel<OP, 256, TO_PART><<<static_cast<unsigned>(n_out), kThreads, 0, s>>>(in, splits, n_out, y, part, count);
+  } else if (splits > 8) {
     const int64_t blocks = (n_out * 32 + kThreads - 1) / kThreads;
     red_finish_kernel<OP, 32, TO_PART><<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(in, splits, n_out, y, part, count);
   } else {

@@ -6,9 +6,10 @@
 //       per thread, so rows up to 32768 floats): one 128-bit read, warp-shuffle / shared-memory
 //       max and sum, one 128-bit write.  Longer rows use a block-per-row kernel that re-reads the
 //       row (from L2) for the second and third step.
-//   inner > 1 (strided): lanes run along `inner` (contiguous), the rows of the block walk `dim`;
-//       the [dim, 32] tile is staged in shared memory when it fits (up to 50 K floats), so global
-//       memory is still read once; otherwise the tile is re-read.
+//   inner > 1 (strided): lanes run along `inner` (contiguous), the warps of the block walk `dim`.
+//       dim <= 1024: each thread keeps its share of a column (up to 32 values) in registers, one
+//       read and one write; longer columns stage the [dim, 32] tile in shared memory when it
+//       fits (up to 50 K floats), else re-read it.
 // Arithmetic as the reference: float max, expf(x - max), float sum (tree order instead of the
 // reference's left-to-right order), IEEE division.  Algorithmic bytes: 8 per element.
 #include <float.h>
@@ -167,6 +168,56 @@ softmax_strided_kernel(const float* x, float* y, int64_t dim, int64_t inner, int
   }
 }
 
+// Strided, columns in registers: block = 32 lanes along inner x TY warps along dim (TY <= 32);
+// thread (tx, ty) keeps elements c = ty, ty+TY, ... of column tx in NC registers, so the tensor is
+// read once with NC independent loads in flight per thread.  Needs dim <= TY*NC <= 1024.
+template <int NC>
+__global__ void __launch_bounds__(1024)
+softmax_cols_kernel(const float* x, float* y, int64_t dim, int64_t inner, int64_t nbx) {
+  __shared__ float red[32][33];
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5, TY = blockDim.x >> 5;
+  const int64_t n = blockIdx.x / nbx, bx = blockIdx.x - n * nbx;
+  const int64_t s = bx * 32 + tx;
+  const bool live = s < inner;
+  const float* xp = x + n * dim * inner + s;
+  float* yp = y + n * dim * inner + s;
+  float v[NC];
+  float m = -FLT_MAX;
+#pragma unroll
+  for (int i = 0; i < NC; ++i) {
+    const int64_t c = ty + i * TY;
+    if (live && c < dim) v[i] = ld_stream(xp + c * inner);
+  }
+#pragma unroll
+  for (int i = 0; i < NC; ++i) {
+    const int64_t c = ty + i * TY;
+    if (live && c < dim) m = std_max(v[i], m);
+  }
+  red[ty][tx] = m;
+  __syncthreads();
+  m = red[0][tx];
+  for (int r = 1; r < TY; ++r) m = std_max(red[r][tx], m);
+  __syncthreads();
+  float sum = 0.f;
+#pragma unroll
+  for (int i = 0; i < NC; ++i) {
+    const int64_t c = ty + i * TY;
+    if (live && c < dim) {
+      v[i] = expf(__fsub_rn(v[i], m));
+      sum = __fadd_rn(sum, v[i]);
+    }
+  }
+  red[ty][tx] = sum;
+  __syncthreads();
+  sum = red[0][tx];
+  for (int r = 1; r < TY; ++r) sum = __fadd_rn(sum, red[r][tx]);
+#pragma unroll
+  for (int i = 0; i < NC; ++i) {
+    const int64_t c = ty + i * TY;
+    if (live && c < dim) st_stream(yp + c * inner, __fdiv_rn(v[i], sum));
+  }
+}
+
 template <int TPR, int NV, bool VEC>
 void launch_rows(const float* x, float* y, int64_t rows, int units, cudaStream_t s) {
   constexpr int BLOCK = TPR < 256 ? 256 : TPR;
@@ -217,6 +268,16 @@ extern "C" int sb200_softmax(const float* x, float* y, int64_t outer, int64_t di
   const int64_t nbx = (inner + kTX - 1) / kTX;
   if (outer * nbx >= (1ll << 31)) return SB200_ERR_UNSUPPORTED;
   const unsigned grid = static_cast<unsigned>(outer * nbx);
+  if (dim <= 1024) {
+    const int nc = dim <= 128 ? 4 : dim <= 256 ? 8 : dim <= 512 ? 16 : 32;
+    const int ty = static_cast<int>((dim + nc - 1) / nc);
+    const unsigned block = 32u * ty;
+    if (nc == 4) softmax_cols_kernel<4><<<grid, block, 0, s>>>(x, y, dim, inner, nbx);
+    else if (nc == 8) softmax_cols_kernel<8><<<grid, block, 0, s>>>(x, y, dim, inner, nbx);
+    else if (nc == 16) softmax_cols_kernel<16><<<grid, block, 0, s>>>(x, y, dim, inner, nbx);
+    else softmax_cols_kernel<32><<<grid, block, 0, s>>>(x, y, dim, inner, nbx);
+    return after_launch("sb200_softmax");
+  }
   const size_t tile_bytes = static_cast<size_t>(dim) * kTX * sizeof(float);
   if (tile_bytes <= 200 * 1024) {
     if (tile_bytes > 40 * 1024) {

@@ -1,5 +1,6 @@
 """GPU parity tests proper: every small case through the kernel C ABI against (a) the golden
 outputs of the compiled reference and (b) the C oracle run on the spot."""
+import hashlib
 import os
 
 import numpy as np
@@ -20,7 +21,11 @@ def golden():
 
 @pytest.mark.parametrize("case", SMALL, ids=[c["name"] for c in SMALL])
 def test_cabi_matches_reference_golden(case, golden):
-    want = golden[case["name"]]
+    want, digest, shape = cases.golden_lookup(golden, case["name"])
+    if want is None:
+        # digest-only fixture: the C oracle (itself pinned to that digest) supplies the values
+        want = cases.run_port(case)
+        assert hashlib.sha256(np.ascontiguousarray(want).tobytes()).digest() == digest
     got = cases.run_cuda(case)
+    assert list(got.shape) == shape
     cases.assert_parity(case, got.reshape(want.shape), want)
-    assert list(got.shape) == list(golden[case["name"] + "/shape"])

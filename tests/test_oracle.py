@@ -1,6 +1,7 @@
 """Pins the C restatement (oracle/oracle_port.c) to the reference: bit-for-bit against the golden
 outputs the compiled reference produced (tests/golden/small_cases.npz), and, where the compiled
 reference library is present, live against it on medium-size seeded tensors."""
+import hashlib
 import os
 
 import numpy as np
@@ -20,16 +21,18 @@ def golden():
 
 @pytest.mark.parametrize("case", SMALL, ids=[c["name"] for c in SMALL])
 def test_port_matches_reference_golden(case, golden):
-    want = golden[case["name"]]
-    want_shape = list(golden[case["name"] + "/shape"])
+    want, digest, want_shape = cases.golden_lookup(golden, case["name"])
     got = cases.run_port(case)
     assert list(got.shape) == want_shape
-    assert orc.bit_equal(got.reshape(want.shape), want), (
-        "max ulp %d" % int(orc.ulp_distance(got, want).max()))
+    if want is None:
+        assert hashlib.sha256(np.ascontiguousarray(got).tobytes()).digest() == digest
+    else:
+        assert orc.bit_equal(got.reshape(want.shape), want), (
+            "max ulp %d" % int(orc.ulp_distance(got, want).max()))
 
 
 def test_golden_covers_every_case(golden):
-    names = {k for k in golden.files if not k.endswith("/shape")}
+    names = {k[:-len("/shape")] for k in golden.files if k.endswith("/shape")}
     assert names == {c["name"] for c in SMALL}
 
 
