@@ -1,0 +1,474 @@
+#!/usr/bin/env python
+"""Benchmark of the tensor-operator hot path on B200.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl b200|reference]
+
+One STEP is one pass of the sharded large-tensor chain of the baseline configuration:
+broadcast Mul  A[8,1,2048,2048] x B[1,16,1,2048] -> O[8,16,2048,2048] (2 GiB), then a full-tensor
+ReduceSum and a full-tensor ReduceMax of O.  With N ranks (one process per GPU, torchrun) the
+tensor is split on dim 0 (STRONG scaling: the total work is the fixed 2 GiB tensor), B is
+replicated, and the per-rank double partials of each reduction are combined by one NCCL
+all-reduce.  Inputs are seeded synthetic tensors (U(-1,1) and N(0,1)) resident in HBM before the
+timed region; every step touches > 2 GiB per GPU at N=1 (> 256 MiB at N=8), larger than the
+126 MB L2, so no L2 flush is interposed.
+
+Reported on one JSON line: the whole-job effective HBM GB/s (algorithmic bytes of the step /
+max-over-ranks device time), the roofline of the dominant kernel (the broadcast Mul) measured
+live with CUDA events, the same metric end to end through the Shadow Network API with host
+buffers (e2e), a per-operator sweep at >= 256 MB sizes, and the reference's CPU implementation
+timed on the host cores (cpu_baseline).  `--impl reference` times only that CPU implementation.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+METRIC, UNIT = "effective_hbm_gb_per_s", "GB/s"
+NOMINAL_PEAK_GBS = 8000.0
+FALLBACK_PEAK_GBS = 6650.0
+A_SHAPE, B_SHAPE, O_SHAPE = (8, 1, 2048, 2048), (1, 16, 1, 2048), (8, 16, 2048, 2048)
+SEED_A, SEED_B = 20240650, 20240651
+MUL, RED_SUM, RED_MAX = 2, 1, 2
+
+
+def numel(shape):
+    n = 1
+    for d in shape:
+        n *= d
+    return n
+
+
+def step_bytes(a_shape, b_shape, o_shape):
+    """Algorithmic bytes: every input read once, every output written once, 4 B per element."""
+    mul = 4 * (numel(a_shape) + numel(b_shape) + numel(o_shape))
+    red = 4 * (numel(o_shape) + 1)
+    return {"binary_broadcast_mul": mul, "reduce_sum_all": red, "reduce_max_all": red}
+
+
+def make_inputs(a_shape, b_shape):
+    a = np.random.Generator(np.random.PCG64(SEED_A)).uniform(-1.0, 1.0, size=a_shape).astype(np.float32)
+    b = np.random.Generator(np.random.PCG64(SEED_B)).normal(0.0, 1.0, size=b_shape).astype(np.float32)
+    return a, b
+
+
+def measured_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_PEAK_GBS, "fallback"
+
+
+def ncu_traffic():
+    """DRAM bytes per launch of the dominant kernel from the committed ncu summary, or None."""
+    try:
+        with open(os.path.join(ROOT, "profiles", "traffic.json")) as f:
+            return json.load(f).get("bcast_reuse_kernel_c5_bytes_per_launch")
+    except Exception:
+        return None
+
+
+class ClockSampler:
+    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+
+    def __init__(self, index: int, period_s: float = 0.005):
+        self.index, self.period = index, period_s
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            self.nv = pynvml
+            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+        except Exception:
+            self.nv = None
+
+    def _loop(self):
+        nv = self.nv
+        names = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20,
+                 "hw_thermal_slowdown": 0x40, "hw_power_brake_slowdown": 0x80}
+        while not self._stop.is_set():
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def __enter__(self):
+        if self.nv is not None:
+            self._thread = threading.Thread(target=self._loop, daemon=True)
+            self._thread.start()
+        return self
+
+    def __exit__(self, *exc):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": sorted(self.reasons), "samples": 0}
+        return {"sm_mhz": int(statistics.median(self.samples)), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(self.samples)}
+
+
+# --------------------------------------------------------------------------------------------------
+# reference CPU implementation (oracle/_ref, else the C port) on a bounded sample
+# --------------------------------------------------------------------------------------------------
+SAMPLE_A, SAMPLE_B, SAMPLE_O = (1, 1, 512, 2048), (1, 16, 1, 2048), (1, 16, 512, 2048)
+SAMPLE_TEXT = "dim-0 slice 1 of 8 and rows 0..511 of 2048 of the workload: A[1,1,512,2048] x B[1,16,1,2048] " \
+              "-> [1,16,512,2048] (1/32 of the step), then full ReduceSum and ReduceMax"
+
+
+class CpuChain:
+    """The step's three operators on the sample, through the reference's Network API."""
+
+    def __init__(self):
+        from oracle import oracle as orc
+        self.orc = orc
+        self.lib = orc.ref_library()
+        self.kind = "reference" if self.lib is not None else "port"
+        self.net = None
+
+    def prepare(self, a, b):
+        self.a, self.b = a, b
+        if self.lib is not None:
+            from shadow_b200.netapi import Net
+            net = Net(self.lib, "c5_sample").input({"a": a.shape, "b": b.shape})
+            net.op("Binary", ["a", "b"], ["o"], operation=MUL)
+            net.op("Reduce", ["o"], ["s"], operation=RED_SUM, axes=[], keep_dims=False)
+            net.op("Reduce", ["o"], ["m"], operation=RED_MAX, axes=[], keep_dims=False)
+            net.load("Native", out_blobs=["s", "m"])
+            net.forward({"a": a, "b": b})   # first call: the reference builds its index tables here
+            self.net = net
+
+    def run(self):
+        if self.net is not None:
+            self.net.forward()              # operators only: inputs are already in the blobs
+            return float(self.net.blob("s").ravel()[0]), float(self.net.blob("m").ravel()[0])
+        o = self.orc.binary(self.a, self.b, MUL)
+        return (float(self.orc.reduce(o, RED_SUM, [], False).ravel()[0]),
+                float(self.orc.reduce(o, RED_MAX, [], False).ravel()[0]))
+
+
+def time_cpu(threads: int, steps: int, warmup: int):
+    """`threads` replicas of the sample chain run concurrently, one per host thread (the reference
+    path itself is single-threaded).  Returns (GB/s, ms per step, kind, results of replica 0)."""
+    a_full, b = make_inputs(A_SHAPE, B_SHAPE)
+    chains = []
+    for t in range(threads):
+        n = t % A_SHAPE[0]
+        r0 = (t // A_SHAPE[0]) * SAMPLE_A[2] % A_SHAPE[2]
+        a = np.ascontiguousarray(a_full[n:n + 1, :, r0:r0 + SAMPLE_A[2], :])
+        c = CpuChain()
+        chains.append((c, a))
+    del a_full
+
+    def prep(item):
+        item[0].prepare(item[1], b)
+
+    workers = [threading.Thread(target=prep, args=(it,)) for it in chains]
+    [w.start() for w in workers]
+    [w.join() for w in workers]
+    results = [None] * threads
+
+    def one_step():
+        def work(i):
+            results[i] = chains[i][0].run()
+        ws = [threading.Thread(target=work, args=(i,)) for i in range(threads)]
+        [w.start() for w in ws]
+        [w.join() for w in ws]
+
+    for _ in range(warmup):
+        one_step()
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        one_step()
+    dt = time.perf_counter() - t0
+    nbytes = sum(step_bytes(SAMPLE_A, SAMPLE_B, SAMPLE_O).values()) * threads
+    return nbytes * steps / dt / 1e9, dt / steps * 1e3, chains[0][0].kind, results[0], chains[0][1]
+
+
+def run_reference_arm(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    threads = max(1, min(os.cpu_count() or 1, 32))
+    steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 1))
+    gbs, ms, kind, _, _ = time_cpu(threads, steps, warmup)
+    line = {
+        "impl": "reference", "metric": METRIC, "value": round(gbs, 4), "unit": UNIT, "n_gpus": args.gpus,
+        "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 3), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "C5 chain (broadcast Mul -> ReduceSum all -> ReduceMax all) on the CPU",
+                   "sample": SAMPLE_TEXT, "replicas": threads},
+        "cpu_baseline": {"value": round(gbs, 4), "unit": UNIT, "cores": threads, "kind": kind,
+                         "sample": "%d concurrent replicas, each: %s" % (threads, SAMPLE_TEXT)},
+        "e2e": {"value": round(gbs, 4), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line))
+    return 0
+
+
+# --------------------------------------------------------------------------------------------------
+# B200 arm
+# --------------------------------------------------------------------------------------------------
+def per_op_sweep(torch, F, device, peak):
+    """Every operator family at a tensor size >= 256 MB (the roofline claim), L2-cold by size."""
+    def t(shape, lo=-1.0, hi=1.0):
+        return torch.empty(shape, device=device).uniform_(lo, hi)
+
+    rows = []
+
+    def bench(name, fn, nbytes, iters=10):
+        for _ in range(3):
+            fn()
+        torch.cuda.synchronize()
+        evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(iters)]
+        for a, b in evs:
+            a.record()
+            fn()
+            b.record()
+        torch.cuda.synchronize()
+        ms = statistics.median(a.elapsed_time(b) for a, b in evs)
+        gbs = nbytes / ms / 1e6
+        rows.append({"op": name, "bytes": nbytes, "ms": round(ms, 4), "gb_per_s": round(gbs, 1),
+                     "frac_of_8tbs": round(gbs / NOMINAL_PEAK_GBS, 4), "frac_of_measured": round(gbs / peak, 4)})
+
+    c1 = (512, 64, 56, 56)
+    a, c, y = t(c1), t(c1), torch.empty(c1, device=device)
+    b = torch.randn(1, 64, 1, 1, device=device)
+    n = a.numel()
+    for name, code in (("Add", 0), ("Mul", 2), ("Max", 5)):
+        bench("binary_broadcast_%s[512,64,56,56]+[1,64,1,1]" % name, lambda: F.binary(a, b, code, out=y), 8 * n + 256)
+    bench("binary_same_Add[512,64,56,56]", lambda: F.binary(a, c, 0, out=y), 12 * n)
+    del a, c, y
+    c2 = (256, 256, 28, 28)
+    x, y = torch.empty(c2, device=device).normal_(0, 2), torch.empty(c2, device=device)
+    n = x.numel()
+    for name, code in (("Relu", 1), ("Leaky", 2), ("Sigmoid", 3), ("Tanh", 5)):
+        bench("activate_%s[256,256,28,28]" % name, lambda: F.activate(x, code, 0.1, out=y), 8 * n)
+    x.uniform_(-10, 10)
+    bench("unary_Exp[256,256,28,28]", lambda: F.unary(x, 4, out=y), 8 * n)
+    x.uniform_(0.01, 10)
+    bench("unary_Log[256,256,28,28]", lambda: F.unary(x, 3, out=y), 8 * n)
+    bench("unary_Sqrt[256,256,28,28]", lambda: F.unary(x, 2, out=y), 8 * n)
+    g, bt = torch.randn(256, device=device) * 0.1 + 1, torch.randn(256, device=device) * 0.1
+    bench("scale[256,256,28,28]", lambda: F.scale(x, 1, g, bt, out=y), 8 * n + 8 * 256)
+    del x, y
+    c3 = (1024, 512, 14, 14)
+    x = torch.randn(c3, device=device)
+    n = x.numel()
+    for axes, outs in (((2, 3), 1024 * 512), ((1,), 1024 * 196), ((0, 2, 3), 512)):
+        for name, code in (("Sum", 1), ("Avg", 4), ("Max", 2), ("Min", 3)):
+            bench("reduce_%s%s[1024,512,14,14]" % (name, list(axes)), lambda: F.reduce(x, code, axes), 4 * (n + outs))
+    x.uniform_(0.99, 1.01)
+    bench("reduce_Prod[2, 3][1024,512,14,14]", lambda: F.reduce(x, 0, (2, 3)), 4 * (n + 1024 * 512))
+    del x
+    x, y = torch.empty(16384, 4096, device=device).normal_(0, 3), torch.empty(16384, 4096, device=device)
+    bench("softmax_rows[16384,4096]", lambda: F.softmax(x, -1, out=y), 8 * x.numel())
+    del x, y
+    x, y = torch.randn(1536, 1000, 7, 7, device=device), torch.empty(1536, 1000, 7, 7, device=device)
+    bench("softmax_strided_axis1[1536,1000,7,7]", lambda: F.softmax(x, 1, out=y), 8 * x.numel())
+    return rows
+
+
+def run_e2e(n_local, local_rank, a_host, b_host, steps, warmup, dist, torch):
+    """The chain through the Shadow Network API (C++ host library) with HOST buffers: Forward copies
+    the pinned inputs to the device, runs Binary/Reduce/Reduce, and the results are read back."""
+    import shadow_b200
+    from shadow_b200.netapi import Net
+    lib = shadow_b200.host_library()
+    a_shape = (n_local,) + A_SHAPE[1:]
+    net = Net(lib, "c5").input({"a": a_shape, "b": B_SHAPE})
+    net.op("Binary", ["a", "b"], ["o"], operation=MUL)
+    net.op("Reduce", ["o"], ["s"], operation=RED_SUM, axes=[], keep_dims=False)
+    net.op("Reduce", ["o"], ["m"], operation=RED_MAX, axes=[], keep_dims=False)
+    net.load("Native", device_id=local_rank, out_blobs=["s", "m"])
+    ins = {"a": a_host.data_ptr(), "b": b_host.data_ptr()}
+    world = dist.get_world_size() if dist is not None else 1
+    res = None
+    for i in range(warmup + steps):
+        if i == warmup:
+            if dist is not None:
+                dist.barrier()
+            t0 = time.perf_counter()
+        net.forward(ins)
+        s, m = float(net.blob("s").ravel()[0]), float(net.blob("m").ravel()[0])
+        if world > 1:
+            # the Network API is single-device, as in the reference: ranks combine their two scalars
+            pair = torch.tensor([s, m], dtype=torch.float64, device="cuda:%d" % local_rank)
+            gathered = [torch.empty_like(pair) for _ in range(world)]
+            dist.all_gather(gathered, pair)
+            s = float(sum(g[0].item() for g in gathered))
+            m = float(max(g[1].item() for g in gathered))
+        res = (s, m)
+    dt = time.perf_counter() - t0
+    if dist is not None:
+        tmax = torch.tensor([dt], dtype=torch.float64, device="cuda:%d" % local_rank)
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        dt = float(tmax.item())
+    h2d = a_host.numel() * 4 + b_host.numel() * 4
+    return dt / steps, h2d, 8, res
+
+
+def run_b200_arm(args):
+    import torch
+    from shadow_b200 import capi, sharded
+    from shadow_b200 import functional as F
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local_rank))
+    assert world == args.gpus or world == 1, "launch with torchrun --nproc-per-node %d" % args.gpus
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    capi.lib()   # fail loudly now if the CUDA library is missing
+
+    # ---- synthetic inputs: the rank's dim-0 slab of A (pinned on the host, then resident in HBM)
+    a_np, b_np = make_inputs(A_SHAPE, B_SHAPE)
+    lo, hi = sharded.shard_bounds(A_SHAPE[0], rank, world)
+    a_host = torch.from_numpy(np.ascontiguousarray(a_np[lo:hi])).pin_memory()
+    b_host = torch.from_numpy(b_np).pin_memory()
+    del a_np
+    n_local = hi - lo
+    A = a_host.to(device, non_blocking=True)
+    B = b_host.to(device, non_blocking=True)
+    O = torch.empty((n_local,) + O_SHAPE[1:], dtype=torch.float32, device=device)
+    torch.cuda.synchronize()
+
+    def step(evs=None):
+        if evs is not None:
+            evs[0].record()
+        F.binary(A, B, MUL, out=O)
+        if evs is not None:
+            evs[1].record()
+        s = sharded.reduce(O, RED_SUM, [], global_dim0=A_SHAPE[0], keep_dims=False)
+        if evs is not None:
+            evs[2].record()
+        m = sharded.reduce(O, RED_MAX, [], global_dim0=A_SHAPE[0], keep_dims=False)
+        if evs is not None:
+            evs[3].record()
+        return s, m
+
+    for _ in range(max(args.warmup, 3)):
+        s, m = step()
+    torch.cuda.synchronize()
+    if dist is not None:
+        dist.barrier()
+    torch.cuda.synchronize()
+    op_events = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    launches_before = capi.launch_count()
+    with ClockSampler(local_rank) as clocks:
+        start.record()
+        for k in range(args.steps):
+            s, m = step(op_events[k])
+        end.record()
+        torch.cuda.synchronize()
+    launches = capi.launch_count() - launches_before
+    ms_total = start.elapsed_time(end)
+    if dist is not None:
+        tmax = torch.tensor([ms_total], dtype=torch.float64, device=device)
+        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        ms_total = float(tmax.item())
+        dist.barrier()
+    ms_step = ms_total / args.steps
+    bytes_job = step_bytes(A_SHAPE, B_SHAPE, O_SHAPE)          # whole job, all ranks
+    bytes_rank = step_bytes((n_local,) + A_SHAPE[1:], B_SHAPE, (n_local,) + O_SHAPE[1:])
+    value = sum(bytes_job.values()) / ms_step / 1e6
+    op_ms = {
+        "binary_broadcast_mul": statistics.mean(e[0].elapsed_time(e[1]) for e in op_events),
+        "reduce_sum_all": statistics.mean(e[1].elapsed_time(e[2]) for e in op_events),
+        "reduce_max_all": statistics.mean(e[2].elapsed_time(e[3]) for e in op_events),
+    }
+    peak, peak_kind = measured_peak()
+    mul_gbs = bytes_rank["binary_broadcast_mul"] / op_ms["binary_broadcast_mul"] / 1e6
+    roofline = {"bound": "hbm", "kernel": "bcast_reuse_kernel (broadcast Mul, per rank)", "achieved": round(mul_gbs, 1),
+                "peak": peak, "peak_source": "MEASURED_PEAKS.json hbm_gbs" if peak_kind == "measured" else "fallback",
+                "unit": "GB/s", "frac": round(mul_gbs / peak, 4), "frac_of_8tbs": round(mul_gbs / NOMINAL_PEAK_GBS, 4),
+                "traffic": ncu_traffic()}
+    per_step_ops = {k: {"ms": round(v, 4), "gb_per_s_per_gpu": round(bytes_rank[k] / v / 1e6, 1)} for k, v in op_ms.items()}
+    result_sum, result_max = float(s.item()), float(m.item())
+
+    # ---- end to end through the Network API with host buffers
+    e2e_s, h2d, d2h, e2e_res = run_e2e(n_local, local_rank, a_host, b_host, max(3, min(args.steps, 10)), 2, dist, torch)
+    e2e_value = sum(bytes_job.values()) / e2e_s / 1e9
+
+    line = {
+        "metric": METRIC, "value": round(value, 2), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": round(ms_step, 4), "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": "C5 chain: broadcast Mul A[8,1,2048,2048]xB[1,16,1,2048] -> [8,16,2048,2048] (2 GiB), "
+                               "ReduceSum all axes, ReduceMax all axes; dim 0 split over the ranks",
+                   "l2": "inputs larger than L2 (each step streams >= 256 MiB per GPU; no flush interposed)",
+                   "bytes_per_step": sum(bytes_job.values()), "collective": "nccl all_reduce of 1 double per reduction" if world > 1 else "none"},
+        "frac_of_8tbs_per_gpu": round(value / world / NOMINAL_PEAK_GBS, 4),
+        "roofline": roofline, "per_step_ops": per_step_ops,
+        "e2e": {"value": round(e2e_value, 3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                "ms_per_step": round(e2e_s * 1e3, 3), "api": "Shadow::Network::Forward + GetBlobDataByName (C++ host library)"},
+        "gpu_launches": launches, "clocks": clocks.summary(),
+        "results": {"sum": result_sum, "max": result_max, "e2e_sum": e2e_res[0], "e2e_max": e2e_res[1]},
+    }
+    if rank == 0 and world == 1:
+        if not args.no_sweep:
+            line["per_op_256mb"] = per_op_sweep(torch, F, device, peak)
+        if not args.no_cpu:
+            gbs, ms, kind, cpu_res, a_sample = time_cpu(1, 3, 1)
+            # the same sample on the GPU, against the CPU result: parity of what was timed
+            As = torch.from_numpy(a_sample).to(device)
+            Os = F.binary(As, B, MUL)
+            gs = float(F.reduce(Os, RED_SUM, [], False).item())
+            gm = float(F.reduce(Os, RED_MAX, [], False).item())
+            tol = 1e-5 * np.log2(numel(SAMPLE_O))
+            line["cpu_baseline"] = {"value": round(gbs, 4), "unit": UNIT, "cores": 1, "kind": kind,
+                                    "sample": SAMPLE_TEXT, "ms_per_sample_step": round(ms, 2),
+                                    "sample_parity": bool(abs(gs - cpu_res[0]) <= tol * abs(cpu_res[0]) and gm == cpu_res[1])}
+    if rank == 0:
+        print(json.dumps(line))
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    return 0
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=50)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--no-sweep", action="store_true", help="skip the per-operator >=256 MB sweep")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        return run_reference_arm(args)
+    return run_b200_arm(args)
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,166 @@
+// The six GPU kernel classes, registered as "<Op>GPU(Default)".  Each Run translates blobs into
+// the raw pointers / sizes of the sb200 C ABI and enqueues on the workspace's stream.  A non-zero
+// status becomes a LOG(FATAL) (print + std::runtime_error), the reference's error convention.
+// There is no other implementation behind these classes: without libsb200 this file does not link.
+#include "op_kernels.hpp"
+#include "sb200.h"
+
+namespace Shadow {
+
+namespace {
+
+void expect_ok(int status, const char* what) {
+  if (status != SB200_OK) {
+    LOG(FATAL) << what << " failed: " << sb200_status_string(status)
+               << (status == SB200_ERR_CUDA ? std::string(" - ") + sb200_last_cuda_error() : std::string());
+  }
+}
+
+void* stream_of(Workspace* ws) { return ws->Ctx()->stream(); }
+
+class BinaryKernelB200 : public BinaryKernel {
+ public:
+  void Run(const BlobPtr& input, BlobPtr& output, Workspace* ws, int operation, float scalar_value) override {
+    expect_ok(sb200_binary_scalar(input->data<float>(), scalar_value, output->mutable_data<float>(),
+                                  static_cast<int64_t>(input->count64()), operation, stream_of(ws)),
+              "sb200_binary_scalar");
+  }
+  void Run(const BlobPtr& input, const BlobPtr& scalar, BlobPtr& output, Workspace* ws, int operation,
+           bool need_broadcast) override {
+    if (need_broadcast) {
+      // shapes stay on the host: no temp buffer, no upload
+      expect_ok(sb200_binary_broadcast(input->data<float>(), input->shape().data(), scalar->data<float>(),
+                                       scalar->shape().data(), output->shape().data(), input->num_axes(),
+                                       output->mutable_data<float>(), operation, stream_of(ws)),
+                "sb200_binary_broadcast");
+    } else {
+      expect_ok(sb200_binary(input->data<float>(), scalar->data<float>(), output->mutable_data<float>(),
+                             static_cast<int64_t>(input->count64()), operation, stream_of(ws)),
+                "sb200_binary");
+    }
+  }
+  DeviceType device_type() const override { return DeviceType::kGPU; }
+  std::string kernel_type() const override { return "Default"; }
+};
+
+class UnaryKernelB200 : public UnaryKernel {
+ public:
+  void Run(const BlobPtr& input, BlobPtr& output, Workspace* ws, int operation) override {
+    expect_ok(sb200_unary(input->data<float>(), output->mutable_data<float>(),
+                          static_cast<int64_t>(input->count64()), operation, stream_of(ws)),
+              "sb200_unary");
+  }
+  DeviceType device_type() const override { return DeviceType::kGPU; }
+  std::string kernel_type() const override { return "Default"; }
+};
+
+class ActivateKernelB200 : public ActivateKernel {
+ public:
+  void Run(const BlobPtr& input, const BlobPtr& slope, BlobPtr& output, Workspace* ws, int activate_type,
+           float slope_val) override {
+    if (activate_type == ActivateCode::kPRelu) {
+      CHECK_GE(input->num_axes(), 2);
+      CHECK_NOTNULL(slope);
+      const bool channel_shared = slope->count64() == 1;
+      if (!channel_shared) CHECK_EQ(slope->count(), input->shape(1));
+      int64_t dim = 1;
+      for (int n = 2; n < input->num_axes(); ++n) dim *= input->shape(n);
+      expect_ok(sb200_prelu(input->data<float>(), output->mutable_data<float>(), input->shape(0), input->shape(1),
+                            dim, slope->data<float>(), channel_shared ? 1 : 0, stream_of(ws)),
+                "sb200_prelu");
+    } else {
+      expect_ok(sb200_activate(input->data<float>(), output->mutable_data<float>(),
+                               static_cast<int64_t>(output->count64()), activate_type, slope_val, stream_of(ws)),
+                "sb200_activate");
+    }
+  }
+  DeviceType device_type() const override { return DeviceType::kGPU; }
+  std::string kernel_type() const override { return "Default"; }
+};
+
+class ScaleKernelB200 : public ScaleKernel {
+ public:
+  void Run(const BlobPtr& input, const BlobPtr& scale, const BlobPtr& bias, BlobPtr& output, Workspace* ws,
+           int axis) override {
+    CHECK(scale != nullptr || bias != nullptr);
+    if (scale != nullptr && bias != nullptr) CHECK(scale->shape() == bias->shape());
+    const BlobPtr& ref = scale != nullptr ? scale : bias;
+    const int inner = input->count(axis + ref->num_axes());
+    expect_ok(sb200_scale_bias(input->data<float>(), output->mutable_data<float>(),
+                               static_cast<int64_t>(input->count64()), scale ? scale->data<float>() : nullptr,
+                               bias ? bias->data<float>() : nullptr, ref->count(), inner, stream_of(ws)),
+              "sb200_scale_bias");
+  }
+
+  // Value form: the vectors are uploaded into the workspace temp buffer on every call, as the
+  // reference does (shadow/operators/kernels/scale.hpp:73-110).
+  void Run(const BlobPtr& input, BlobPtr& output, Workspace* ws, int axis, const VecFloat& scale_value,
+           const VecFloat& bias_value) override {
+    const int dim = input->shape(axis), inner = input->count(axis + 1);
+    CHECK(!scale_value.empty() || !bias_value.empty());
+    if (!scale_value.empty()) CHECK_EQ(static_cast<int>(scale_value.size()), dim);
+    if (!bias_value.empty()) CHECK_EQ(static_cast<int>(bias_value.size()), dim);
+    ws->GrowTempBuffer(2 * (static_cast<size_t>(dim) * sizeof(float) + 256));
+    BlobPtr scale, bias;
+    if (!scale_value.empty()) {
+      scale = ws->CreateTempBlob({dim}, DataType::kF32);
+      scale->set_data<float>(scale_value.data(), dim);
+    }
+    if (!bias_value.empty()) {
+      bias = ws->CreateTempBlob({dim}, DataType::kF32);
+      bias->set_data<float>(bias_value.data(), dim);
+    }
+    expect_ok(sb200_scale_bias(input->data<float>(), output->mutable_data<float>(),
+                               static_cast<int64_t>(input->count64()), scale ? scale->data<float>() : nullptr,
+                               bias ? bias->data<float>() : nullptr, dim, inner, stream_of(ws)),
+              "sb200_scale_bias");
+  }
+  DeviceType device_type() const override { return DeviceType::kGPU; }
+  std::string kernel_type() const override { return "Default"; }
+};
+
+class ReduceKernelB200 : public ReduceKernel {
+ public:
+  void Run(const BlobPtr& input, BlobPtr& output, Workspace* ws, int operation, const VecInt& axes) override {
+    CHECK(!axes.empty());
+    const int rank = input->num_axes();
+    const int64_t need = sb200_reduce_scratch_bytes(input->shape().data(), rank, axes.data(),
+                                                    static_cast<int>(axes.size()), operation);
+    CHECK_GE(need, 0) << "Reduce: bad axes";
+    void* scratch = nullptr;
+    if (need > 0) {
+      ws->GrowTempBuffer(static_cast<size_t>(need) + 256);
+      const int64_t ints = (need + 3) / 4;
+      CHECK_LE(ints, 0x7fffffff);
+      scratch = ws->CreateTempBlob({static_cast<int>(ints)}, DataType::kI32)->mutable_data<int>();
+    }
+    expect_ok(sb200_reduce(input->data<float>(), input->shape().data(), rank, axes.data(),
+                           static_cast<int>(axes.size()), operation, output->mutable_data<float>(), scratch, need,
+                           stream_of(ws)),
+              "sb200_reduce");
+  }
+  DeviceType device_type() const override { return DeviceType::kGPU; }
+  std::string kernel_type() const override { return "Default"; }
+};
+
+class SoftmaxKernelB200 : public SoftmaxKernel {
+ public:
+  void Run(const BlobPtr& input, BlobPtr& output, Workspace* ws, int axis) override {
+    const int64_t outer = input->count(0, axis), dim = input->shape(axis), inner = input->count(axis + 1);
+    expect_ok(sb200_softmax(input->data<float>(), output->mutable_data<float>(), outer, dim, inner, stream_of(ws)),
+              "sb200_softmax");
+  }
+  DeviceType device_type() const override { return DeviceType::kGPU; }
+  std::string kernel_type() const override { return "Default"; }
+};
+
+}  // namespace
+
+REGISTER_OP_KERNEL_DEFAULT(BinaryGPU, BinaryKernelB200);
+REGISTER_OP_KERNEL_DEFAULT(UnaryGPU, UnaryKernelB200);
+REGISTER_OP_KERNEL_DEFAULT(ActivateGPU, ActivateKernelB200);
+REGISTER_OP_KERNEL_DEFAULT(ScaleGPU, ScaleKernelB200);
+REGISTER_OP_KERNEL_DEFAULT(ReduceGPU, ReduceKernelB200);
+REGISTER_OP_KERNEL_DEFAULT(SoftmaxGPU, SoftmaxKernelB200);
+
+}  // namespace Shadow

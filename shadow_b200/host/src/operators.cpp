@@ -1,0 +1,251 @@
+// Operator front-ends of the six tensor operators (+ Input): argument parsing, shape inference and
+// the checks the reference makes, then one call into the registered kernel.  Argument names,
+// defaults and failure conditions follow shadow/operators/{binary,unary,activate,scale,reduce,
+// softmax,input}_op.cpp.
+#include <algorithm>
+
+#include "op_kernels.hpp"
+
+namespace Shadow {
+
+namespace {
+
+template <typename K>
+std::shared_ptr<K> kernel_for(const shadow::OpParam& op_param, Workspace* ws) {
+  auto kernel = std::dynamic_pointer_cast<K>(CreateKernel(op_param.type(), ws->Ctx()->device_type()));
+  CHECK_NOTNULL(kernel);
+  return kernel;
+}
+
+// Input: a pure placeholder; the backend shapes its tops from the v_i arguments named after them
+// (shadow/operators/input_op.cpp:7-17).
+class InputOp : public Operator {
+ public:
+  using Operator::Operator;
+  void Run(const std::vector<BlobPtr>&, std::vector<BlobPtr>&) override {}
+};
+
+// Binary (shadow/operators/binary_op.cpp:9-65): `operation` 0..6 is required; the presence of a
+// `scalar` argument selects the one-input form.  Two-input form: NumPy-style broadcast with the
+// lower rank left-padded by 1s; each dim must match or be 1; output dim is the larger.
+class BinaryOp : public Operator {
+ public:
+  BinaryOp(const shadow::OpParam& op_param, Workspace* ws) : Operator(op_param, ws) {
+    operation_ = get_single_argument<int>("operation", -1);
+    CHECK_GE(operation_, 0);
+    CHECK_LE(operation_, 6);
+    has_scalar_ = has_argument("scalar");
+    if (has_scalar_) scalar_value_ = get_single_argument<float>("scalar", 0);
+    kernel_ = kernel_for<BinaryKernel>(op_param, ws_);
+  }
+
+  void Run(const std::vector<BlobPtr>& inputs, std::vector<BlobPtr>& outputs) override {
+    CHECK_EQ(inputs.size(), has_scalar_ ? 1u : 2u);
+    const auto& lhs = inputs[0];
+    auto& out = outputs[0];
+    if (has_scalar_) {
+      out->reshape(lhs->shape());
+      kernel_->Run(lhs, out, ws_, operation_, scalar_value_);
+      return;
+    }
+    const auto& rhs = inputs[1];
+    if (lhs->shape() == rhs->shape()) {
+      out->reshape(lhs->shape());
+      kernel_->Run(lhs, rhs, out, ws_, operation_, false);
+      return;
+    }
+    // The kernel reads rank-aligned shapes from the blobs, so the shorter shape is padded for the
+    // duration of the call and restored afterwards, also when the call throws.
+    const VecInt lhs_shape = lhs->shape(), rhs_shape = rhs->shape();
+    struct Restore {
+      const BlobPtr &a, &b;
+      VecInt sa, sb;
+      ~Restore() { a->set_shape(sa), b->set_shape(sb); }
+    } restore{lhs, rhs, lhs_shape, rhs_shape};
+    const size_t rank = std::max(lhs_shape.size(), rhs_shape.size());
+    VecInt pl(rank - lhs_shape.size(), 1), pr(rank - rhs_shape.size(), 1);
+    pl.insert(pl.end(), lhs_shape.begin(), lhs_shape.end());
+    pr.insert(pr.end(), rhs_shape.begin(), rhs_shape.end());
+    lhs->set_shape(pl), rhs->set_shape(pr);
+    CHECK_EQ(lhs->num_axes(), rhs->num_axes());
+    VecInt out_shape;
+    for (size_t n = 0; n < rank; ++n) {
+      const int dl = pl[n], dr = pr[n];
+      CHECK(dl == dr || dl == 1 || dr == 1);
+      out_shape.push_back(std::max(dl, dr));
+    }
+    out->reshape(out_shape);
+    kernel_->Run(lhs, rhs, out, ws_, operation_, true);
+  }
+
+ private:
+  int operation_ = -1;
+  float scalar_value_ = 0.f;
+  bool has_scalar_ = false;
+  std::shared_ptr<BinaryKernel> kernel_;
+};
+
+// Unary (shadow/operators/unary_op.cpp:9-28): `operation` 0..14 required.
+class UnaryOp : public Operator {
+ public:
+  UnaryOp(const shadow::OpParam& op_param, Workspace* ws) : Operator(op_param, ws) {
+    operation_ = get_single_argument<int>("operation", -1);
+    CHECK_GE(operation_, 0);
+    CHECK_LE(operation_, 14);
+    kernel_ = kernel_for<UnaryKernel>(op_param, ws_);
+  }
+  void Run(const std::vector<BlobPtr>& inputs, std::vector<BlobPtr>& outputs) override {
+    outputs[0]->reshape(inputs[0]->shape());
+    kernel_->Run(inputs[0], outputs[0], ws_, operation_);
+  }
+
+ private:
+  int operation_;
+  std::shared_ptr<UnaryKernel> kernel_;
+};
+
+// Activate (shadow/operators/activate_op.cpp:9-34): `type` default 1 (ReLU), `slope` default 0.1;
+// PReLU (type 0) takes the slope blob as a second input.
+class ActivateOp : public Operator {
+ public:
+  ActivateOp(const shadow::OpParam& op_param, Workspace* ws) : Operator(op_param, ws) {
+    type_ = get_single_argument<int>("type", 1);
+    slope_ = get_single_argument<float>("slope", 0.1f);
+    CHECK_GE(type_, 0);
+    CHECK_LE(type_, 8);
+    kernel_ = kernel_for<ActivateKernel>(op_param, ws_);
+  }
+  void Run(const std::vector<BlobPtr>& inputs, std::vector<BlobPtr>& outputs) override {
+    const bool prelu = type_ == ActivateCode::kPRelu;
+    CHECK_EQ(inputs.size(), prelu ? 2u : 1u);
+    outputs[0]->reshape(inputs[0]->shape());
+    kernel_->Run(inputs[0], prelu ? inputs[1] : BlobPtr(), outputs[0], ws_, type_, slope_);
+  }
+
+ private:
+  int type_;
+  float slope_;
+  std::shared_ptr<ActivateKernel> kernel_;
+};
+
+// Scale (shadow/operators/scale_op.cpp:9-52): `axis` default 1; has_scale / has_bias (default
+// false) select blob inputs; otherwise scale_value / bias_value vectors (a single value is
+// repeated over the axis).
+class ScaleOp : public Operator {
+ public:
+  ScaleOp(const shadow::OpParam& op_param, Workspace* ws) : Operator(op_param, ws) {
+    axis_ = get_single_argument<int>("axis", 1);
+    has_scale_ = get_single_argument<bool>("has_scale", false);
+    has_bias_ = get_single_argument<bool>("has_bias", false);
+    scale_value_ = get_repeated_argument<float>("scale_value");
+    bias_value_ = get_repeated_argument<float>("bias_value");
+    kernel_ = kernel_for<ScaleKernel>(op_param, ws_);
+  }
+  void Run(const std::vector<BlobPtr>& inputs, std::vector<BlobPtr>& outputs) override {
+    const auto& in = inputs[0];
+    auto& out = outputs[0];
+    out->reshape(in->shape());
+    if (has_scale_ || has_bias_) {
+      CHECK_EQ(inputs.size(), (has_scale_ && has_bias_) ? 3u : 2u);
+      const BlobPtr none;
+      const BlobPtr& scale = has_scale_ ? inputs[1] : none;
+      const BlobPtr& bias = has_bias_ ? inputs[has_scale_ ? 2 : 1] : none;
+      kernel_->Run(in, scale, bias, out, ws_, axis_);
+      return;
+    }
+    const int dim = in->shape(axis_);
+    auto widen = [dim](VecFloat* v) {
+      if (v->size() > 1) {
+        CHECK_EQ(static_cast<int>(v->size()), dim);
+      } else if (v->size() == 1) {
+        *v = VecFloat(dim, (*v)[0]);
+      }
+    };
+    widen(&scale_value_), widen(&bias_value_);
+    kernel_->Run(in, out, ws_, axis_, scale_value_, bias_value_);
+  }
+
+ private:
+  int axis_;
+  bool has_scale_, has_bias_;
+  VecFloat scale_value_, bias_value_;
+  std::shared_ptr<ScaleKernel> kernel_;
+};
+
+// Reduce (shadow/operators/reduce_op.cpp:9-65): `operation` default 0 (Prod), `axes` (empty = all),
+// `keep_dims` default true.  In-place is refused.  Reduced dims become 1; with keep_dims false they
+// are squeezed after the kernel ran (all axes -> shape [] with one element).
+class ReduceOp : public Operator {
+ public:
+  ReduceOp(const shadow::OpParam& op_param, Workspace* ws) : Operator(op_param, ws) {
+    operation_ = get_single_argument<int>("operation", 0);
+    CHECK_GE(operation_, 0);
+    CHECK_LE(operation_, 6);
+    axes_ = get_repeated_argument<int>("axes");
+    keep_dims_ = get_single_argument<bool>("keep_dims", true);
+    kernel_ = kernel_for<ReduceKernel>(op_param, ws_);
+  }
+  void Run(const std::vector<BlobPtr>& inputs, std::vector<BlobPtr>& outputs) override {
+    const auto& in = inputs[0];
+    auto& out = outputs[0];
+    CHECK_NE(in, out);
+    const int rank = in->num_axes();
+    VecInt axes = axes_;
+    if (axes.empty()) {
+      for (int n = 0; n < rank; ++n) axes.push_back(n);
+    }
+    VecInt out_shape = in->shape();
+    for (int axis : axes) out_shape[in->canonical_index(axis)] = 1;
+    out->reshape(out_shape);
+    kernel_->Run(in, out, ws_, operation_, axes);
+    if (!keep_dims_) {
+      VecInt squeezed;
+      for (int n = 0; n < rank; ++n) {
+        const bool reduced = std::find(axes.begin(), axes.end(), n) != axes.end();
+        if (reduced) {
+          CHECK_EQ(out->shape(n), 1);
+        } else {
+          squeezed.push_back(out->shape(n));
+        }
+      }
+      out->set_shape(squeezed);
+    }
+  }
+
+ private:
+  int operation_;
+  bool keep_dims_;
+  VecInt axes_;
+  std::shared_ptr<ReduceKernel> kernel_;
+};
+
+// Softmax (shadow/operators/softmax_op.cpp:9-28): `axis` default 1, negative values count from
+// the end.
+class SoftmaxOp : public Operator {
+ public:
+  SoftmaxOp(const shadow::OpParam& op_param, Workspace* ws) : Operator(op_param, ws) {
+    axis_ = get_single_argument<int>("axis", 1);
+    kernel_ = kernel_for<SoftmaxKernel>(op_param, ws_);
+  }
+  void Run(const std::vector<BlobPtr>& inputs, std::vector<BlobPtr>& outputs) override {
+    axis_ = inputs[0]->canonical_index(axis_);
+    outputs[0]->reshape(inputs[0]->shape());
+    kernel_->Run(inputs[0], outputs[0], ws_, axis_);
+  }
+
+ private:
+  int axis_;
+  std::shared_ptr<SoftmaxKernel> kernel_;
+};
+
+}  // namespace
+
+REGISTER_OPERATOR(Input, InputOp);
+REGISTER_OPERATOR(Binary, BinaryOp);
+REGISTER_OPERATOR(Unary, UnaryOp);
+REGISTER_OPERATOR(Activate, ActivateOp);
+REGISTER_OPERATOR(Scale, ScaleOp);
+REGISTER_OPERATOR(Reduce, ReduceOp);
+REGISTER_OPERATOR(Softmax, SoftmaxOp);
+
+}  // namespace Shadow
