@@ -262,18 +262,18 @@ def per_op_sweep(torch, F, device, peak):
         bench("binary_broadcast_%s[512,64,56,56]+[1,64,1,1]" % name, lambda: F.binary(a, b, code, out=y), 8 * n + 256)
     bench("binary_same_Add[512,64,56,56]", lambda: F.binary(a, c, 0, out=y), 12 * n)
     del a, c, y
-    c2 = (256, 256, 28, 28)
+    c2 = (512, 256, 28, 28)
     x, y = torch.empty(c2, device=device).normal_(0, 2), torch.empty(c2, device=device)
     n = x.numel()
     for name, code in (("Relu", 1), ("Leaky", 2), ("Sigmoid", 3), ("Tanh", 5)):
-        bench("activate_%s[256,256,28,28]" % name, lambda: F.activate(x, code, 0.1, out=y), 8 * n)
+        bench("activate_%s[512,256,28,28]" % name, lambda: F.activate(x, code, 0.1, out=y), 8 * n)
     x.uniform_(-10, 10)
-    bench("unary_Exp[256,256,28,28]", lambda: F.unary(x, 4, out=y), 8 * n)
+    bench("unary_Exp[512,256,28,28]", lambda: F.unary(x, 4, out=y), 8 * n)
     x.uniform_(0.01, 10)
-    bench("unary_Log[256,256,28,28]", lambda: F.unary(x, 3, out=y), 8 * n)
-    bench("unary_Sqrt[256,256,28,28]", lambda: F.unary(x, 2, out=y), 8 * n)
+    bench("unary_Log[512,256,28,28]", lambda: F.unary(x, 3, out=y), 8 * n)
+    bench("unary_Sqrt[512,256,28,28]", lambda: F.unary(x, 2, out=y), 8 * n)
     g, bt = torch.randn(256, device=device) * 0.1 + 1, torch.randn(256, device=device) * 0.1
-    bench("scale[256,256,28,28]", lambda: F.scale(x, 1, g, bt, out=y), 8 * n + 8 * 256)
+    bench("scale[512,256,28,28]", lambda: F.scale(x, 1, g, bt, out=y), 8 * n + 8 * 256)
     del x, y
     c3 = (1024, 512, 14, 14)
     x = torch.randn(c3, device=device)
@@ -332,6 +332,9 @@ def run_e2e(n_local, local_rank, a_host, b_host, steps, warmup, dist, torch):
 
 
 def run_b200_arm(args):
+    global A_SHAPE, O_SHAPE
+    if args.batch != A_SHAPE[0]:
+        A_SHAPE, O_SHAPE = (args.batch,) + A_SHAPE[1:], (args.batch,) + O_SHAPE[1:]
     import torch
     from shadow_b200 import capi, sharded
     from shadow_b200 import functional as F
@@ -416,7 +419,10 @@ def run_b200_arm(args):
     result_sum, result_max = float(s.item()), float(m.item())
 
     # ---- end to end through the Network API with host buffers
-    e2e_s, h2d, d2h, e2e_res = run_e2e(n_local, local_rank, a_host, b_host, max(3, min(args.steps, 10)), 2, dist, torch)
+    if args.no_e2e:
+        e2e_s, h2d, d2h, e2e_res = float("nan"), 0, 0, (None, None)
+    else:
+        e2e_s, h2d, d2h, e2e_res = run_e2e(n_local, local_rank, a_host, b_host, max(3, min(args.steps, 10)), 2, dist, torch)
     e2e_value = sum(bytes_job.values()) / e2e_s / 1e9
 
     line = {
@@ -429,7 +435,7 @@ def run_b200_arm(args):
                    "bytes_per_step": sum(bytes_job.values()), "collective": "nccl all_reduce of 1 double per reduction" if world > 1 else "none"},
         "frac_of_8tbs_per_gpu": round(value / world / NOMINAL_PEAK_GBS, 4),
         "roofline": roofline, "per_step_ops": per_step_ops,
-        "e2e": {"value": round(e2e_value, 3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+        "e2e": None if args.no_e2e else {"value": round(e2e_value, 3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": round(e2e_s * 1e3, 3), "api": "Shadow::Network::Forward + GetBlobDataByName (C++ host library)"},
         "gpu_launches": launches, "clocks": clocks.summary(),
         "results": {"sum": result_sum, "max": result_max, "e2e_sum": e2e_res[0], "e2e_max": e2e_res[1]},
@@ -464,6 +470,9 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-sweep", action="store_true", help="skip the per-operator >=256 MB sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end (host buffers) leg")
+    ap.add_argument("--batch", type=int, default=A_SHAPE[0],
+                    help="dim 0 of A (default 8 = the baseline configuration; smaller only for profiler captures)")
     args = ap.parse_args()
     if args.impl == "reference":
         return run_reference_arm(args)
