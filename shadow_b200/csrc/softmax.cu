@@ -10,8 +10,11 @@
 //       dim <= 1024: each thread keeps its share of a column (up to 32 values) in registers, one
 //       read and one write; longer columns stage the [dim, 32] tile in shared memory when it
 //       fits (up to 50 K floats), else re-read it.
-// Arithmetic as the reference: float max, expf(x - max), float sum (tree order instead of the
-// reference's left-to-right order), IEEE division.  Algorithmic bytes: 8 per element.
+// Arithmetic: float max, expf(x - max), float sum (tree order instead of the reference's
+// left-to-right order), then one correctly rounded reciprocal per row and a multiply per element
+// instead of the reference's per-element division (an IEEE float division costs ~60 issue slots on
+// this part and capped the row kernel; the result differs by at most 1 ulp, inside the softmax
+// tolerance of 1e-5*log2(n) relative).  Algorithmic bytes: 8 per element.
 #include <float.h>
 
 #include "common.cuh"
@@ -85,16 +88,17 @@ softmax_rows_kernel(const float* x, float* y, int64_t rows, int units_per_row) {
     }
   }
   sum = row_reduce<TPR>(sum, OpAddF(), 0.f, red);
+  const float inv = __frcp_rn(sum);
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     const int u = t + i * TPR;
     if (live && u < units_per_row) {
       if (VEC) {
-        float4 q = make_float4(__fdiv_rn(v[i][0], sum), __fdiv_rn(v[i][W > 1 ? 1 : 0], sum),
-                               __fdiv_rn(v[i][W > 2 ? 2 : 0], sum), __fdiv_rn(v[i][W > 3 ? 3 : 0], sum));
+        float4 q = make_float4(__fmul_rn(v[i][0], inv), __fmul_rn(v[i][W > 1 ? 1 : 0], inv),
+                               __fmul_rn(v[i][W > 2 ? 2 : 0], inv), __fmul_rn(v[i][W > 3 ? 3 : 0], inv));
         st_stream(reinterpret_cast<float4*>(y + row_off) + u, q);
       } else {
-        st_stream(y + row_off + u, __fdiv_rn(v[i][0], sum));
+        st_stream(y + row_off + u, __fmul_rn(v[i][0], inv));
       }
     }
   }
@@ -113,7 +117,8 @@ softmax_long_rows_kernel(const float* x, float* y, int64_t rows, int64_t dim) {
     float sum = 0.f;
     for (int64_t i = threadIdx.x; i < dim; i += 256) sum = __fadd_rn(sum, expf(__fsub_rn(xr[i], m)));
     sum = block_reduce(sum, OpAddF(), 0.f, red);
-    for (int64_t i = threadIdx.x; i < dim; i += 256) yr[i] = __fdiv_rn(expf(__fsub_rn(xr[i], m)), sum);
+    const float inv = __frcp_rn(sum);
+    for (int64_t i = threadIdx.x; i < dim; i += 256) yr[i] = __fmul_rn(expf(__fsub_rn(xr[i], m)), inv);
     __syncthreads();
   }
 }
@@ -160,10 +165,11 @@ softmax_strided_kernel(const float* x, float* y, int64_t dim, int64_t inner, int
   sum = red[0][tx];
 #pragma unroll
   for (int r = 1; r < kTY; ++r) sum = __fadd_rn(sum, red[r][tx]);
+  const float inv = __frcp_rn(sum);
   if (live) {
     for (int64_t c = ty; c < dim; c += kTY) {
       float e = STAGE ? tile[c * kTX + tx] : expf(__fsub_rn(xp[c * inner], m));
-      st_stream(yp + c * inner, __fdiv_rn(e, sum));
+      st_stream(yp + c * inner, __fmul_rn(e, inv));
     }
   }
 }
@@ -211,10 +217,11 @@ softmax_cols_kernel(const float* x, float* y, int64_t dim, int64_t inner, int64_
   __syncthreads();
   sum = red[0][tx];
   for (int r = 1; r < TY; ++r) sum = __fadd_rn(sum, red[r][tx]);
+  const float inv = __frcp_rn(sum);
 #pragma unroll
   for (int i = 0; i < NC; ++i) {
     const int64_t c = ty + i * TY;
-    if (live && c < dim) st_stream(yp + c * inner, __fdiv_rn(v[i], sum));
+    if (live && c < dim) st_stream(yp + c * inner, __fmul_rn(v[i], inv));
   }
 }
 
