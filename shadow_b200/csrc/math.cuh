@@ -49,12 +49,13 @@ __device__ __forceinline__ double exp_core(float x) {
 }
 
 __device__ __forceinline__ float exp_accurate(float x) {
-  if (!(x == x)) return x + x;              // NaN
-  if (x > 90.f) return CUDART_INF_F;        // float overflow threshold is 88.7228
-  if (x < -105.f) return 0.f;               // below half the smallest denormal (-103.97)
-  // denormal results come out right: the scaling is done in double and the single conversion
-  // to float rounds into the denormal range
-  return static_cast<float>(exp_core(x));
+  // Branch-free: clamp into the range where exp_core is valid.  e^-105 converts to 0 and e^90 to
+  // +inf, which are the float results for everything beyond the clamp; denormal results come out
+  // right because the scaling is done in double and the single conversion to float rounds into
+  // the denormal range.  fminf/fmaxf drop a NaN, so it is put back at the end.
+  const float xc = fminf(fmaxf(x, -105.f), 90.f);
+  const float y = static_cast<float>(exp_core(xc));
+  return (x == x) ? y : x;
 }
 
 // 1/d for a double d in [2, 1e9], relative error ~1e-14: hardware float reciprocal as the seed,
@@ -69,13 +70,12 @@ __device__ __forceinline__ double rcp_newton(double d) {
 // tanh(x) = 1 - 2/(e^{2|x|} + 1) in double, rounded once; for |x| < 2^-12 the float result is x
 // itself (tanh x = x - x^3/3 and the correction is below half an ulp).
 __device__ __forceinline__ float tanh_accurate(float x) {
-  const float ax = fabsf(x);
-  if (!(x == x)) return x + x;
-  if (ax < 2.44140625e-4f) return x;
-  if (ax > 10.f) return copysignf(1.f, x);      // 1 - 2e^{-20} rounds to 1 in float
-  const double e = exp_core(ax + ax);           // e^{2|x|} in [1, 4.9e8]
+  const float ax = fminf(fabsf(x), 10.f);         // beyond 10, 1 - 2e^{-2|x|} rounds to 1 (also for inf)
+  const double e = exp_core(ax + ax);             // e^{2|x|} in [1, 4.9e8]
   const double t = fma(-2.0, rcp_newton(e + 1.0), 1.0);
-  return copysignf(static_cast<float>(t), x);
+  float y = copysignf(static_cast<float>(t), x);
+  y = (fabsf(x) < 2.44140625e-4f) ? x : y;        // tiny arguments (and +-0) return x itself
+  return (x == x) ? y : x;                        // NaN
 }
 
 // ---- functors -----------------------------------------------------------------------------------
