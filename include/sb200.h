@@ -130,6 +130,28 @@ int64_t sb200_reduce_scratch_bytes(const int* in_shape, int num_axes, const int*
 int sb200_reduce(const float* x, const int* in_shape, int num_axes, const int* axes, int n_axes,
                  int operation, float* y, void* scratch, int64_t scratch_bytes, void* stream);
 
+/* Same reduction as sb200_reduce for callers that have no scratch buffer to pass and must not
+ * allocate one.  It has no counterpart in the reference (whose kernels always take their temp
+ * memory from the Workspace).  Who needs it: code running after all device memory has been handed
+ * out for good - a serving loop that sizes every buffer at start-up and forbids allocation on the
+ * request path - and callers that hold only the input and output pointers, with no Workspace to
+ * grow.  The cross-block partials go to a buffer of SB200_STATIC_SCRATCH_BYTES that is built into
+ * the library (a static device array; every GPU that loads the library holds it until the process
+ * exits).  Rules that follow from that:
+ *  - a reduction whose scratch need (sb200_reduce_scratch_bytes) exceeds the built-in buffer is
+ *    refused with SB200_ERR_SCRATCH before anything is launched (sb200_last_cuda_error() says how
+ *    many bytes were needed); use sb200_reduce for those;
+ *  - the FIRST call on each device looks up the buffer's device address (cudaGetSymbolAddress, no
+ *    allocation); make that first call before starting any stream capture on that device;
+ *  - all calls on a device share the one buffer and find the previous call's partials in it.
+ *    Nothing has to start at zero: every slot a call reads was written by that call's own first
+ *    kernel.  But two calls that can run at the same time on one GPU (different streams) would
+ *    overwrite each other's partials: keep calls on a device ordered on one stream;
+ *  - no cudaMalloc/cudaFree and no allocating library routine is called. */
+#define SB200_STATIC_SCRATCH_BYTES (1 << 20)
+int sb200_reduce_static(const float* x, const int* in_shape, int num_axes, const int* axes, int n_axes,
+                        int operation, float* y, void* stream);
+
 /* Two-step form for a tensor sharded over several GPUs on an axis that is being reduced: step 1
  * writes one DOUBLE partial per kept position (sum for Sum/Avg/L1, sum of squares for L2, product
  * for Prod, max/min value for Max/Min) so the caller can combine the shards' partials (sum, product,

@@ -13,6 +13,9 @@ namespace sb200 {
 // Records the text of a failed CUDA call for sb200_last_cuda_error() and returns SB200_ERR_CUDA.
 int cuda_failure(cudaError_t err, const char* where);
 
+// Stores a message for sb200_last_cuda_error() for failures that are not CUDA errors.
+void set_error_text(const char* text);
+
 // Number of kernels this library has launched in the calling process (read by sb200_launch_count()).
 void count_launch(int n = 1);
 

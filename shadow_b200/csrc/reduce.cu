@@ -20,7 +20,9 @@
 // Algorithmic bytes: 4*(|x| + |y|); scratch traffic is splits*outputs*8 B, negligible.
 #include <float.h>
 
+#include <cstdio>
 #include <initializer_list>
+#include <mutex>
 #include <type_traits>
 
 #include "common.cuh"
@@ -615,6 +617,38 @@ int reduce_common(const float* x, const int* in_shape, int num_axes, const int* 
   return dispatch(P, operation, x, y, partial, scratch, emit_partial, static_cast<cudaStream_t>(stream));
 }
 
+// ---- built-in scratch for sb200_reduce_static ------------------------------------------------------
+// One fixed array per GPU that loads this library (it lives in the module's global data until the
+// process exits).  Host code may not use the name below as a pointer: on the host it is only a
+// stand-in for the device symbol.  The device address is asked for once per device, with that
+// device current, through cudaGetSymbolAddress, and that address is what the kernels receive.
+constexpr int64_t kStaticScratchBytes = SB200_STATIC_SCRATCH_BYTES;
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_static_scratch_addr[kMaxDevices] = {nullptr};
+std::mutex g_static_scratch_mutex;
+
+// Device address of the built-in scratch on the CURRENT device, or an error status.
+int static_scratch_address(void** out) {
+  int dev = -1;
+  cudaError_t err = cudaGetDevice(&dev);
+  if (err != cudaSuccess) return cuda_failure(err, "sb200_reduce_static(cudaGetDevice)");
+  if (dev < 0 || dev >= kMaxDevices) {
+    set_error_text("sb200_reduce_static: device ordinal outside 0..63");
+    return SB200_ERR_UNSUPPORTED;
+  }
+  std::lock_guard<std::mutex> lock(g_static_scratch_mutex);
+  if (g_static_scratch_addr[dev] == nullptr) {
+    void* ptr = nullptr;
+    err = cudaGetSymbolAddress(&ptr, g_static_scratch);
+    if (err != cudaSuccess) return cuda_failure(err, "sb200_reduce_static(cudaGetSymbolAddress)");
+    g_static_scratch_addr[dev] = ptr;
+  }
+  *out = g_static_scratch_addr[dev];
+  return SB200_OK;
+}
+
 }  // namespace
 }  // namespace sb200
 
@@ -637,6 +671,28 @@ int64_t sb200_reduce_scratch_bytes(const int* in_shape, int num_axes, const int*
 int sb200_reduce(const float* x, const int* in_shape, int num_axes, const int* axes, int n_axes,
                  int operation, float* y, void* scratch, int64_t scratch_bytes, void* stream) {
   return reduce_common(x, in_shape, num_axes, axes, n_axes, operation, y, nullptr, scratch, scratch_bytes,
+                       false, stream);
+}
+
+int sb200_reduce_static(const float* x, const int* in_shape, int num_axes, const int* axes, int n_axes,
+                        int operation, float* y, void* stream) {
+  const int64_t need = sb200_reduce_scratch_bytes(in_shape, num_axes, axes, n_axes, operation);
+  if (need < 0) return SB200_ERR_BAD_ARGUMENT;
+  if (need > kStaticScratchBytes) {
+    char msg[200];
+    std::snprintf(msg, sizeof(msg),
+                  "sb200_reduce_static: this reduction needs %lld bytes of scratch, the built-in buffer holds %lld; "
+                  "use sb200_reduce with caller scratch", static_cast<long long>(need),
+                  static_cast<long long>(kStaticScratchBytes));
+    set_error_text(msg);
+    return SB200_ERR_SCRATCH;
+  }
+  void* scratch = nullptr;
+  if (need > 0) {
+    int rc = static_scratch_address(&scratch);
+    if (rc != SB200_OK) return rc;
+  }
+  return reduce_common(x, in_shape, num_axes, axes, n_axes, operation, y, nullptr, scratch, kStaticScratchBytes,
                        false, stream);
 }
 

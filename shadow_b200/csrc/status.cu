@@ -17,6 +17,8 @@ int cuda_failure(cudaError_t err, const char* where) {
   return SB200_ERR_CUDA;
 }
 
+void set_error_text(const char* text) { std::snprintf(g_cuda_error, sizeof(g_cuda_error), "%s", text); }
+
 void count_launch(int n) { g_launches.fetch_add(n, std::memory_order_relaxed); }
 
 int sm_count() {
