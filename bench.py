@@ -346,6 +346,7 @@ def run_b200_arm(args):
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ["NCCL_DEBUG"] = "WARN"      # keep stdout to the one JSON line
         dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local_rank))
     assert world == args.gpus or world == 1, "launch with torchrun --nproc-per-node %d" % args.gpus
     torch.cuda.set_device(local_rank)
@@ -364,42 +365,84 @@ def run_b200_arm(args):
     O = torch.empty((n_local,) + O_SHAPE[1:], dtype=torch.float32, device=device)
     torch.cuda.synchronize()
 
+    r_sum = torch.empty(1, dtype=torch.float32, device=device)
+    r_max = torch.empty(1, dtype=torch.float32, device=device)
+    record = torch.empty(2, dtype=torch.float64, device=device)          # this rank's (sum, max) partials
+    gathered = torch.empty(2 * world, dtype=torch.float64, device=device)
+    total = numel(O_SHAPE)
+
     def step(evs=None):
-        if evs is not None:
-            evs[0].record()
+        """One pass of the chain.  With several ranks the two reductions share ONE collective: each
+        rank's double partials (sum, max) are all-gathered and merged locally in rank order."""
+        def mark(i):
+            if evs is not None:
+                evs[i].record()
+        mark(0)
         F.binary(A, B, MUL, out=O)
-        if evs is not None:
-            evs[1].record()
-        s = sharded.reduce(O, RED_SUM, [], global_dim0=A_SHAPE[0], keep_dims=False)
-        if evs is not None:
-            evs[2].record()
-        m = sharded.reduce(O, RED_MAX, [], global_dim0=A_SHAPE[0], keep_dims=False)
-        if evs is not None:
-            evs[3].record()
-        return s, m
+        mark(1)
+        if world == 1:
+            F.reduce(O, RED_SUM, [], out=r_sum)
+            mark(2)
+            F.reduce(O, RED_MAX, [], out=r_max)
+        else:
+            F.reduce_partial(O, RED_SUM, [], out=record[0:1])
+            mark(2)
+            F.reduce_partial(O, RED_MAX, [], out=record[1:2])
+            dist.all_gather_into_tensor(gathered, record)
+            F.reduce_combine(gathered, world, 2, 1, RED_SUM, total, out=r_sum)
+            F.reduce_combine(gathered[1:], world, 2, 1, RED_MAX, total, out=r_max)
+        mark(3)
 
     for _ in range(max(args.warmup, 3)):
-        s, m = step()
+        step()
     torch.cuda.synchronize()
+
+    # ---- the step as a CUDA graph: the launches (and the collective) are captured once and the
+    # timed region replays them, so the host cost per step is one graph launch
+    graph = None
+    if not args.no_graph:
+        graph = torch.cuda.CUDAGraph()
+        launches_before = capi.launch_count()
+        with torch.cuda.graph(graph):
+            step()
+        launches_per_step = capi.launch_count() - launches_before
+        for _ in range(3):
+            graph.replay()
+        torch.cuda.synchronize()
+
+    def run_step():
+        if graph is not None:
+            graph.replay()
+        else:
+            step()
+
     if dist is not None:
         dist.barrier()
     torch.cuda.synchronize()
-    op_events = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(args.steps)]
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches_before = capi.launch_count()
     with ClockSampler(local_rank) as clocks:
         start.record()
         for k in range(args.steps):
-            s, m = step(op_events[k])
+            run_step()
         end.record()
         torch.cuda.synchronize()
-    launches = capi.launch_count() - launches_before
+    launches = (launches_per_step * args.steps) if graph is not None else (capi.launch_count() - launches_before)
     ms_total = start.elapsed_time(end)
     if dist is not None:
         tmax = torch.tensor([ms_total], dtype=torch.float64, device=device)
         dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
         ms_total = float(tmax.item())
         dist.barrier()
+    s, m = r_sum.clone(), r_max.clone()
+
+    # ---- per-operator durations: the same steps launched directly with CUDA events between the
+    # operators (events cannot be read inside a graph replay)
+    n_inst = max(3, min(args.steps, 20))
+    op_events = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(n_inst)]
+    for k in range(n_inst):
+        step(op_events[k])
+    torch.cuda.synchronize()
     ms_step = ms_total / args.steps
     bytes_job = step_bytes(A_SHAPE, B_SHAPE, O_SHAPE)          # whole job, all ranks
     bytes_rank = step_bytes((n_local,) + A_SHAPE[1:], B_SHAPE, (n_local,) + O_SHAPE[1:])
@@ -407,6 +450,7 @@ def run_b200_arm(args):
     op_ms = {
         "binary_broadcast_mul": statistics.mean(e[0].elapsed_time(e[1]) for e in op_events),
         "reduce_sum_all": statistics.mean(e[1].elapsed_time(e[2]) for e in op_events),
+        # with several ranks this span also holds the all-gather and the two merge kernels
         "reduce_max_all": statistics.mean(e[2].elapsed_time(e[3]) for e in op_events),
     }
     peak, peak_kind = measured_peak()
@@ -432,7 +476,9 @@ def run_b200_arm(args):
         "config": {"workload": "C5 chain: broadcast Mul A[8,1,2048,2048]xB[1,16,1,2048] -> [8,16,2048,2048] (2 GiB), "
                                "ReduceSum all axes, ReduceMax all axes; dim 0 split over the ranks",
                    "l2": "inputs larger than L2 (each step streams >= 256 MiB per GPU; no flush interposed)",
-                   "bytes_per_step": sum(bytes_job.values()), "collective": "nccl all_reduce of 1 double per reduction" if world > 1 else "none"},
+                   "bytes_per_step": sum(bytes_job.values()),
+                   "collective": "one nccl all_gather of 16 B per rank per step (sum and max partials together)" if world > 1 else "none",
+                   "launch": "cuda graph replay" if graph is not None else "direct launches"},
         "frac_of_8tbs_per_gpu": round(value / world / NOMINAL_PEAK_GBS, 4),
         "roofline": roofline, "per_step_ops": per_step_ops,
         "e2e": None if args.no_e2e else {"value": round(e2e_value, 3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
@@ -470,6 +516,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--no-sweep", action="store_true", help="skip the per-operator >=256 MB sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-graph", action="store_true", help="launch every step directly instead of replaying a CUDA graph")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end (host buffers) leg")
     ap.add_argument("--batch", type=int, default=A_SHAPE[0],
                     help="dim 0 of A (default 8 = the baseline configuration; smaller only for profiler captures)")

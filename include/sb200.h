@@ -163,6 +163,12 @@ int sb200_reduce_partial(const float* x, const int* in_shape, int num_axes, cons
                          int64_t scratch_bytes, void* stream);
 int sb200_reduce_finalize(const double* partial, float* y, int64_t count, int operation,
                           int64_t total_reduced_count, void* stream);
+/* Finalize from SEVERAL partial records without a reducing collective: part p of output o is
+ * parts[p * part_stride + o] (for instance the all-gathered records of n_parts ranks); the parts
+ * are merged in index order (sum / product / max / min by `operation`) and finished as above.
+ * part_stride > count lets one gathered buffer carry the partials of several reductions. */
+int sb200_reduce_combine(const double* parts, int64_t n_parts, int64_t part_stride, float* y, int64_t count,
+                         int operation, int64_t total_reduced_count, void* stream);
 
 /* Softmax over the middle axis of x viewed as [outer, dim, inner]: max, exp(x - max), sum,
  * divide, all in float.  Replaces Vision::Softmax<kGPU,float>(in, outer, dim, inner, val, out, ctx)

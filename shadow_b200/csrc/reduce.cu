@@ -353,7 +353,7 @@ redG_kernel(const float* __restrict__ x, float* y, double* part, const __grid_co
 template <int OP, int LANES, bool TO_PART>
 __global__ void __launch_bounds__(kThreads)
 red_finish_kernel(const double* __restrict__ in, int64_t splits, int64_t n_out, float* y, double* part,
-                  double count) {
+                  double count, int64_t split_stride) {
   using R = RedOp<OP>;
   using Acc = typename R::Acc;
   __shared__ Acc smem[32];
@@ -362,7 +362,7 @@ red_finish_kernel(const double* __restrict__ in, int64_t splits, int64_t n_out, 
   const int lane = static_cast<int>(gid % LANES);
   if (o >= n_out) return;   // whole warps (LANES == 32) / whole blocks (256) leave together
   Acc acc = R::init();
-  for (int64_t s = lane; s < splits; s += LANES) acc = R::merge(acc, static_cast<Acc>(in[s * n_out + o]));
+  for (int64_t s = lane; s < splits; s += LANES) acc = R::merge(acc, static_cast<Acc>(in[s * split_stride + o]));
   if (LANES == 32) acc = warp_reduce(acc, typename R::Merge());
   if (LANES == 256) acc = block_reduce(acc, typename R::Merge(), R::init(), smem);
   if (lane == 0) emit<OP, TO_PART>(acc, y, part, o, 0, n_out, count);
@@ -554,17 +554,19 @@ void launch_stage1(const Plan& P, const float* x, float* y, double* part, cudaSt
   }
 }
 
+// in[s * split_stride + o] is part s of output o (split_stride == n_out for the kernels' own scratch).
 template <int OP, bool TO_PART>
 void launch_finish(const double* in, int64_t splits, int64_t n_out, float* y, double* part, double count,
-                   cudaStream_t s) {
+                   cudaStream_t s, int64_t split_stride = -1) {
+  if (split_stride < 0) split_stride = n_out;
   if (splits > 256) {
-    red_finish_kernel<OP, 256, TO_PART><<<static_cast<unsigned>(n_out), kThreads, 0, s>>>(in, splits, n_out, y, part, count);
+    red_finish_kernel<OP, 256, TO_PART><<<static_cast<unsigned>(n_out), kThreads, 0, s>>>(in, splits, n_out, y, part, count, split_stride);
   } else if (splits > 8) {
     const int64_t blocks = (n_out * 32 + kThreads - 1) / kThreads;
-    red_finish_kernel<OP, 32, TO_PART><<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(in, splits, n_out, y, part, count);
+    red_finish_kernel<OP, 32, TO_PART><<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(in, splits, n_out, y, part, count, split_stride);
   } else {
     const int64_t blocks = (n_out + kThreads - 1) / kThreads;
-    red_finish_kernel<OP, 1, TO_PART><<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(in, splits, n_out, y, part, count);
+    red_finish_kernel<OP, 1, TO_PART><<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(in, splits, n_out, y, part, count, split_stride);
   }
 }
 
@@ -702,24 +704,30 @@ int sb200_reduce_partial(const float* x, const int* in_shape, int num_axes, cons
                        scratch_bytes, true, stream);
 }
 
-int sb200_reduce_finalize(const double* partial, float* y, int64_t count, int operation,
-                          int64_t total_reduced_count, void* stream) {
-  if (count < 0 || total_reduced_count < 1 || (count > 0 && (partial == nullptr || y == nullptr)))
+int sb200_reduce_combine(const double* parts, int64_t n_parts, int64_t part_stride, float* y, int64_t count,
+                         int operation, int64_t total_reduced_count, void* stream) {
+  if (count < 0 || n_parts < 1 || part_stride < count || total_reduced_count < 1 ||
+      (count > 0 && (parts == nullptr || y == nullptr)))
     return SB200_ERR_BAD_ARGUMENT;
   if (count == 0) return SB200_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const double c = static_cast<double>(total_reduced_count);
   switch (operation) {
-    case SB200_RED_PROD: launch_finish<SB200_RED_PROD, false>(partial, 1, count, y, nullptr, c, s); break;
-    case SB200_RED_SUM: launch_finish<SB200_RED_SUM, false>(partial, 1, count, y, nullptr, c, s); break;
-    case SB200_RED_MAX: launch_finish<SB200_RED_MAX, false>(partial, 1, count, y, nullptr, c, s); break;
-    case SB200_RED_MIN: launch_finish<SB200_RED_MIN, false>(partial, 1, count, y, nullptr, c, s); break;
-    case SB200_RED_AVG: launch_finish<SB200_RED_AVG, false>(partial, 1, count, y, nullptr, c, s); break;
-    case SB200_RED_L1: launch_finish<SB200_RED_L1, false>(partial, 1, count, y, nullptr, c, s); break;
-    case SB200_RED_L2: launch_finish<SB200_RED_L2, false>(partial, 1, count, y, nullptr, c, s); break;
+    case SB200_RED_PROD: launch_finish<SB200_RED_PROD, false>(parts, n_parts, count, y, nullptr, c, s, part_stride); break;
+    case SB200_RED_SUM: launch_finish<SB200_RED_SUM, false>(parts, n_parts, count, y, nullptr, c, s, part_stride); break;
+    case SB200_RED_MAX: launch_finish<SB200_RED_MAX, false>(parts, n_parts, count, y, nullptr, c, s, part_stride); break;
+    case SB200_RED_MIN: launch_finish<SB200_RED_MIN, false>(parts, n_parts, count, y, nullptr, c, s, part_stride); break;
+    case SB200_RED_AVG: launch_finish<SB200_RED_AVG, false>(parts, n_parts, count, y, nullptr, c, s, part_stride); break;
+    case SB200_RED_L1: launch_finish<SB200_RED_L1, false>(parts, n_parts, count, y, nullptr, c, s, part_stride); break;
+    case SB200_RED_L2: launch_finish<SB200_RED_L2, false>(parts, n_parts, count, y, nullptr, c, s, part_stride); break;
     default: return SB200_ERR_BAD_ARGUMENT;
   }
-  return after_launch("sb200_reduce_finalize");
+  return after_launch("sb200_reduce_combine");
+}
+
+int sb200_reduce_finalize(const double* partial, float* y, int64_t count, int operation,
+                          int64_t total_reduced_count, void* stream) {
+  return sb200_reduce_combine(partial, 1, count, y, count, operation, total_reduced_count, stream);
 }
 
 }  // extern "C"

@@ -149,14 +149,24 @@ def reduce(x: torch.Tensor, operation: int = 0, axes: Sequence[int] = (), keep_d
     return y
 
 
-def reduce_partial(x: torch.Tensor, operation: int, axes: Sequence[int]) -> torch.Tensor:
-    """Double partial per kept position (see sb200_reduce_partial); shape = x.shape with reduced dims 1."""
+def reduce_partial(x: torch.Tensor, operation: int, axes: Sequence[int],
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Double partial per kept position (see sb200_reduce_partial); shape = x.shape with reduced dims 1.
+    ``out``: a contiguous float64 CUDA tensor with that many elements to write into."""
     _chk(x, "x")
     axes = list(axes) if len(axes) else list(range(x.dim()))
     out_shape = list(x.shape)
     for ax in axes:
         out_shape[ax] = 1
-    part = torch.empty(out_shape, dtype=torch.float64, device=x.device)
+    if out is None:
+        part = torch.empty(out_shape, dtype=torch.float64, device=x.device)
+    else:
+        n = 1
+        for d in out_shape:
+            n *= d
+        if not (out.is_cuda and out.dtype == torch.float64 and out.is_contiguous() and out.numel() == n):
+            raise ValueError("out must be a contiguous float64 CUDA tensor of %d elements" % n)
+        part = out
     shape_c, axes_c = capi.ints(x.shape), capi.ints(axes)
     nbytes = capi.lib().sb200_reduce_scratch_bytes(shape_c, x.dim(), axes_c, len(axes), operation)
     capi.check(capi.lib().sb200_reduce_partial(x.data_ptr(), shape_c, x.dim(), axes_c, len(axes), operation,
@@ -169,6 +179,16 @@ def reduce_finalize(part: torch.Tensor, operation: int, total_reduced_count: int
     y = torch.empty(part.shape, dtype=torch.float32, device=part.device)
     capi.check(capi.lib().sb200_reduce_finalize(part.data_ptr(), y.data_ptr(), part.numel(), operation,
                                                 total_reduced_count, _stream()), "sb200_reduce_finalize")
+    return y
+
+
+def reduce_combine(parts: torch.Tensor, n_parts: int, part_stride: int, count: int, operation: int,
+                   total_reduced_count: int, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Merge ``n_parts`` double records (``parts[p*part_stride + o]``) and finish to float
+    (see sb200_reduce_combine)."""
+    y = torch.empty(count, dtype=torch.float32, device=parts.device) if out is None else _chk(out, "out")
+    capi.check(capi.lib().sb200_reduce_combine(parts.data_ptr(), n_parts, part_stride, y.data_ptr(), count, operation,
+                                               total_reduced_count, _stream()), "sb200_reduce_combine")
     return y
 
 

@@ -106,3 +106,45 @@ def reduce(x_local: torch.Tensor, operation: int, axes: Sequence[int], global_di
     if not keep_dims:
         y = y.reshape([d for n, d in enumerate(y.shape) if n not in axes])
     return y
+
+
+class ReduceMany:
+    """Several reductions (different operations, same axes) of one dim-0-sharded tensor with ONE
+    collective: every rank writes its double partials into one record, the records are
+    all-gathered, and each rank merges them locally in rank order (deterministic) and finishes.
+    Buffers are allocated once, so a step can be captured in a CUDA graph and replayed."""
+
+    def __init__(self, operations: Sequence[int], local_shape: Sequence[int], axes: Sequence[int], global_dim0: int,
+                 device, group=None):
+        from . import functional as F
+        self.F = F
+        self.ops = list(operations)
+        self.axes = list(axes) if len(axes) else list(range(len(local_shape)))
+        self.group = group
+        self.rank, self.size = world()
+        self.count = 1
+        self.total = 1
+        for n, d in enumerate(local_shape):
+            if n in self.axes:
+                self.total *= global_dim0 if n == 0 else d
+            else:
+                self.count *= d
+        self.crosses = 0 in self.axes and self.size > 1
+        self.record = torch.empty(len(self.ops) * self.count, dtype=torch.float64, device=device)
+        self.gathered = torch.empty(self.size * self.record.numel(), dtype=torch.float64, device=device)
+        self.results = [torch.empty(self.count, dtype=torch.float32, device=device) for _ in self.ops]
+
+    def __call__(self, x_local: torch.Tensor):
+        F = self.F
+        if not self.crosses:
+            for i, op in enumerate(self.ops):
+                F.reduce(x_local, op, self.axes, keep_dims=True, out=self.results[i])
+            return self.results
+        for i, op in enumerate(self.ops):
+            F.reduce_partial(x_local, op, self.axes, out=self.record[i * self.count:(i + 1) * self.count])
+        dist.all_gather_into_tensor(self.gathered, self.record, group=self.group)
+        stride = self.record.numel()
+        for i, op in enumerate(self.ops):
+            F.reduce_combine(self.gathered[i * self.count:], self.size, stride, self.count, op, self.total,
+                             out=self.results[i])
+        return self.results
