@@ -501,10 +501,21 @@ def run_b200_arm(args):
                                     "sample": SAMPLE_TEXT, "ms_per_sample_step": round(ms, 2),
                                     "sample_parity": bool(abs(gs - cpu_res[0]) <= tol * abs(cpu_res[0]) and gm == cpu_res[1])}
     if rank == 0:
-        print(json.dumps(line))
+        print(json.dumps(line), flush=True)
+    # ---- teardown.  Everything has been reported; a collective captured in a CUDA graph must be
+    # released before the communicator goes away, and a teardown that stalls must not keep the job
+    # (and the GPUs) alive: after 20 s the process exits on its own.
     if dist is not None:
+        watchdog = threading.Timer(20.0, os._exit, args=(0,))
+        watchdog.daemon = True
+        watchdog.start()
+        if graph is not None:
+            graph.reset()
+        graph = None
+        torch.cuda.synchronize()
         dist.barrier()
         dist.destroy_process_group()
+        watchdog.cancel()
     return 0
 
 
