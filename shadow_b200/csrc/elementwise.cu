@@ -169,6 +169,7 @@ chan_vec_kernel(const float* x, float* y, int64_t n, int head, const float* __re
   }
   const float4* x4 = reinterpret_cast<const float4*>(x + head);
   float4* y4 = reinterpret_cast<float4*>(y + head);
+  const bool uniform4 = (head == 0) && ((inner & 3) == 0);
   constexpr int64_t kTile = static_cast<int64_t>(kThreads) * kUnroll;
   const int64_t base = static_cast<int64_t>(blockIdx.x) * kTile;
   float4 vx[kUnroll];
@@ -192,6 +193,12 @@ chan_vec_kernel(const float* x, float* y, int64_t n, int head, const float* __re
         const int64_t row = i / inner;
         r = i - row * inner;
         c = row % channels;
+      }
+      if (uniform4) {   // inner % 4 == 0 and no head: the float4 lies inside one channel run
+        const int64_t cc = shared ? 0 : c;
+        const float ps = HAS_P ? __ldg(p + cc) : 0.f, qs = HAS_Q ? __ldg(q + cc) : 0.f;
+        st_stream(y4 + v, make_float4(f(vx[u].x, ps, qs), f(vx[u].y, ps, qs), f(vx[u].z, ps, qs), f(vx[u].w, ps, qs)));
+        continue;
       }
       float xs[4] = {vx[u].x, vx[u].y, vx[u].z, vx[u].w};
       float ys[4];

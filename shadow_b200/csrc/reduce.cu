@@ -34,7 +34,8 @@ namespace {
 constexpr int kMaxDims = 8;
 constexpr int kThreads = 256;
 constexpr int kUnroll = 4;
-constexpr int kChunkTiles = 8;   // tiles (kThreads*kUnroll units) per block in the split kernels
+constexpr int kTargetWaves = 10;  // grids of the split kernels aim at this many waves of resident blocks
+constexpr int kMinTiles = 2;      // ... but never fewer than this many tile iterations per block
 
 // ---- per-operation arithmetic --------------------------------------------------------------------
 template <int OP>
@@ -253,7 +254,7 @@ redB_kernel(const float* __restrict__ x, float* y, double* part, const __grid_co
   using Acc = typename R::Acc;
   constexpr int TY = kThreads / TX;
   constexpr int W = VEC ? 4 : 1;
-  __shared__ Acc smem[TY][TX * W + 1];
+  __shared__ Acc smem[kThreads / 32][TX * W + 1];
   const int tx = threadIdx.x % TX, ty = threadIdx.x / TX;
   const int64_t k0 = blockIdx.x / g.nbx, bx = blockIdx.x - k0 * g.nbx;
   const int64_t s = blockIdx.y;
@@ -294,17 +295,29 @@ redB_kernel(const float* __restrict__ x, float* y, double* part, const __grid_co
       }
     }
   }
+  // rows that share a warp (lanes with equal tx) are merged with shuffles; the per-warp results go
+  // through shared memory and the first TX*W threads merge the warps in index order
+  constexpr int kWarps = kThreads / 32;
+  constexpr int kRowsPerWarp = 32 / TX;   // TX is 8, 16 or 32
 #pragma unroll
-  for (int e = 0; e < W; ++e) smem[ty][tx * W + e] = acc[e];
+  for (int e = 0; e < W; ++e) {
+#pragma unroll
+    for (int o = TX; o < 32; o <<= 1) acc[e] = R::merge(acc[e], __shfl_xor_sync(0xffffffffu, acc[e], o));
+  }
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (lane < TX) {
+#pragma unroll
+    for (int e = 0; e < W; ++e) smem[warp][lane * W + e] = acc[e];
+  }
+  (void)kRowsPerWarp;
   __syncthreads();
-  // TX*W threads finish one column each, walking the TY rows in order
   if (threadIdx.x < TX * W) {
     const int c = threadIdx.x;
     const int64_t colu = bx * TX + c / W;
     if (colu < g.K1u) {
       Acc a = smem[0][c];
-#pragma unroll 4
-      for (int r = 1; r < TY; ++r) a = R::merge(a, smem[r][c]);
+#pragma unroll
+      for (int r = 1; r < kWarps; ++r) a = R::merge(a, smem[r][c]);
       const int64_t out = k0 * g.K1 + colu * W + (c % W);
       emit<OP, TO_PART>(a, y, part, out, s, g.n_out, g.count);
     }
@@ -458,14 +471,13 @@ int make_plan(const int* in_shape, int num_axes, const int* axes, int n_axes, co
       g.div_r1u = FastDiv32(g.R1u);
       g.chunk_units = g.n_units;
     } else {
-      // Many small blocks stream better than few long-running ones (see elementwise.cu): aim at
-      // kChunkTiles tiles per block, but never fewer blocks than fill the machine.
-      int64_t splits = (g.n_units + kThreads * kUnroll * kChunkTiles - 1) / (kThreads * kUnroll * kChunkTiles);
-      if (K * splits < target_blocks) {
-        splits = (target_blocks + K - 1) / K;
-        const int64_t max_by_work = (g.n_units + kThreads * kUnroll * 2 - 1) / (kThreads * kUnroll * 2);
-        if (splits > max_by_work) splits = max_by_work;
-      }
+      // Many small blocks stream better than few long-running ones (see elementwise.cu), and a
+      // grid of only a few waves loses up to a whole block duration in its last, partly filled
+      // wave: aim at >= kTargetWaves waves of resident blocks, at least kMinTiles tiles per block.
+      int64_t splits = (target_blocks * kTargetWaves + K - 1) / K;
+      if (K >= target_blocks * 4) splits = 1;   // already several waves of blocks: no second kernel
+      const int64_t max_by_work = (g.n_units + kThreads * kUnroll * kMinTiles - 1) / (kThreads * kUnroll * kMinTiles);
+      if (splits > max_by_work) splits = max_by_work;
       if (splits > 65535) splits = 65535;
       if (splits < 1) splits = 1;
       int64_t chunk = (g.n_units + splits - 1) / splits;
@@ -493,12 +505,10 @@ int make_plan(const int* in_shape, int num_axes, const int* axes, int n_axes, co
     g.nbx = (g.K1u + best_tx - 1) / best_tx;
     const int ty = kThreads / best_tx;
     const int64_t blocks = g.nbx * K0;
-    int64_t splits = (Rm + ty * kUnroll * kChunkTiles - 1) / (ty * kUnroll * kChunkTiles);
-    if (blocks * splits < target_blocks) {
-      splits = (target_blocks + blocks - 1) / blocks;
-      const int64_t max_by_work = (Rm + ty * kUnroll - 1) / (ty * kUnroll);
-      if (splits > max_by_work) splits = max_by_work;
-    }
+    int64_t splits = (target_blocks * kTargetWaves + blocks - 1) / blocks;
+    if (blocks >= target_blocks * 4) splits = 1;   // already several waves of blocks: no second kernel
+    const int64_t max_by_work = (Rm + ty * kUnroll * kMinTiles - 1) / (ty * kUnroll * kMinTiles);
+    if (splits > max_by_work) splits = max_by_work;
     if (splits > 65535) splits = 65535;
     if (splits < 1) splits = 1;
     int64_t chunk = (Rm + splits - 1) / splits;
