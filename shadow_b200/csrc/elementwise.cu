@@ -23,6 +23,14 @@ namespace {
 constexpr int kThreads = 256;
 constexpr int kUnroll = 4;
 
+// Functors may ask for the guarded tile form through a static member kGuardedTile.
+template <typename F, typename = void>
+struct GuardedTileTrait { static constexpr bool value = false; };
+template <typename F>
+struct GuardedTileTrait<F, decltype(void(F::kGuardedTile))> { static constexpr bool value = F::kGuardedTile; };
+template <typename F>
+__host__ __device__ constexpr bool guarded_tile() { return GuardedTileTrait<F>::value; }
+
 // Calls f with as many operands as the kernel has inputs.
 template <int NIN, typename F>
 __device__ __forceinline__ float apply(const F& f, float a, float b) {
@@ -63,7 +71,7 @@ ew_vec_kernel(const float* a, const float* b, float* y, int64_t n, int head, F f
   const int64_t base = static_cast<int64_t>(blockIdx.x) * kTile;
   float4 va[kUnroll] = {}, vb[kUnroll] = {};
   const int64_t first = base + threadIdx.x;
-  if (base + kTile <= nvec) {
+  if (!guarded_tile<F>() && base + kTile <= nvec) {
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
       if (NIN >= 1) va[u] = ld_stream(a4 + first + u * kThreads);

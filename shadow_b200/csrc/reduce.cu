@@ -37,6 +37,13 @@ constexpr int kUnroll = 4;
 constexpr int kTargetWaves = 10;  // grids of the split kernels aim at this many waves of resident blocks
 constexpr int kMinTiles = 2;      // ... but never fewer than this many tile iterations per block
 
+// Number of reduced elements with its reciprocal (both doubles, computed on the host).
+struct Divisor {
+  double n, inv;
+  Divisor() : n(1.0), inv(1.0) {}
+  explicit Divisor(double v) : n(v), inv(1.0 / v) {}
+};
+
 // ---- per-operation arithmetic --------------------------------------------------------------------
 template <int OP>
 struct RedOp {
@@ -62,8 +69,18 @@ struct RedOp {
     if (OP == SB200_RED_MIN) return (b < a) ? b : a;
     return a + b;
   }
-  __device__ __forceinline__ static float finish(Acc a, double count) {
-    if (OP == SB200_RED_AVG) return static_cast<float>(static_cast<double>(a) / count);
+  __device__ __forceinline__ static float finish(Acc a, Divisor count) {
+    if (OP == SB200_RED_AVG) {
+      // a / n in double, correctly rounded, without the ~50-instruction division: with inv = RN(1/n)
+      // from the host, q = RN(a*inv), r = a - n*q (exact in an fma), q' = RN(q + r*inv) is the
+      // correctly rounded quotient (Markstein's theorem; n is a small integer, never all-ones).
+      const double ad = static_cast<double>(a);
+      double q = ad * count.inv;
+      const double r = fma(-q, count.n, ad);
+      q = fma(r, count.inv, q);
+      // inf / nan sums give nan in r: fall back to the plain product for them
+      return static_cast<float>(r == r ? q : ad * count.inv);
+    }
     if (OP == SB200_RED_L2) return __fsqrt_rn(static_cast<float>(a));
     return static_cast<float>(a);
   }
@@ -75,7 +92,7 @@ struct RedOp {
 // Where a block's result goes: the final float, or a double partial at part[split*n_out + out].
 template <int OP, bool TO_PART>
 __device__ __forceinline__ void emit(typename RedOp<OP>::Acc acc, float* y, double* part, int64_t out,
-                                     int64_t split, int64_t n_out, double count) {
+                                     int64_t split, int64_t n_out, Divisor count) {
   if (TO_PART) part[split * n_out + out] = static_cast<double>(acc);
   else y[out] = RedOp<OP>::finish(acc, count);
 }
@@ -99,7 +116,7 @@ struct GeomA {
   FastDiv32 div_r1u;
   int64_t n_units;      // R0 * R1u
   int64_t chunk_units;  // units per split (block kernel)
-  double count;         // divisor for Avg
+  Divisor count;         // divisor for Avg
 };
 
 template <int OP, bool VEC, bool TO_PART>
@@ -158,7 +175,7 @@ constexpr int kRowsMaxUnitsPerRow = 256;
 template <int OP, bool VEC, bool TO_PART>
 __global__ void __launch_bounds__(RowsTile<OP>::kT)
 redA_rows_kernel(const float* __restrict__ x, float* y, double* part, int64_t K, int r1u,
-                 int rows_per_block, double count) {
+                 int rows_per_block, Divisor count) {
   using R = RedOp<OP>;
   using Acc = typename R::Acc;
   constexpr int T = RowsTile<OP>::kT, UPT = RowsTile<OP>::kUPT;
@@ -219,36 +236,49 @@ redA_block_kernel(const float* __restrict__ x, float* y, double* part, const __g
   const int64_t begin = s * g.chunk_units;
   int64_t end = begin + g.chunk_units;
   if (end > g.n_units) end = g.n_units;
-  typename R::Acc acc = R::init();
+  // One accumulator per unroll slot: the slots' chains are independent, and a full tile takes the
+  // unguarded path so that its kUnroll loads are all issued before the first is consumed.
+  typename R::Acc accs[kUnroll];
+#pragma unroll
+  for (int u = 0; u < kUnroll; ++u) accs[u] = R::init();
   constexpr int64_t kTile = static_cast<int64_t>(kThreads) * kUnroll;
-  for (int64_t j0 = begin; j0 < end; j0 += kTile) {
+  auto address = [&](int64_t j, int64_t* c) {
+    const float* p = base;
+    *c = j;
+    if (g.R0 > 1) {
+      uint32_t r0, cc;
+      g.div_r1u.divmod(static_cast<uint32_t>(j), r0, cc);   // n_units < 2^32 whenever R0 > 1
+      p += static_cast<int64_t>(r0) * g.r0_stride;
+      *c = cc;
+    }
+    return p;
+  };
+  int64_t j0 = begin;
+  for (; j0 + kTile <= end; j0 += kTile) {
     float4 v4[kUnroll];
     float v1[kUnroll];
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      const int64_t j = j0 + u * kThreads + threadIdx.x;
-      if (j < end) {
-        const float* p = base;
-        int64_t c = j;
-        if (g.R0 > 1) {
-          uint32_t r0, cc;
-          g.div_r1u.divmod(static_cast<uint32_t>(j), r0, cc);   // n_units < 2^32 whenever R0 > 1
-          p += static_cast<int64_t>(r0) * g.r0_stride;
-          c = cc;
-        }
-        if (VEC) v4[u] = ld_stream(reinterpret_cast<const float4*>(p) + c);
-        else v1[u] = ld_stream(p + c);
-      }
+      int64_t c;
+      const float* p = address(j0 + u * kThreads + threadIdx.x, &c);
+      if (VEC) v4[u] = ld_stream(reinterpret_cast<const float4*>(p) + c);
+      else v1[u] = ld_stream(p + c);
     }
 #pragma unroll
     for (int u = 0; u < kUnroll; ++u) {
-      const int64_t j = j0 + u * kThreads + threadIdx.x;
-      if (j < end) {
-        if (VEC) acc = step4<OP>(acc, v4[u]);
-        else acc = R::step(acc, v1[u]);
-      }
+      if (VEC) accs[u] = step4<OP>(accs[u], v4[u]);
+      else accs[u] = R::step(accs[u], v1[u]);
     }
   }
+  for (int64_t j = j0 + threadIdx.x; j < end; j += kThreads) {   // ragged last tile
+    int64_t c;
+    const float* p = address(j, &c);
+    if (VEC) accs[0] = step4<OP>(accs[0], ld_stream(reinterpret_cast<const float4*>(p) + c));
+    else accs[0] = R::step(accs[0], ld_stream(p + c));
+  }
+  typename R::Acc acc = accs[0];
+#pragma unroll
+  for (int u = 1; u < kUnroll; ++u) acc = R::merge(acc, accs[u]);
   acc = block_reduce(acc, typename R::Merge(), R::init(), smem);
   if (threadIdx.x == 0) emit<OP, TO_PART>(acc, y, part, k, s, g.K, g.count);
 }
@@ -260,7 +290,7 @@ struct GeomB {
   int64_t nbx;          // blocks along K1
   int64_t r_chunk;      // rows per split
   int64_t n_out;        // K0*K1
-  double count;
+  Divisor count;
 };
 
 // blockIdx.x = k0*nbx + bx, blockIdx.y = split.  TX lanes along K1, TY = kThreads/TX rows along R.
@@ -285,31 +315,34 @@ redB_kernel(const float* __restrict__ x, float* y, double* part, const __grid_co
   for (int e = 0; e < W; ++e) acc[e] = R::init();
   if (active) {
     const float* base = x + k0 * g.R * g.K1 + col * W;
-    for (int64_t r0 = r_begin + ty; r0 < r_end; r0 += static_cast<int64_t>(TY) * kUnroll) {
+    auto take = [&](const float4& q4, float q1) {
+      if (VEC) {
+        acc[0] = R::step(acc[0], q4.x);
+        acc[W > 1 ? 1 : 0] = R::step(acc[W > 1 ? 1 : 0], q4.y);
+        acc[W > 2 ? 2 : 0] = R::step(acc[W > 2 ? 2 : 0], q4.z);
+        acc[W > 3 ? 3 : 0] = R::step(acc[W > 3 ? 3 : 0], q4.w);
+      } else {
+        acc[0] = R::step(acc[0], q1);
+      }
+    };
+    int64_t r0 = r_begin + ty;
+    // full steps: kUnroll rows per thread, loads issued together and unguarded
+    for (; r0 + static_cast<int64_t>(kUnroll - 1) * TY < r_end; r0 += static_cast<int64_t>(TY) * kUnroll) {
       float4 v4[kUnroll];
       float v1[kUnroll];
 #pragma unroll
       for (int u = 0; u < kUnroll; ++u) {
-        const int64_t r = r0 + static_cast<int64_t>(u) * TY;
-        if (r < r_end) {
-          if (VEC) v4[u] = ld_stream(reinterpret_cast<const float4*>(base + r * g.K1));
-          else v1[u] = ld_stream(base + r * g.K1);
-        }
+        const float* p = base + (r0 + static_cast<int64_t>(u) * TY) * g.K1;
+        if (VEC) v4[u] = ld_stream(reinterpret_cast<const float4*>(p));
+        else v1[u] = ld_stream(p);
       }
 #pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        const int64_t r = r0 + static_cast<int64_t>(u) * TY;
-        if (r < r_end) {
-          if (VEC) {
-            acc[0] = R::step(acc[0], v4[u].x);
-            acc[W > 1 ? 1 : 0] = R::step(acc[W > 1 ? 1 : 0], v4[u].y);
-            acc[W > 2 ? 2 : 0] = R::step(acc[W > 2 ? 2 : 0], v4[u].z);
-            acc[W > 3 ? 3 : 0] = R::step(acc[W > 3 ? 3 : 0], v4[u].w);
-          } else {
-            acc[0] = R::step(acc[0], v1[u]);
-          }
-        }
-      }
+      for (int u = 0; u < kUnroll; ++u) take(v4[u], v1[u]);
+    }
+    for (; r0 < r_end; r0 += TY) {   // remaining rows
+      const float* p = base + r0 * g.K1;
+      if (VEC) take(ld_stream(reinterpret_cast<const float4*>(p)), 0.f);
+      else take(make_float4(0.f, 0.f, 0.f, 0.f), ld_stream(p));
     }
   }
   // rows that share a warp (lanes with equal tx) are merged with shuffles; the per-warp results go
@@ -347,7 +380,7 @@ struct GeomG {
   int64_t k_extent[kMaxDims], k_stride[kMaxDims];
   int64_t r_extent[kMaxDims], r_stride[kMaxDims];
   int64_t n_out, n_red;
-  double count;
+  Divisor count;
 };
 
 template <int OP, bool TO_PART>
@@ -383,7 +416,7 @@ redG_kernel(const float* __restrict__ x, float* y, double* part, const __grid_co
 template <int OP, int LANES, bool TO_PART>
 __global__ void __launch_bounds__(kThreads)
 red_finish_kernel(const double* __restrict__ in, int64_t splits, int64_t n_out, float* y, double* part,
-                  double count, int64_t split_stride) {
+                  Divisor count, int64_t split_stride) {
   using R = RedOp<OP>;
   using Acc = typename R::Acc;
   __shared__ Acc smem[32];
@@ -441,7 +474,7 @@ int make_plan(const int* in_shape, int num_axes, const int* axes, int n_axes, co
   if (nd > kMaxDims) return SB200_ERR_UNSUPPORTED;
   P->n_out = n_out, P->n_red = n_red, P->splits = 1, P->scratch_bytes = 0, P->vec = false;
   P->a_warp = false, P->a_rows = false, P->rows_per_block = 1, P->tx = 32;
-  const double count = static_cast<double>(n_red);
+  const Divisor count(static_cast<double>(n_red));
   const int64_t target_blocks = static_cast<int64_t>(sm_count()) * 8;
 
   // pattern -> family
@@ -585,7 +618,7 @@ void launch_stage1(const Plan& P, const float* x, float* y, double* part, cudaSt
 
 // in[s * split_stride + o] is part s of output o (split_stride == n_out for the kernels' own scratch).
 template <int OP, bool TO_PART>
-void launch_finish(const double* in, int64_t splits, int64_t n_out, float* y, double* part, double count,
+void launch_finish(const double* in, int64_t splits, int64_t n_out, float* y, double* part, Divisor count,
                    cudaStream_t s, int64_t split_stride = -1) {
   if (split_stride < 0) split_stride = n_out;
   if (splits > 256) {
@@ -603,7 +636,7 @@ void launch_finish(const double* in, int64_t splits, int64_t n_out, float* y, do
 template <int OP>
 int run(const Plan& P, const float* x, float* y, double* partial, void* scratch, bool emit_partial,
         cudaStream_t s) {
-  const double count = static_cast<double>(P.n_red);
+  const Divisor count(static_cast<double>(P.n_red));
   if (P.splits > 1) {
     double* tmp = static_cast<double*>(scratch);
     launch_stage1<OP, true>(P, x, nullptr, tmp, s);
@@ -740,7 +773,7 @@ int sb200_reduce_combine(const double* parts, int64_t n_parts, int64_t part_stri
     return SB200_ERR_BAD_ARGUMENT;
   if (count == 0) return SB200_OK;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const double c = static_cast<double>(total_reduced_count);
+  const Divisor c(static_cast<double>(total_reduced_count));
   switch (operation) {
     case SB200_RED_PROD: launch_finish<SB200_RED_PROD, false>(parts, n_parts, count, y, nullptr, c, s, part_stride); break;
     case SB200_RED_SUM: launch_finish<SB200_RED_SUM, false>(parts, n_parts, count, y, nullptr, c, s, part_stride); break;

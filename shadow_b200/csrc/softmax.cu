@@ -225,6 +225,74 @@ softmax_cols_kernel(const float* x, float* y, int64_t dim, int64_t inner, int64_
   }
 }
 
+// Strided softmax, plane layout.  A block owns W consecutive positions of `inner` for one outer
+// index; its threads are laid out as G row groups x W columns, so consecutive threads read
+// consecutive addresses (a [G, W] patch of the contiguous [dim, inner] plane) whatever W is - no
+// lane is wasted on a ragged `inner` such as 49.  Pass 1 keeps an online (max, sum) pair per
+// thread (rescaling the sum when a new maximum appears), the G groups are merged through shared
+// memory, pass 2 re-reads the patch - it was just read by this block, so it comes from L2 - and
+// writes exp(x - max) / sum.  HBM traffic stays one read and one write per element.
+template <int U>
+__global__ void __launch_bounds__(256)
+softmax_plane_kernel(const float* x, float* y, int64_t dim, int64_t inner, int W, int G, int64_t ntile) {
+  __shared__ float sm_m[256], sm_l[256];
+  const int t = threadIdx.x;
+  const int g = t / W, sidx = t - g * W;
+  const int64_t n = blockIdx.x / ntile, tile = blockIdx.x - n * ntile;
+  const int64_t col = tile * W + sidx;
+  const bool live = (g < G) && (col < inner);
+  const float* xp = x + n * dim * inner + col;
+  float* yp = y + n * dim * inner + col;
+  float m = -FLT_MAX, l = 0.f;
+  // Pass 1 only feeds the sum, whose tolerance is far looser than one exponential's: it uses the
+  // hardware 2^x unit directly (exp(d) = 2^(d*log2 e), about 2 ulp plus the rounding of the
+  // product), a fraction of the cost of expf.  Pass 2 produces the outputs with the accurate expf.
+  auto fast_exp = [](float d) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d * 1.4426950408889634f));
+    return r;
+  };
+  auto absorb = [&](float v) {
+    if (v > m) {             // new maximum: bring the running sum to the new reference point
+      l = l * fast_exp(m - v);
+      m = v;
+    }
+    l = l + fast_exp(v - m);
+  };
+  const int64_t step = static_cast<int64_t>(G) * inner;
+  if (live) {
+    const float* p = xp + static_cast<int64_t>(g) * inner;
+    int64_t c = g;
+    for (; c + static_cast<int64_t>(U - 1) * G < dim; c += static_cast<int64_t>(U) * G, p += U * step) {
+      float v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) v[u] = p[u * step];   // default caching: stays in L2 for pass 2
+#pragma unroll
+      for (int u = 0; u < U; ++u) absorb(v[u]);
+    }
+    for (; c < dim; c += G, p += step) absorb(*p);
+  }
+  if (t < 256) { sm_m[t] = m; sm_l[t] = l; }
+  __syncthreads();
+  float M = -FLT_MAX, L = 0.f;
+  if (live) {
+    for (int k = 0; k < G; ++k) M = std_max(sm_m[k * W + sidx], M);
+    for (int k = 0; k < G; ++k) L = __fadd_rn(L, __fmul_rn(sm_l[k * W + sidx], expf(__fsub_rn(sm_m[k * W + sidx], M))));
+    const float inv = __frcp_rn(L);
+    const float* p = xp + static_cast<int64_t>(g) * inner;
+    float* q = yp + static_cast<int64_t>(g) * inner;
+    int64_t c = g;
+    for (; c + static_cast<int64_t>(U - 1) * G < dim; c += static_cast<int64_t>(U) * G, p += U * step, q += U * step) {
+      float v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) v[u] = ld_stream(p + u * step);
+#pragma unroll
+      for (int u = 0; u < U; ++u) st_stream(q + u * step, __fmul_rn(expf(__fsub_rn(v[u], M)), inv));
+    }
+    for (; c < dim; c += G, p += step, q += step) st_stream(q, __fmul_rn(expf(__fsub_rn(ld_stream(p), M)), inv));
+  }
+}
+
 template <int TPR, int NV, bool VEC>
 void launch_rows(const float* x, float* y, int64_t rows, int units, cudaStream_t s) {
   constexpr int BLOCK = TPR < 256 ? 256 : TPR;
@@ -272,29 +340,11 @@ extern "C" int sb200_softmax(const float* x, float* y, int64_t outer, int64_t di
     }
     return after_launch("sb200_softmax");
   }
-  const int64_t nbx = (inner + kTX - 1) / kTX;
-  if (outer * nbx >= (1ll << 31)) return SB200_ERR_UNSUPPORTED;
-  const unsigned grid = static_cast<unsigned>(outer * nbx);
-  if (dim <= 1024) {
-    const int nc = dim <= 128 ? 4 : dim <= 256 ? 8 : dim <= 512 ? 16 : 32;
-    const int ty = static_cast<int>((dim + nc - 1) / nc);
-    const unsigned block = 32u * ty;
-    if (nc == 4) softmax_cols_kernel<4><<<grid, block, 0, s>>>(x, y, dim, inner, nbx);
-    else if (nc == 8) softmax_cols_kernel<8><<<grid, block, 0, s>>>(x, y, dim, inner, nbx);
-    else if (nc == 16) softmax_cols_kernel<16><<<grid, block, 0, s>>>(x, y, dim, inner, nbx);
-    else softmax_cols_kernel<32><<<grid, block, 0, s>>>(x, y, dim, inner, nbx);
-    return after_launch("sb200_softmax");
-  }
-  const size_t tile_bytes = static_cast<size_t>(dim) * kTX * sizeof(float);
-  if (tile_bytes <= 200 * 1024) {
-    if (tile_bytes > 40 * 1024) {
-      cudaError_t err = cudaFuncSetAttribute(softmax_strided_kernel<true>,
-                                             cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
-      if (err != cudaSuccess) return cuda_failure(err, "sb200_softmax(cudaFuncSetAttribute)");
-    }
-    softmax_strided_kernel<true><<<grid, kTX * kTY, tile_bytes, s>>>(x, y, dim, inner, nbx);
-  } else {
-    softmax_strided_kernel<false><<<grid, kTX * kTY, 0, s>>>(x, y, dim, inner, nbx);
-  }
+  const int W = static_cast<int>(inner < 256 ? inner : 256);
+  const int G = 256 / W;
+  const int64_t ntile = (inner + W - 1) / W;
+  if (outer * ntile >= (1ll << 31)) return SB200_ERR_UNSUPPORTED;
+  const unsigned grid = static_cast<unsigned>(outer * ntile);
+  softmax_plane_kernel<4><<<grid, 256, 0, s>>>(x, y, dim, inner, W, G, ntile);
   return after_launch("sb200_softmax");
 }

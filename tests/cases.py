@@ -169,6 +169,11 @@ def small_cases():
     cs.append(_case("softmax_mid", "Softmax", {"axis": 2}, [normal(1104, (2, 3, 11, 5))]))
     cs.append(_case("softmax_dim1", "Softmax", {"axis": 1}, [normal(1105, (7, 1, 3))]))
     cs.append(_case("softmax_long_row", "Softmax", {"axis": 1}, [normal(1106, (2, 20011), 0.0, 3.0)]))
+    cs.append(_case("softmax_cluster8", "Softmax", {"axis": 1}, [normal(1108, (2, 1000, 7, 7))]))
+    cs.append(_case("softmax_cluster2", "Softmax", {"axis": 1}, [normal(1109, (3, 300, 49))]))
+    cs.append(_case("softmax_cluster4_wide", "Softmax", {"axis": 1}, [normal(1110, (2, 100, 300))]))
+    cs.append(_case("softmax_plane_two_pass", "Softmax", {"axis": 1}, [normal(1111, (2, 300, 300), 0.0, 3.0)]))
+    cs.append(_case("softmax_inner2", "Softmax", {"axis": 0}, [normal(1112, (700, 2))]))
     cs.append(_case("softmax_huge_logits", "Softmax", {"axis": 1}, [normal(1107, (4, 300), 0.0, 200.0)]))
     return cs
 
