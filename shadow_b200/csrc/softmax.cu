@@ -345,6 +345,6 @@ extern "C" int sb200_softmax(const float* x, float* y, int64_t outer, int64_t di
   const int64_t ntile = (inner + W - 1) / W;
   if (outer * ntile >= (1ll << 31)) return SB200_ERR_UNSUPPORTED;
   const unsigned grid = static_cast<unsigned>(outer * ntile);
-  softmax_plane_kernel<4><<<grid, 256, 0, s>>>(x, y, dim, inner, W, G, ntile);
+  softmax_plane_kernel<32><<<grid, 256, 0, s>>>(x, y, dim, inner, W, G, ntile);
   return after_launch("sb200_softmax");
 }
