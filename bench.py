@@ -81,47 +81,49 @@ def ncu_traffic():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons of one GPU through NVML while the timed region runs."""
+    """SM clock and throttle reasons of one GPU while work runs, read by an `nvidia-smi -lms`
+    child process.  (Polling NVML from a thread of this process takes driver locks that the
+    launches of a short timed region then wait for: at 8 GPUs it doubled the step time.)"""
 
-    def __init__(self, index: int, period_s: float = 0.005):
-        self.index, self.period = index, period_s
-        self.samples, self.reasons, self.max_mhz = [], set(), None
-        self._stop = threading.Event()
-        self._thread = None
-        try:
-            import pynvml
-            pynvml.nvmlInit()
-            self.nv = pynvml
-            self.handle = pynvml.nvmlDeviceGetHandleByIndex(index)
-            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
-        except Exception:
-            self.nv = None
+    QUERY = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown," \
+            "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
-    def _loop(self):
-        nv = self.nv
-        names = {"sw_power_cap": 0x4, "hw_slowdown": 0x8, "sw_thermal_slowdown": 0x20,
-                 "hw_thermal_slowdown": 0x40, "hw_power_brake_slowdown": 0x80}
-        while not self._stop.is_set():
-            try:
-                self.samples.append(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
-                mask = nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle)
-                for k, bit in names.items():
-                    if mask & bit:
-                        self.reasons.add(k)
-            except Exception:
-                pass
-            time.sleep(self.period)
+    def __init__(self, index: int, period_ms: int = 20):
+        self.index, self.period_ms = index, period_ms
+        self.proc, self.samples, self.reasons, self.max_mhz = None, [], set(), None
 
     def __enter__(self):
-        if self.nv is not None:
-            self._thread = threading.Thread(target=self._loop, daemon=True)
-            self._thread.start()
+        import subprocess
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), "--query-gpu=" + self.QUERY, "--format=csv,noheader,nounits",
+                 "-lms", str(self.period_ms)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except Exception:
+            self.proc = None
         return self
 
     def __exit__(self, *exc):
-        self._stop.set()
-        if self._thread is not None:
-            self._thread.join()
+        if self.proc is None:
+            return
+        self.proc.terminate()
+        try:
+            out, _ = self.proc.communicate(timeout=5)
+        except Exception:
+            self.proc.kill()
+            out = ""
+        for line in out.splitlines():
+            parts = [p.strip() for p in line.split(",")]
+            if len(parts) < 6:
+                continue
+            try:
+                self.samples.append(int(float(parts[0])))
+                self.max_mhz = int(float(parts[1]))
+            except ValueError:
+                continue
+            for name, val in zip(self.NAMES, parts[2:6]):
+                if val.lower().startswith("active"):
+                    self.reasons.add(name)
 
     def summary(self):
         if not self.samples:
@@ -432,12 +434,22 @@ def run_b200_arm(args):
     torch.cuda.synchronize()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches_before = capi.launch_count()
+    t_wall = time.perf_counter()
     with ClockSampler(local_rank) as clocks:
         start.record()
         for k in range(args.steps):
             run_step()
         end.record()
         torch.cuda.synchronize()
+        t_wall = time.perf_counter() - t_wall
+        # a timed region shorter than a few sampling periods yields no clock samples: keep the very
+        # same loop running (untimed) under the sampler until about 0.25 s of load have been seen
+        extra = 0
+        if t_wall < 0.25 and not args.no_clocks:
+            extra = int(min(20000, (0.25 - t_wall) / max(t_wall / args.steps, 1e-6)))
+            for k in range(extra):
+                run_step()
+            torch.cuda.synchronize()
     launches = (launches_per_step * args.steps) if graph is not None else (capi.launch_count() - launches_before)
     ms_total = start.elapsed_time(end)
     if dist is not None:
@@ -494,7 +506,8 @@ def run_b200_arm(args):
         "roofline": roofline, "per_step_ops": per_step_ops,
         "e2e": None if args.no_e2e else {"value": round(e2e_value, 3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                 "ms_per_step": round(e2e_s * 1e3, 3), "api": "Shadow::Network::Forward + GetBlobDataByName (C++ host library)"},
-        "gpu_launches": launches, "clocks": clocks.summary(),
+        "gpu_launches": launches,
+        "clocks": dict(clocks.summary(), window="timed region + %d identical untimed steps" % extra),
         "results": {"sum": result_sum, "max": result_max, "e2e_sum": e2e_res[0], "e2e_max": e2e_res[1]},
     }
     if rank == 0 and world == 1:
@@ -539,6 +552,7 @@ def main():
     ap.add_argument("--no-sweep", action="store_true", help="skip the per-operator >=256 MB sweep")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-graph", action="store_true", help="launch every step directly instead of replaying a CUDA graph")
+    ap.add_argument("--no-clocks", action="store_true", help="do not prolong the loop for clock sampling")
     ap.add_argument("--no-e2e", action="store_true", help="skip the end-to-end (host buffers) leg")
     ap.add_argument("--batch", type=int, default=A_SHAPE[0],
                     help="dim 0 of A (default 8 = the baseline configuration; smaller only for profiler captures)")
