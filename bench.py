@@ -360,6 +360,11 @@ def run_b200_arm(args):
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         os.environ["NCCL_DEBUG"] = "WARN"      # keep stdout to the one JSON line
+        # a rank that stalls in a collective must not keep 8 GPUs busy: the whole run takes well
+        # under a minute, so after 3 minutes the process ends itself
+        safety = threading.Timer(180.0, os._exit, args=(3,))
+        safety.daemon = True
+        safety.start()
         dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local_rank))
     assert world == args.gpus or world == 1, "launch with torchrun --nproc-per-node %d" % args.gpus
     torch.cuda.set_device(local_rank)
@@ -434,28 +439,29 @@ def run_b200_arm(args):
     torch.cuda.synchronize()
     start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches_before = capi.launch_count()
-    t_wall = time.perf_counter()
     with ClockSampler(local_rank) as clocks:
         start.record()
         for k in range(args.steps):
             run_step()
         end.record()
         torch.cuda.synchronize()
-        t_wall = time.perf_counter() - t_wall
-        # a timed region shorter than a few sampling periods yields no clock samples: keep the very
-        # same loop running (untimed) under the sampler until about 0.25 s of load have been seen
+        ms_total = start.elapsed_time(end)
+        if dist is not None:
+            tmax = torch.tensor([ms_total], dtype=torch.float64, device=device)
+            dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+            ms_total = float(tmax.item())
+        # A timed region shorter than a few sampling periods yields no clock samples: keep the very
+        # same loop running (untimed) under the sampler until about 0.25 s of load have been seen.
+        # The count derives from the max-over-ranks time, so every rank runs the same number of
+        # steps (each step holds a collective).
         extra = 0
-        if t_wall < 0.25 and not args.no_clocks:
-            extra = int(min(20000, (0.25 - t_wall) / max(t_wall / args.steps, 1e-6)))
+        if ms_total < 250.0 and not args.no_clocks:
+            extra = int(min(5000, (250.0 - ms_total) / max(ms_total / args.steps, 1e-3)))
             for k in range(extra):
                 run_step()
             torch.cuda.synchronize()
     launches = (launches_per_step * args.steps) if graph is not None else (capi.launch_count() - launches_before)
-    ms_total = start.elapsed_time(end)
     if dist is not None:
-        tmax = torch.tensor([ms_total], dtype=torch.float64, device=device)
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-        ms_total = float(tmax.item())
         dist.barrier()
     s, m = r_sum.clone(), r_max.clone()
 
