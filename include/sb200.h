@@ -170,6 +170,22 @@ int sb200_reduce_finalize(const double* partial, float* y, int64_t count, int op
 int sb200_reduce_combine(const double* parts, int64_t n_parts, int64_t part_stride, float* y, int64_t count,
                          int operation, int64_t total_reduced_count, void* stream);
 
+/* Eltwise: y = fold of n_inputs same-size tensors, operation 0 Prod, 1 Sum, 2 Max, 3 Min, folded left
+ * to right; Sum computes ((0 + coeff[0]*x0) + coeff[1]*x1) + ... with separately rounded multiply
+ * and add (coeff NULL = all ones; coeff is only allowed for Sum).  `inputs` is a HOST array of
+ * n_inputs DEVICE pointers, `coeff` a HOST array.  One launch per 8 inputs (the reference makes one
+ * pass over the output per input).  Replaces EltwiseKernelDefault<kGPU>::Run
+ * (shadow/operators/kernels/eltwise.hpp:19-71) with its Blas::Mul/Max/Min/Set/BlasSaxpy calls. */
+int sb200_eltwise(const float* const* inputs, int n_inputs, const float* coeff, float* y, int64_t n,
+                  int operation, void* stream);
+
+/* Axpy: out[r*inner + i] = y[...] + alpha[r] * x[...] for r < outer (alpha has one value per
+ * (n, c) pair; inner = H*W); multiply and add rounded separately.  Replaces
+ * Vision::Axpy<kGPU,float>(alpha, x, y, outer_num, inner_num, out, ctx)
+ * (shadow/operators/kernels/axpy.hpp:10-13, axpy.cu). */
+int sb200_axpy(const float* alpha, const float* x, const float* y, float* out, int64_t outer, int64_t inner,
+               void* stream);
+
 /* Softmax over the middle axis of x viewed as [outer, dim, inner]: max, exp(x - max), sum,
  * divide, all in float.  Replaces Vision::Softmax<kGPU,float>(in, outer, dim, inner, val, out, ctx)
  * (shadow/operators/kernels/softmax.hpp:10-12, softmax.cu:9-70); the reference's `val` scratch of

@@ -65,6 +65,8 @@ def port():
         L.orc_reduce.argtypes = [_FP, _IP, C.c_int, _IP, C.c_int, C.c_int, _FP]
         L.orc_softmax.argtypes = [_FP, i64, i64, i64, _FP, _FP]
         L.orc_fill.argtypes = [i64, C.c_float, _FP]
+        L.orc_eltwise.argtypes = [C.POINTER(_FP), C.c_int, _FP, i64, C.c_int, _FP]
+        L.orc_axpy.argtypes = [_FP, _FP, _FP, i64, i64, _FP]
         _lib = L
     return _lib
 
@@ -190,6 +192,32 @@ def softmax(x, axis: int = 1) -> np.ndarray:
     y = np.empty_like(x)
     _ok(port().orc_softmax(_fp(x), outer, dim, inner, _fp(val), _fp(y)), "softmax")
     return y
+
+
+def eltwise(inputs, operation: int, coeff=None) -> np.ndarray:
+    """EltwiseOp (shadow/operators/eltwise_op.cpp:7-56): >= 2 same-shape inputs; Prod 0, Sum 1 (optional
+    one coefficient per input), Max 2, Min 3."""
+    xs = [_f32(x) for x in inputs]
+    if len(xs) < 2 or any(x.shape != xs[0].shape for x in xs):
+        raise ValueError("eltwise needs >= 2 inputs of one shape")
+    if coeff is not None and len(coeff) and (operation != 1 or len(coeff) != len(xs)):
+        raise ValueError("coefficients only for Sum, one per input")
+    ptrs = (_FP * len(xs))(*[_fp(x) for x in xs])
+    cf = _f32(coeff) if coeff is not None and len(coeff) else None
+    y = np.empty_like(xs[0])
+    _ok(port().orc_eltwise(ptrs, len(xs), _fp(cf) if cf is not None else None, xs[0].size, operation, _fp(y)), "eltwise")
+    return y
+
+
+def axpy(alpha, x, y) -> np.ndarray:
+    """AxpyOp (shadow/operators/axpy_op.cpp:16-51): alpha [N,C] or [N,C,1,1], x and y [N,C,...]."""
+    alpha, x, y = _f32(alpha), _f32(x), _f32(y)
+    if x.shape != y.shape or alpha.shape[0] != x.shape[0] or alpha.shape[1] != x.shape[1]:
+        raise ValueError("axpy shapes")
+    inner = int(np.prod(x.shape[2:], dtype=np.int64))
+    out = np.empty_like(x)
+    _ok(port().orc_axpy(_fp(alpha), _fp(x), _fp(y), alpha.size, inner, _fp(out)), "axpy")
+    return out
 
 
 def fill(n: int, val: float) -> np.ndarray:

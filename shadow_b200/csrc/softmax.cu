@@ -6,10 +6,14 @@
 //       per thread, so rows up to 32768 floats): one 128-bit read, warp-shuffle / shared-memory
 //       max and sum, one 128-bit write.  Longer rows use a block-per-row kernel that re-reads the
 //       row (from L2) for the second and third step.
-//   inner > 1 (strided): lanes run along `inner` (contiguous), the warps of the block walk `dim`.
-//       dim <= 1024: each thread keeps its share of a column (up to 32 values) in registers, one
-//       read and one write; longer columns stage the [dim, 32] tile in shared memory when it
-//       fits (up to 50 K floats), else re-read it.
+//   inner > 1 (strided): the threads of a block tile the contiguous [dim, inner] plane as G row
+//       groups x W columns (W = min(inner, 256)), so reads are contiguous for any `inner`; pass 1
+//       keeps an online (max, sum) per thread, pass 2 re-reads the patch and writes.  The second
+//       read hits L2 only when the patches in flight fit there; for [N,1000,7,7] they do not, and
+//       the kernel moves 12 instead of 8 bytes per element (0.48 of 8 TB/s measured).  Holding a
+//       196 KB patch on chip needs either all of one SM's shared memory (one block per SM, no
+//       overlap) or a cluster's registers; a cluster/DSMEM variant was built and measured 4x
+//       slower than this kernel, so it is not kept.
 // Arithmetic: float max, expf(x - max), float sum (tree order instead of the reference's
 // left-to-right order), then one correctly rounded reciprocal per row and a multiply per element
 // instead of the reference's per-element division (an IEEE float division costs ~60 issue slots on
@@ -120,108 +124,6 @@ softmax_long_rows_kernel(const float* x, float* y, int64_t rows, int64_t dim) {
     const float inv = __frcp_rn(sum);
     for (int64_t i = threadIdx.x; i < dim; i += 256) yr[i] = __fmul_rn(expf(__fsub_rn(xr[i], m)), inv);
     __syncthreads();
-  }
-}
-
-// Strided: blockIdx.x = n * nbx + bx; block = 32 lanes along inner x TY rows along dim.
-constexpr int kTX = 32, kTY = 8;
-
-template <bool STAGE>
-__global__ void __launch_bounds__(kTX * kTY)
-softmax_strided_kernel(const float* x, float* y, int64_t dim, int64_t inner, int64_t nbx) {
-  extern __shared__ float tile[];   // [dim][32] when STAGE
-  __shared__ float red[kTY][kTX];
-  const int tx = threadIdx.x % kTX, ty = threadIdx.x / kTX;
-  const int64_t n = blockIdx.x / nbx, bx = blockIdx.x - n * nbx;
-  const int64_t s = bx * kTX + tx;
-  const bool live = s < inner;
-  const float* xp = x + n * dim * inner + s;
-  float* yp = y + n * dim * inner + s;
-  float m = -FLT_MAX;
-  if (live) {
-    for (int64_t c = ty; c < dim; c += kTY) {
-      float v = ld_stream(xp + c * inner);
-      if (STAGE) tile[c * kTX + tx] = v;
-      m = std_max(v, m);
-    }
-  }
-  red[ty][tx] = m;
-  __syncthreads();
-  m = red[0][tx];
-#pragma unroll
-  for (int r = 1; r < kTY; ++r) m = std_max(red[r][tx], m);
-  __syncthreads();
-  float sum = 0.f;
-  if (live) {
-    for (int64_t c = ty; c < dim; c += kTY) {
-      float v = STAGE ? tile[c * kTX + tx] : xp[c * inner];
-      float e = expf(__fsub_rn(v, m));
-      if (STAGE) tile[c * kTX + tx] = e;
-      sum = __fadd_rn(sum, e);
-    }
-  }
-  red[ty][tx] = sum;
-  __syncthreads();
-  sum = red[0][tx];
-#pragma unroll
-  for (int r = 1; r < kTY; ++r) sum = __fadd_rn(sum, red[r][tx]);
-  const float inv = __frcp_rn(sum);
-  if (live) {
-    for (int64_t c = ty; c < dim; c += kTY) {
-      float e = STAGE ? tile[c * kTX + tx] : expf(__fsub_rn(xp[c * inner], m));
-      st_stream(yp + c * inner, __fmul_rn(e, inv));
-    }
-  }
-}
-
-// Strided, columns in registers: block = 32 lanes along inner x TY warps along dim (TY <= 32);
-// thread (tx, ty) keeps elements c = ty, ty+TY, ... of column tx in NC registers, so the tensor is
-// read once with NC independent loads in flight per thread.  Needs dim <= TY*NC <= 1024.
-template <int NC>
-__global__ void __launch_bounds__(1024)
-softmax_cols_kernel(const float* x, float* y, int64_t dim, int64_t inner, int64_t nbx) {
-  __shared__ float red[32][33];
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5, TY = blockDim.x >> 5;
-  const int64_t n = blockIdx.x / nbx, bx = blockIdx.x - n * nbx;
-  const int64_t s = bx * 32 + tx;
-  const bool live = s < inner;
-  const float* xp = x + n * dim * inner + s;
-  float* yp = y + n * dim * inner + s;
-  float v[NC];
-  float m = -FLT_MAX;
-#pragma unroll
-  for (int i = 0; i < NC; ++i) {
-    const int64_t c = ty + i * TY;
-    if (live && c < dim) v[i] = ld_stream(xp + c * inner);
-  }
-#pragma unroll
-  for (int i = 0; i < NC; ++i) {
-    const int64_t c = ty + i * TY;
-    if (live && c < dim) m = std_max(v[i], m);
-  }
-  red[ty][tx] = m;
-  __syncthreads();
-  m = red[0][tx];
-  for (int r = 1; r < TY; ++r) m = std_max(red[r][tx], m);
-  __syncthreads();
-  float sum = 0.f;
-#pragma unroll
-  for (int i = 0; i < NC; ++i) {
-    const int64_t c = ty + i * TY;
-    if (live && c < dim) {
-      v[i] = expf(__fsub_rn(v[i], m));
-      sum = __fadd_rn(sum, v[i]);
-    }
-  }
-  red[ty][tx] = sum;
-  __syncthreads();
-  sum = red[0][tx];
-  for (int r = 1; r < TY; ++r) sum = __fadd_rn(sum, red[r][tx]);
-  const float inv = __frcp_rn(sum);
-#pragma unroll
-  for (int i = 0; i < NC; ++i) {
-    const int64_t c = ty + i * TY;
-    if (live && c < dim) st_stream(yp + c * inner, __fmul_rn(v[i], inv));
   }
 }
 

@@ -207,3 +207,34 @@ def softmax(x: torch.Tensor, axis: int = 1, out: Optional[torch.Tensor] = None) 
     capi.check(capi.lib().sb200_softmax(x.data_ptr(), y.data_ptr(), outer, x.shape[axis], inner, _stream()),
                "sb200_softmax")
     return y
+
+
+def eltwise(inputs: Sequence[torch.Tensor], operation: int, coeff: Sequence[float] = (),
+            out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Eltwise operator (shadow/operators/eltwise_op.cpp:7-56): >= 2 inputs of one shape."""
+    import ctypes as C
+    xs = [_chk(x, "input") for x in inputs]
+    if len(xs) < 2 or any(tuple(x.shape) != tuple(xs[0].shape) for x in xs):
+        raise ValueError("eltwise needs >= 2 inputs of one shape")
+    if len(coeff) and (operation != 1 or len(coeff) != len(xs)):
+        raise ValueError("coefficients only for Sum, one per input")
+    y = torch.empty_like(xs[0]) if out is None else _chk(out, "out")
+    ptrs = (C.c_void_p * len(xs))(*[x.data_ptr() for x in xs])
+    cf = (C.c_float * len(coeff))(*[float(c) for c in coeff]) if len(coeff) else None
+    capi.check(capi.lib().sb200_eltwise(ptrs, len(xs), cf, y.data_ptr(), y.numel(), operation, _stream()),
+               "sb200_eltwise")
+    return y
+
+
+def axpy(alpha: torch.Tensor, x: torch.Tensor, y: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Axpy operator (shadow/operators/axpy_op.cpp:16-51): out = alpha[n,c] * x + y."""
+    _chk(alpha, "alpha"), _chk(x, "x"), _chk(y, "y")
+    if tuple(x.shape) != tuple(y.shape) or alpha.shape[0] != x.shape[0] or alpha.shape[1] != x.shape[1]:
+        raise ValueError("axpy shapes")
+    inner = 1
+    for d in x.shape[2:]:
+        inner *= d
+    o = torch.empty_like(x) if out is None else _chk(out, "out")
+    capi.check(capi.lib().sb200_axpy(alpha.data_ptr(), x.data_ptr(), y.data_ptr(), o.data_ptr(), alpha.numel(), inner,
+                                     _stream()), "sb200_axpy")
+    return o

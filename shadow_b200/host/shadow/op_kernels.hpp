@@ -59,6 +59,19 @@ class ReduceKernel : public Kernel {
   virtual void Run(const BlobPtr& input, BlobPtr& output, Workspace* ws, int operation, const VecInt& axes) = 0;
 };
 
+// shadow/operators/kernels/eltwise.hpp:11-17 (codes Prod 0, Sum 1, Max 2, Min 3)
+class EltwiseKernel : public Kernel {
+ public:
+  virtual void Run(const std::vector<BlobPtr>& inputs, BlobPtr& output, Workspace* ws, int operation,
+                   const VecFloat& coeff) = 0;
+};
+
+// shadow/operators/kernels/axpy.hpp:20-27
+class AxpyKernel : public Kernel {
+ public:
+  virtual void Run(const BlobPtr& alpha, const BlobPtr& x, const BlobPtr& y, BlobPtr& output, Workspace* ws) = 0;
+};
+
 class SoftmaxKernel : public Kernel {
  public:
   virtual void Run(const BlobPtr& input, BlobPtr& output, Workspace* ws, int axis) = 0;

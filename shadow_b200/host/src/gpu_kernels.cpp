@@ -1,4 +1,4 @@
-// The six GPU kernel classes, registered as "<Op>GPU(Default)".  Each Run translates blobs into
+// The GPU kernel classes (six tensor operators + Eltwise and Axpy), registered as "<Op>GPU(Default)".  Each Run translates blobs into
 // the raw pointers / sizes of the sb200 C ABI and enqueues on the workspace's stream.  A non-zero
 // status becomes a LOG(FATAL) (print + std::runtime_error), the reference's error convention.
 // There is no other implementation behind these classes: without libsb200 this file does not link.
@@ -154,8 +154,37 @@ class SoftmaxKernelB200 : public SoftmaxKernel {
   std::string kernel_type() const override { return "Default"; }
 };
 
+class EltwiseKernelB200 : public EltwiseKernel {
+ public:
+  void Run(const std::vector<BlobPtr>& inputs, BlobPtr& output, Workspace* ws, int operation,
+           const VecFloat& coeff) override {
+    std::vector<const float*> ptrs;
+    for (const auto& in : inputs) ptrs.push_back(in->data<float>());
+    // the front-end always passes one coefficient per input (1 by default); only Sum uses them
+    const float* cf = (operation == 1 && coeff.size() == inputs.size()) ? coeff.data() : nullptr;
+    expect_ok(sb200_eltwise(ptrs.data(), static_cast<int>(ptrs.size()), cf, output->mutable_data<float>(),
+                            static_cast<int64_t>(inputs[0]->count64()), operation, stream_of(ws)),
+              "sb200_eltwise");
+  }
+  DeviceType device_type() const override { return DeviceType::kGPU; }
+  std::string kernel_type() const override { return "Default"; }
+};
+
+class AxpyKernelB200 : public AxpyKernel {
+ public:
+  void Run(const BlobPtr& alpha, const BlobPtr& x, const BlobPtr& y, BlobPtr& output, Workspace* ws) override {
+    expect_ok(sb200_axpy(alpha->data<float>(), x->data<float>(), y->data<float>(), output->mutable_data<float>(),
+                         static_cast<int64_t>(alpha->count64()), x->count(2), stream_of(ws)),
+              "sb200_axpy");
+  }
+  DeviceType device_type() const override { return DeviceType::kGPU; }
+  std::string kernel_type() const override { return "Default"; }
+};
+
 }  // namespace
 
+REGISTER_OP_KERNEL_DEFAULT(EltwiseGPU, EltwiseKernelB200);
+REGISTER_OP_KERNEL_DEFAULT(AxpyGPU, AxpyKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(BinaryGPU, BinaryKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(UnaryGPU, UnaryKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(ActivateGPU, ActivateKernelB200);

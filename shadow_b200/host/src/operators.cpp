@@ -238,8 +238,62 @@ class SoftmaxOp : public Operator {
   std::shared_ptr<SoftmaxKernel> kernel_;
 };
 
+// Eltwise (shadow/operators/eltwise_op.cpp:7-56): `operation` 0..3 required (Prod, Sum, Max, Min);
+// `coeff` (optional, Sum only) holds one coefficient per input; all inputs share one shape.
+class EltwiseOp : public Operator {
+ public:
+  EltwiseOp(const shadow::OpParam& op_param, Workspace* ws) : Operator(op_param, ws) {
+    operation_ = get_single_argument<int>("operation", -1);
+    CHECK_GE(operation_, 0);
+    CHECK_LE(operation_, 3);
+    coeff_ = get_repeated_argument<float>("coeff");
+    kernel_ = kernel_for<EltwiseKernel>(op_param, ws_);
+  }
+  void Run(const std::vector<BlobPtr>& inputs, std::vector<BlobPtr>& outputs) override {
+    CHECK_GE(inputs.size(), 2u);
+    for (size_t n = 1; n < inputs.size(); ++n) CHECK(inputs[n]->shape() == inputs[0]->shape());
+    outputs[0]->reshape(inputs[0]->shape());
+    CHECK(coeff_.empty() || coeff_.size() == inputs.size()) << "Eltwise op takes one coefficient per input blob.";
+    CHECK(!(operation_ != 1 && !coeff_.empty())) << "Eltwise op only takes coefficients for summation.";
+    VecFloat coeff(inputs.size(), 1.f);
+    for (size_t n = 0; n < coeff_.size(); ++n) coeff[n] = coeff_[n];
+    kernel_->Run(inputs, outputs[0], ws_, operation_, coeff);
+  }
+
+ private:
+  int operation_;
+  VecFloat coeff_;
+  std::shared_ptr<EltwiseKernel> kernel_;
+};
+
+// Axpy (shadow/operators/axpy_op.cpp:16-51): F = a * X + Y with a of shape [N, C] (or [N, C, 1, 1]).
+class AxpyOp : public Operator {
+ public:
+  AxpyOp(const shadow::OpParam& op_param, Workspace* ws) : Operator(op_param, ws) {
+    kernel_ = kernel_for<AxpyKernel>(op_param, ws_);
+  }
+  void Run(const std::vector<BlobPtr>& inputs, std::vector<BlobPtr>& outputs) override {
+    CHECK_EQ(inputs.size(), 3u) << "This op must have three inputs: alpha, x and y";
+    const auto &alpha = inputs[0], &x = inputs[1], &y = inputs[2];
+    CHECK_EQ(alpha->shape(0), x->shape(0));
+    CHECK_EQ(alpha->shape(1), x->shape(1));
+    if (alpha->num_axes() == 4) {
+      CHECK_EQ(alpha->shape(2), 1);
+      CHECK_EQ(alpha->shape(3), 1);
+    }
+    CHECK(x->shape() == y->shape());
+    outputs[0]->reshape(x->shape());
+    kernel_->Run(alpha, x, y, outputs[0], ws_);
+  }
+
+ private:
+  std::shared_ptr<AxpyKernel> kernel_;
+};
+
 }  // namespace
 
+REGISTER_OPERATOR(Eltwise, EltwiseOp);
+REGISTER_OPERATOR(Axpy, AxpyOp);
 REGISTER_OPERATOR(Input, InputOp);
 REGISTER_OPERATOR(Binary, BinaryOp);
 REGISTER_OPERATOR(Unary, UnaryOp);

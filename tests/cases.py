@@ -161,6 +161,22 @@ def small_cases():
     cs.append(_case("reduce_krk_vec", "Reduce", {"operation": 5, "axes": [1], "keep_dims": True}, [normal(1011, (6, 300, 40))]))
     cs.append(_case("reduce_deep", "Reduce", {"operation": 1, "axes": [1, 3], "keep_dims": False}, [normal(1012, (3, 4, 5, 6, 7))]))
     cs.append(_case("reduce_one_elem", "Reduce", {"operation": 6, "axes": [], "keep_dims": True}, [np.array([[-3.0]], np.float32)]))
+    # ---- Eltwise / Axpy ---------------------------------------------------------------------
+    e3 = [normal(1200 + k, (3, 5, 7, 9)) for k in range(3)]
+    for code, nm in enumerate(("Prod", "Sum", "Max", "Min")):
+        cs.append(_case("eltwise_%s_3" % nm, "Eltwise", {"operation": code}, e3))
+        cs.append(_case("eltwise_%s_2" % nm, "Eltwise", {"operation": code}, e3[:2]))
+    cs.append(_case("eltwise_Sum_coeff", "Eltwise", {"operation": 1, "coeff": [0.5, -1.25, 2.0]}, e3))
+    e11 = [normal(1210 + k, (2, 1031)) for k in range(11)]       # more than 8 inputs: chained launches, ragged size
+    cs.append(_case("eltwise_Sum_11", "Eltwise", {"operation": 1, "coeff": [float(np.float32(0.1 * (k + 1))) for k in range(11)]}, e11))
+    cs.append(_case("eltwise_Max_11", "Eltwise", {"operation": 2}, e11))
+    cs.append(_case("eltwise_Prod_9", "Eltwise", {"operation": 0}, [uniform(1230 + k, (4, 64), 0.8, 1.2) for k in range(9)]))
+    sp_a, sp_b = special_pairs()
+    cs.append(_case("eltwise_Max_special", "Eltwise", {"operation": 2}, [sp_a, sp_b, sp_b]))
+    cs.append(_case("eltwise_Sum_special", "Eltwise", {"operation": 1}, [sp_a, sp_b]))
+    cs.append(_case("axpy_4d", "Axpy", {}, [normal(1240, (3, 6)), normal(1241, (3, 6, 5, 8)), normal(1242, (3, 6, 5, 8))]))
+    cs.append(_case("axpy_alpha4d", "Axpy", {}, [normal(1243, (2, 5, 1, 1)), normal(1244, (2, 5, 7, 7)), normal(1245, (2, 5, 7, 7))]))
+    cs.append(_case("axpy_inner3", "Axpy", {}, [normal(1246, (4, 9)), normal(1247, (4, 9, 3)), normal(1248, (4, 9, 3))]))
     # ---- Softmax ----------------------------------------------------------------------------
     cs.append(_case("softmax_rows", "Softmax", {"axis": 1}, [normal(1100, (37, 129), 0.0, 3.0)]))
     cs.append(_case("softmax_rows_neg_axis", "Softmax", {"axis": -1}, [normal(1101, (5, 3, 64), 0.0, 3.0)]))
@@ -209,6 +225,10 @@ def run_port(case) -> np.ndarray:
         return orc.reduce(x[0], a.get("operation", 0), a.get("axes", []), a.get("keep_dims", True))
     if op == "Softmax":
         return orc.softmax(x[0], a.get("axis", 1))
+    if op == "Eltwise":
+        return orc.eltwise(x, a["operation"], a.get("coeff", []))
+    if op == "Axpy":
+        return orc.axpy(x[0], x[1], x[2])
     raise KeyError(op)
 
 
@@ -238,6 +258,8 @@ def tolerance_class(case) -> str:
         return "exact"
     if op == "Reduce":
         return "exact" if a.get("operation", 0) in (2, 3) else "rel"
+    if op in ("Eltwise", "Axpy"):
+        return "exact"
     return "rel"
 
 
@@ -274,6 +296,10 @@ def run_cuda(case, device="cuda:0"):
         y = F.reduce(x[0], a.get("operation", 0), a.get("axes", []), a.get("keep_dims", True))
     elif op == "Softmax":
         y = F.softmax(x[0], a.get("axis", 1))
+    elif op == "Eltwise":
+        y = F.eltwise(x, a["operation"], a.get("coeff", []))
+    elif op == "Axpy":
+        y = F.axpy(x[0], x[1], x[2])
     else:
         raise KeyError(op)
     torch.cuda.synchronize()
