@@ -1,0 +1,133 @@
+"""Edge conditions of the kernel entry points: in-place calls, sub-buffers that are not 16-byte
+aligned (head/tail peeling and the scalar fallbacks), ragged sizes, guard bands around outputs."""
+import numpy as np
+import pytest
+
+import cases
+from oracle import oracle as orc
+
+pytestmark = pytest.mark.gpu
+
+GUARD = 64   # floats of sentinel before and after every output
+
+
+def _torch():
+    import torch
+    return torch
+
+
+def _view(arr, offset, pad=GUARD):
+    """Device copy of `arr` placed `offset` floats after a 256-byte aligned address, with sentinel
+    guard bands; returns (view, whole_buffer)."""
+    torch = _torch()
+    n = arr.size
+    buf = torch.full((pad + offset + n + pad + 8,), 12345.0, dtype=torch.float32, device="cuda")
+    v = buf[pad + offset:pad + offset + n]
+    v.copy_(torch.from_numpy(np.ascontiguousarray(arr).ravel()))
+    return v.view(arr.shape), buf
+
+
+def _guards_intact(buf, offset, n, pad=GUARD):
+    b = buf.cpu().numpy()
+    return bool(np.all(b[:pad + offset] == 12345.0) and np.all(b[pad + offset + n:] == 12345.0))
+
+
+@pytest.mark.parametrize("off_in,off_out", [(0, 0), (1, 1), (3, 3), (2, 2), (1, 2), (0, 3), (3, 0)])
+@pytest.mark.parametrize("n", [1, 5, 1023, 4100])
+def test_unaligned_elementwise(off_in, off_out, n):
+    from shadow_b200 import functional as F
+    torch = _torch()
+    x = cases.uniform(n + off_in, (n,), -3, 3)
+    b = cases.uniform(n + 99, (n,), -3, 3)
+    dx, _ = _view(x, off_in)
+    db, _ = _view(b, off_in)
+    for name, fn, want in (
+        ("neg", lambda o: F.unary(dx, 13, out=o), orc.unary(x, 13)),
+        ("exp", lambda o: F.unary(dx, 4, out=o), orc.unary(x, 4)),
+        ("relu", lambda o: F.activate(dx, 1, 0.1, out=o), orc.activate(x, 1)),
+        ("add", lambda o: F.binary(dx, db, 0, out=o), orc.binary(x, b, 0)),
+        ("mul_scalar", lambda o: F.binary_scalar(dx, 0.7, 2, out=o), orc.binary_scalar(x, 0.7, 2)),
+        ("eltwise_max", lambda o: F.eltwise([dx, db], 2, out=o), orc.eltwise([x, b], 2)),
+    ):
+        out, buf = _view(np.zeros(n, np.float32), off_out)
+        fn(out)
+        torch.cuda.synchronize()
+        got = out.cpu().numpy()
+        tol = 1 if name == "exp" else 0
+        assert int(orc.ulp_distance(got, want).max()) <= tol, name
+        assert _guards_intact(buf, off_out, n), name
+    fill, buf = _view(np.zeros(n, np.float32), off_out)
+    F.fill(fill, 2.5)
+    torch.cuda.synchronize()
+    assert bool((fill == 2.5).all().item()) and _guards_intact(buf, off_out, n)
+
+
+@pytest.mark.parametrize("offset", [0, 1, 2, 3])
+def test_unaligned_channel_broadcast_reduce_softmax(offset):
+    from shadow_b200 import functional as F
+    torch = _torch()
+    x = cases.normal(50 + offset, (3, 6, 5, 7))
+    dx, _ = _view(x, offset)
+    g, bt = cases.normal(60, (6,)), cases.normal(61, (6,))
+    dg, dbt = torch.from_numpy(g).cuda(), torch.from_numpy(bt).cuda()
+    out, buf = _view(np.zeros_like(x), offset)
+    F.scale(dx, 1, dg, dbt, out=out)
+    assert orc.bit_equal(out.cpu().numpy(), orc.scale(x, 1, g, bt)) and _guards_intact(buf, offset, x.size)
+    out, buf = _view(np.zeros_like(x), (offset + 1) % 4)            # input and output misaligned differently
+    F.scale(dx, 1, dg, dbt, out=out)
+    assert orc.bit_equal(out.cpu().numpy(), orc.scale(x, 1, g, bt)) and _guards_intact(buf, (offset + 1) % 4, x.size)
+    out, buf = _view(np.zeros_like(x), offset)
+    F.activate(dx, 0, 0.1, dg, out=out)                             # PReLU
+    assert orc.bit_equal(out.cpu().numpy(), orc.activate(x, 0, 0.1, g))
+    b = cases.normal(62, (1, 6, 1, 7))
+    db, _ = _view(b, offset)
+    out, buf = _view(np.zeros_like(x), offset)
+    F.binary(dx, db, 1, out=out)                                    # broadcast Sub
+    assert orc.bit_equal(out.cpu().numpy(), orc.binary(x, b, 1)) and _guards_intact(buf, offset, x.size)
+    for axes in ([2, 3], [1], [0, 2, 3], []):
+        for op in (1, 2):
+            want = orc.reduce(x, op, axes, True)
+            out, buf = _view(np.zeros_like(want), offset)
+            F.reduce(dx, op, axes, True, out=out)
+            torch.cuda.synchronize()
+            case = {"name": "r", "op": "Reduce", "args": {"operation": op, "axes": axes}, "inputs": [x]}
+            cases.assert_parity(case, out.cpu().numpy().reshape(want.shape), want)
+            assert _guards_intact(buf, offset, want.size)
+    for axis in (1, 3):
+        want = orc.softmax(x, axis)
+        out, buf = _view(np.zeros_like(x), offset)
+        F.softmax(dx, axis, out=out)
+        torch.cuda.synchronize()
+        case = {"name": "s", "op": "Softmax", "args": {"axis": axis}, "inputs": [x]}
+        cases.assert_parity(case, out.cpu().numpy(), want)
+        assert _guards_intact(buf, offset, x.size)
+    alpha = cases.normal(63, (3, 6))
+    y = cases.normal(64, x.shape)
+    dy, _ = _view(y, offset)
+    out, buf = _view(np.zeros_like(x), offset)
+    F.axpy(torch.from_numpy(alpha).cuda(), dx, dy, out=out)
+    assert orc.bit_equal(out.cpu().numpy(), orc.axpy(alpha, x, y)) and _guards_intact(buf, offset, x.size)
+
+
+def test_in_place_calls():
+    from shadow_b200 import functional as F
+    torch = _torch()
+    x = cases.normal(70, (4, 8, 9, 11), 0, 2)
+    b = cases.normal(71, x.shape)
+    bc = cases.normal(72, (1, 8, 1, 1))
+    g, bt = cases.normal(73, (8,)), cases.normal(74, (8,))
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()   # noqa: E731
+    t = dev(x); F.unary(t, 13, out=t); assert orc.bit_equal(t.cpu().numpy(), orc.unary(x, 13))
+    t = dev(x); F.activate(t, 2, 0.1, out=t); assert orc.bit_equal(t.cpu().numpy(), orc.activate(x, 2, np.float32(0.1)))
+    t = dev(x); F.activate(t, 5, 0.1, out=t); assert int(orc.ulp_distance(t.cpu().numpy(), orc.activate(x, 5)).max()) <= 2
+    t = dev(x); F.binary_scalar(t, 1.5, 0, out=t); assert orc.bit_equal(t.cpu().numpy(), orc.binary_scalar(x, 1.5, 0))
+    t = dev(x); F.binary(t, dev(b), 2, out=t); assert orc.bit_equal(t.cpu().numpy(), orc.binary(x, b, 2))
+    t = dev(b); F.binary(dev(x), t, 1, out=t); assert orc.bit_equal(t.cpu().numpy(), orc.binary(x, b, 1))   # out aliases the 2nd input
+    t = dev(x); F.binary(t, dev(bc), 0, out=t); assert orc.bit_equal(t.cpu().numpy(), orc.binary(x, bc, 0))  # broadcast, full input in place
+    t = dev(x); F.scale(t, 1, dev(g), dev(bt), out=t); assert orc.bit_equal(t.cpu().numpy(), orc.scale(x, 1, g, bt))
+    t = dev(x); F.activate(t, 0, 0.1, dev(g), out=t); assert orc.bit_equal(t.cpu().numpy(), orc.activate(x, 0, 0.1, g))
+    t = dev(x); F.eltwise([t, dev(b)], 0, out=t); assert orc.bit_equal(t.cpu().numpy(), orc.eltwise([x, b], 0))
+    t = dev(x); F.softmax(t, 1, out=t)
+    cases.assert_parity({"name": "s", "op": "Softmax", "args": {"axis": 1}, "inputs": [x]}, t.cpu().numpy(), orc.softmax(x, 1))
+    t = dev(x); F.softmax(t, 3, out=t)
+    cases.assert_parity({"name": "s", "op": "Softmax", "args": {"axis": 3}, "inputs": [x]}, t.cpu().numpy(), orc.softmax(x, 3))
