@@ -272,6 +272,10 @@ def per_op_sweep(torch, F, device, peak):
     for name, code in (("Add", 0), ("Mul", 2), ("Max", 5)):
         bench("binary_broadcast_%s[512,64,56,56]+[1,64,1,1]" % name, lambda: F.binary(a, b, code, out=y), 8 * n + 256)
     bench("binary_same_Add[512,64,56,56]", lambda: F.binary(a, c, 0, out=y), 12 * n)
+    bench("eltwise_Sum_3_inputs[512,64,56,56]", lambda: F.eltwise([a, c, a], 1, [0.5, 0.25, 2.0], out=y), 16 * n)
+    bench("eltwise_Max_2_inputs[512,64,56,56]", lambda: F.eltwise([a, c], 2, out=y), 12 * n)
+    alpha = torch.randn(512, 64, device=device)
+    bench("axpy[512,64,56,56]", lambda: F.axpy(alpha, a, c, out=y), 12 * n + 4 * 512 * 64)
     del a, c, y
     c2 = (512, 256, 28, 28)
     x, y = torch.empty(c2, device=device).normal_(0, 2), torch.empty(c2, device=device)

@@ -114,6 +114,13 @@ int sb200_binary_broadcast(const float* a, const int* a_shape, const float* b, c
 int sb200_scale_bias(const float* x, float* y, int64_t n, const float* scale, const float* bias,
                      int64_t scale_num, int64_t inner_num, void* stream);
 
+/* Inference batch normalisation: y[i] = (x[i] - mean[c]*scale_factor) / sqrt(|variance[c]*scale_factor| + eps)
+ * with c = (i / inner_num) % channels, each step one IEEE float operation as on the reference CPU.
+ * Replaces Vision::BatchNorm<kGPU,float>(in, count, mean, variance, channel, inner_num, scale_factor,
+ * eps, out, ctx) (shadow/operators/kernels/batch_norm.hpp:10-15, batch_norm.cu). */
+int sb200_batch_norm(const float* x, float* y, int64_t n, const float* mean, const float* variance,
+                     int64_t channels, int64_t inner_num, float scale_factor, float eps, void* stream);
+
 /* Reduce x (HOST shape in_shape[num_axes]) over the HOST list `axes` (non-negative, distinct,
  * n_axes >= 1) with SB200_RED_*; y receives one float per kept position, row-major over the
  * kept axes.  Prod/Sum/Avg/L1/L2 accumulate in double, Max/Min in float starting from

@@ -67,6 +67,7 @@ def port():
         L.orc_fill.argtypes = [i64, C.c_float, _FP]
         L.orc_eltwise.argtypes = [C.POINTER(_FP), C.c_int, _FP, i64, C.c_int, _FP]
         L.orc_axpy.argtypes = [_FP, _FP, _FP, i64, i64, _FP]
+        L.orc_batch_norm.argtypes = [_FP, i64, _FP, _FP, i64, i64, C.c_float, C.c_float, _FP]
         _lib = L
     return _lib
 
@@ -218,6 +219,23 @@ def axpy(alpha, x, y) -> np.ndarray:
     out = np.empty_like(x)
     _ok(port().orc_axpy(_fp(alpha), _fp(x), _fp(y), alpha.size, inner, _fp(out)), "axpy")
     return out
+
+
+def batch_norm(x, mean, variance, scale=None, eps: float = 1e-5) -> np.ndarray:
+    """BatchNormOp, inference (shadow/operators/batch_norm_op.cpp:9-43): optional 4th input `scale`
+    (one element) gives scale_factor = scale == 0 ? 0 : 1/scale."""
+    x, mean, variance = _f32(x), _f32(mean), _f32(variance)
+    if mean.size != x.shape[1] or variance.size != x.shape[1]:
+        raise ValueError("mean/variance must have one value per channel")
+    sf = np.float32(1)
+    if scale is not None:
+        sc = np.float32(_f32(scale).ravel()[0])
+        sf = np.float32(0) if sc == 0 else np.float32(1) / sc
+    inner = int(np.prod(x.shape[2:], dtype=np.int64))
+    y = np.empty_like(x)
+    _ok(port().orc_batch_norm(_fp(x), x.size, _fp(mean), _fp(variance), x.shape[1], inner, sf, np.float32(eps), _fp(y)),
+        "batch_norm")
+    return y
 
 
 def fill(n: int, val: float) -> np.ndarray:

@@ -365,6 +365,14 @@ int sb200_binary(const float* a, const float* b, float* y, int64_t n, int operat
   }
 }
 
+int sb200_batch_norm(const float* x, float* y, int64_t n, const float* mean, const float* variance,
+                     int64_t channels, int64_t inner_num, float scale_factor, float eps, void* stream) {
+  if (n < 0 || channels < 1 || inner_num < 1 || mean == nullptr || variance == nullptr) return SB200_ERR_BAD_ARGUMENT;
+  if (n > 0 && (x == nullptr || y == nullptr)) return SB200_ERR_BAD_ARGUMENT;
+  return launch_chan<true, true>(x, y, n, mean, variance, inner_num, channels, 0, BatchNormFn{scale_factor, eps},
+                                 static_cast<cudaStream_t>(stream), "sb200_batch_norm");
+}
+
 int sb200_scale_bias(const float* x, float* y, int64_t n, const float* scale, const float* bias,
                      int64_t scale_num, int64_t inner_num, void* stream) {
   if (n < 0 || scale_num < 1 || inner_num < 1 || (scale == nullptr && bias == nullptr))

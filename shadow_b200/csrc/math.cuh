@@ -175,6 +175,14 @@ struct ScaleFn {
 struct BiasFn {
   __device__ __forceinline__ float operator()(float x, float, float b) const { return __fadd_rn(x, b); }
 };
+struct BatchNormFn {   // (x - mean*sf) / sqrt(|var*sf| + eps), every step one IEEE float operation
+  float sf, eps;
+  __device__ __forceinline__ float operator()(float x, float mean, float var) const {
+    const float m = __fmul_rn(mean, sf);
+    const float d = __fsqrt_rn(__fadd_rn(fabsf(__fmul_rn(var, sf)), eps));
+    return __fdiv_rn(__fsub_rn(x, m), d);
+  }
+};
 struct PReluFn {       // x > 0 ? x : x * slope[c]
   __device__ __forceinline__ float operator()(float x, float s, float) const {
     return x > 0.f ? x : __fmul_rn(x, s);

@@ -238,3 +238,19 @@ def axpy(alpha: torch.Tensor, x: torch.Tensor, y: torch.Tensor, out: Optional[to
     capi.check(capi.lib().sb200_axpy(alpha.data_ptr(), x.data_ptr(), y.data_ptr(), o.data_ptr(), alpha.numel(), inner,
                                      _stream()), "sb200_axpy")
     return o
+
+
+def batch_norm(x: torch.Tensor, mean: torch.Tensor, variance: torch.Tensor, scale_factor: float = 1.0,
+               eps: float = 1e-5, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Inference BatchNorm (shadow/operators/batch_norm_op.cpp:9-43); `scale_factor` is what the
+    operator front-end derives from its optional 4th input."""
+    _chk(x, "x"), _chk(mean, "mean"), _chk(variance, "variance")
+    if mean.numel() != x.shape[1] or variance.numel() != x.shape[1]:
+        raise ValueError("mean/variance must have one value per channel")
+    inner = 1
+    for d in x.shape[2:]:
+        inner *= d
+    y = torch.empty_like(x) if out is None else _chk(out, "out")
+    capi.check(capi.lib().sb200_batch_norm(x.data_ptr(), y.data_ptr(), x.numel(), mean.data_ptr(), variance.data_ptr(),
+                                           x.shape[1], inner, scale_factor, eps, _stream()), "sb200_batch_norm")
+    return y

@@ -72,6 +72,13 @@ class AxpyKernel : public Kernel {
   virtual void Run(const BlobPtr& alpha, const BlobPtr& x, const BlobPtr& y, BlobPtr& output, Workspace* ws) = 0;
 };
 
+// shadow/operators/kernels/batch_norm.hpp:20-28
+class BatchNormKernel : public Kernel {
+ public:
+  virtual void Run(const BlobPtr& input, const BlobPtr& mean, const BlobPtr& variance, BlobPtr& output, Workspace* ws,
+                   float scale_factor, float eps) = 0;
+};
+
 class SoftmaxKernel : public Kernel {
  public:
   virtual void Run(const BlobPtr& input, BlobPtr& output, Workspace* ws, int axis) = 0;

@@ -181,8 +181,25 @@ class AxpyKernelB200 : public AxpyKernel {
   std::string kernel_type() const override { return "Default"; }
 };
 
+class BatchNormKernelB200 : public BatchNormKernel {
+ public:
+  void Run(const BlobPtr& input, const BlobPtr& mean, const BlobPtr& variance, BlobPtr& output, Workspace* ws,
+           float scale_factor, float eps) override {
+    const int channel = input->shape(1);
+    CHECK_EQ(channel, mean->count());
+    CHECK_EQ(channel, variance->count());
+    expect_ok(sb200_batch_norm(input->data<float>(), output->mutable_data<float>(),
+                               static_cast<int64_t>(input->count64()), mean->data<float>(), variance->data<float>(),
+                               channel, input->count(2), scale_factor, eps, stream_of(ws)),
+              "sb200_batch_norm");
+  }
+  DeviceType device_type() const override { return DeviceType::kGPU; }
+  std::string kernel_type() const override { return "Default"; }
+};
+
 }  // namespace
 
+REGISTER_OP_KERNEL_DEFAULT(BatchNormGPU, BatchNormKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(EltwiseGPU, EltwiseKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(AxpyGPU, AxpyKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(BinaryGPU, BinaryKernelB200);

@@ -290,8 +290,38 @@ class AxpyOp : public Operator {
   std::shared_ptr<AxpyKernel> kernel_;
 };
 
+// BatchNorm, inference only (shadow/operators/batch_norm_op.cpp:9-43): `use_global_stats` must be
+// true, `eps` default 1e-5; inputs x, mean, variance and optionally a one-element scale blob whose
+// reciprocal (0 if the scale is 0) multiplies mean and variance.  The scale is read back from the
+// device on every Run, as in the reference.
+class BatchNormOp : public Operator {
+ public:
+  BatchNormOp(const shadow::OpParam& op_param, Workspace* ws) : Operator(op_param, ws) {
+    CHECK(get_single_argument<bool>("use_global_stats", true));
+    eps_ = get_single_argument<float>("eps", 1e-5f);
+    kernel_ = kernel_for<BatchNormKernel>(op_param, ws_);
+  }
+  void Run(const std::vector<BlobPtr>& inputs, std::vector<BlobPtr>& outputs) override {
+    CHECK_GE(inputs.size(), 3u);
+    outputs[0]->reshape(inputs[0]->shape());
+    float scale_factor = 1;
+    if (inputs.size() == 4) {
+      float scale = 1;
+      CHECK_EQ(inputs[3]->count(), 1);
+      inputs[3]->get_data<float>(&scale, 1);
+      scale_factor = scale == 0 ? 0 : 1 / scale;
+    }
+    kernel_->Run(inputs[0], inputs[1], inputs[2], outputs[0], ws_, scale_factor, eps_);
+  }
+
+ private:
+  float eps_;
+  std::shared_ptr<BatchNormKernel> kernel_;
+};
+
 }  // namespace
 
+REGISTER_OPERATOR(BatchNorm, BatchNormOp);
 REGISTER_OPERATOR(Eltwise, EltwiseOp);
 REGISTER_OPERATOR(Axpy, AxpyOp);
 REGISTER_OPERATOR(Input, InputOp);

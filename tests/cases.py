@@ -177,6 +177,13 @@ def small_cases():
     cs.append(_case("axpy_4d", "Axpy", {}, [normal(1240, (3, 6)), normal(1241, (3, 6, 5, 8)), normal(1242, (3, 6, 5, 8))]))
     cs.append(_case("axpy_alpha4d", "Axpy", {}, [normal(1243, (2, 5, 1, 1)), normal(1244, (2, 5, 7, 7)), normal(1245, (2, 5, 7, 7))]))
     cs.append(_case("axpy_inner3", "Axpy", {}, [normal(1246, (4, 9)), normal(1247, (4, 9, 3)), normal(1248, (4, 9, 3))]))
+    xb = normal(1250, (3, 6, 5, 7))
+    mean, var = normal(1251, (6,)), uniform(1252, (6,), 0.1, 2.0)
+    cs.append(_case("batch_norm_3in", "BatchNorm", {"eps": float(np.float32(1e-5))}, [xb, mean, var]))
+    cs.append(_case("batch_norm_scale", "BatchNorm", {}, [xb, mean, var, np.array([0.999], np.float32)]))
+    cs.append(_case("batch_norm_scale0", "BatchNorm", {}, [xb, mean, var, np.array([0.0], np.float32)]))
+    cs.append(_case("batch_norm_negvar_2d", "BatchNorm", {"eps": float(np.float32(1e-3))},
+                    [normal(1253, (9, 4)), normal(1254, (4,)), normal(1255, (4,))]))
     # ---- Softmax ----------------------------------------------------------------------------
     cs.append(_case("softmax_rows", "Softmax", {"axis": 1}, [normal(1100, (37, 129), 0.0, 3.0)]))
     cs.append(_case("softmax_rows_neg_axis", "Softmax", {"axis": -1}, [normal(1101, (5, 3, 64), 0.0, 3.0)]))
@@ -229,6 +236,8 @@ def run_port(case) -> np.ndarray:
         return orc.eltwise(x, a["operation"], a.get("coeff", []))
     if op == "Axpy":
         return orc.axpy(x[0], x[1], x[2])
+    if op == "BatchNorm":
+        return orc.batch_norm(x[0], x[1], x[2], x[3] if len(x) == 4 else None, a.get("eps", 1e-5))
     raise KeyError(op)
 
 
@@ -258,7 +267,7 @@ def tolerance_class(case) -> str:
         return "exact"
     if op == "Reduce":
         return "exact" if a.get("operation", 0) in (2, 3) else "rel"
-    if op in ("Eltwise", "Axpy"):
+    if op in ("Eltwise", "Axpy", "BatchNorm"):
         return "exact"
     return "rel"
 
@@ -300,6 +309,12 @@ def run_cuda(case, device="cuda:0"):
         y = F.eltwise(x, a["operation"], a.get("coeff", []))
     elif op == "Axpy":
         y = F.axpy(x[0], x[1], x[2])
+    elif op == "BatchNorm":
+        sf = 1.0
+        if len(x) == 4:
+            sc = np.float32(case["inputs"][3].ravel()[0])
+            sf = float(np.float32(0) if sc == 0 else np.float32(1) / sc)
+        y = F.batch_norm(x[0], x[1], x[2], sf, a.get("eps", 1e-5))
     else:
         raise KeyError(op)
     torch.cuda.synchronize()
