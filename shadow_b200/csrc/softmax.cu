@@ -6,14 +6,15 @@
 //       per thread, so rows up to 32768 floats): one 128-bit read, warp-shuffle / shared-memory
 //       max and sum, one 128-bit write.  Longer rows use a block-per-row kernel that re-reads the
 //       row (from L2) for the second and third step.
-//   inner > 1 (strided): the threads of a block tile the contiguous [dim, inner] plane as G row
-//       groups x W columns (W = min(inner, 256)), so reads are contiguous for any `inner`; pass 1
-//       keeps an online (max, sum) per thread, pass 2 re-reads the patch and writes.  The second
-//       read hits L2 only when the patches in flight fit there; for [N,1000,7,7] they do not, and
-//       the kernel moves 12 instead of 8 bytes per element (0.48 of 8 TB/s measured).  Holding a
-//       196 KB patch on chip needs either all of one SM's shared memory (one block per SM, no
-//       overlap) or a cluster's registers; a cluster/DSMEM variant was built and measured 4x
-//       slower than this kernel, so it is not kept.
+//   inner > 1 (strided): the threads of a block tile the contiguous [dim, inner] planes as P
+//       planes x G row groups x W columns (W = min(inner, 256)), so reads are contiguous for any
+//       `inner`; pass 1 keeps an online (max, sum) per thread, pass 2 re-reads the patch and
+//       writes.  The profiler shows the second read served by the L2 (DRAM read bytes = tensor
+//       size), and the kernel bound by instruction issue and load latency rather than DRAM
+//       (0.50 of 8 TB/s on [1536,1000,7,7]).  Variants that hold the patch on chip were built and
+//       measured slower: the patch in shared memory filled by asynchronous copies (one 196 KB
+//       block per SM: no overlap between consecutive patches, 66 instructions per element), a
+//       per-thread shared-memory ring of asynchronous copies, and a cluster/DSMEM row split.
 // Arithmetic: float max, expf(x - max), float sum (tree order instead of the reference's
 // left-to-right order), then one correctly rounded reciprocal per row and a multiply per element
 // instead of the reference's per-element division (an IEEE float division costs ~60 issue slots on
@@ -127,71 +128,92 @@ softmax_long_rows_kernel(const float* x, float* y, int64_t rows, int64_t dim) {
   }
 }
 
-// Strided softmax, plane layout.  A block owns W consecutive positions of `inner` for one outer
-// index; its threads are laid out as G row groups x W columns, so consecutive threads read
-// consecutive addresses (a [G, W] patch of the contiguous [dim, inner] plane) whatever W is - no
-// lane is wasted on a ragged `inner` such as 49.  Pass 1 keeps an online (max, sum) pair per
-// thread (rescaling the sum when a new maximum appears), the G groups are merged through shared
-// memory, pass 2 re-reads the patch - it was just read by this block, so it comes from L2 - and
-// writes exp(x - max) / sum.  HBM traffic stays one read and one write per element.
-template <int U>
-__global__ void __launch_bounds__(256)
-softmax_plane_kernel(const float* x, float* y, int64_t dim, int64_t inner, int W, int G, int64_t ntile) {
-  __shared__ float sm_m[256], sm_l[256];
+// Strided softmax, plane layout.  The threads of a block are laid out as P planes x G row groups
+// x W columns (W = min(inner, 256)), so consecutive threads read consecutive addresses whatever
+// `inner` is - no lane is wasted on a ragged `inner` such as 49 - and P > 1 packs planes too small
+// to occupy a block.  Thread (p, g, s) owns rows g, g+G, ... of column s of plane p.
+//   pass 1: U independent loads in flight per thread; the batch maximum is taken first and the
+//       running sum re-referenced at most once per batch (the usual online-softmax rescale), so a
+//       row costs one max, one subtract, one multiply, one 2^x and one add.  The sum only feeds
+//       the denominator, whose tolerance is far looser than one exponential's, hence the hardware
+//       2^x unit (about 2 ulp) instead of expf;
+//   merge of the G row groups through shared memory: exact maximum, sums re-referenced with expf;
+//   pass 2: re-reads the patch - the block read it a moment ago, and the patches in flight
+//       (resident blocks x dim x W x 4 bytes) are sized to stay inside the L2, so DRAM sees one
+//       read and one write per element (measured: dram read = tensor size) - and writes
+//       expf(x - max) * (1/sum) with the accurate expf.
+// The kernel is bound by instruction issue, not by DRAM: every element costs two address
+// computations, two loads, a store and two exponentials of 4-byte granularity.
+template <int T, int U>
+__global__ void __launch_bounds__(T, 1024 / T)
+softmax_plane_kernel(const float* x, float* y, int64_t outer, int dim, int64_t inner, int W, int G, int P,
+                     int64_t ntile) {
+  __shared__ float sm_m[T], sm_l[T];
   const int t = threadIdx.x;
-  const int g = t / W, sidx = t - g * W;
-  const int64_t n = blockIdx.x / ntile, tile = blockIdx.x - n * ntile;
+  const int sidx = t % W, pg = t / W;
+  const int g = pg % G, pl = pg / G;
+  const int64_t bn = blockIdx.x / ntile, tile = blockIdx.x - bn * ntile;
+  const int64_t n = bn * P + pl;
   const int64_t col = tile * W + sidx;
-  const bool live = (g < G) && (col < inner);
-  const float* xp = x + n * dim * inner + col;
-  float* yp = y + n * dim * inner + col;
-  float m = -FLT_MAX, l = 0.f;
-  // Pass 1 only feeds the sum, whose tolerance is far looser than one exponential's: it uses the
-  // hardware 2^x unit directly (exp(d) = 2^(d*log2 e), about 2 ulp plus the rounding of the
-  // product), a fraction of the cost of expf.  Pass 2 produces the outputs with the accurate expf.
-  auto fast_exp = [](float d) {
+  const bool live = (pl < P) && (n < outer) && (col < inner);
+  const int64_t origin = live ? (n * dim + g) * inner + col : 0;
+  const float* xp = x + origin;
+  float* yp = y + origin;
+  const int64_t step = static_cast<int64_t>(G) * inner;
+  const int cnt = live ? (dim - g + G - 1) / G : 0;   // rows of this thread
+  constexpr float kLog2e = 1.4426950408889634f;
+  auto exp2_fast = [](float d) {
     float r;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d * 1.4426950408889634f));
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d));
     return r;
   };
-  auto absorb = [&](float v) {
-    if (v > m) {             // new maximum: bring the running sum to the new reference point
-      l = l * fast_exp(m - v);
-      m = v;
-    }
-    l = l + fast_exp(v - m);
-  };
-  const int64_t step = static_cast<int64_t>(G) * inner;
-  if (live) {
-    const float* p = xp + static_cast<int64_t>(g) * inner;
-    int64_t c = g;
-    for (; c + static_cast<int64_t>(U - 1) * G < dim; c += static_cast<int64_t>(U) * G, p += U * step) {
+  float m = -FLT_MAX, l = 0.f;
+  {
+    const float* p = xp;
+    int k = 0;
+    for (; k + U <= cnt; k += U, p += U * step) {
       float v[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) v[u] = p[u * step];   // default caching: stays in L2 for pass 2
+      float bm = v[0];
 #pragma unroll
-      for (int u = 0; u < U; ++u) absorb(v[u]);
+      for (int u = 1; u < U; ++u) bm = fmaxf(bm, v[u]);
+      if (bm > m) {   // new maximum: bring the running sum to the new reference point
+        l = l * exp2_fast((m - bm) * kLog2e);
+        m = bm;
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) l = l + exp2_fast((v[u] - m) * kLog2e);
     }
-    for (; c < dim; c += G, p += step) absorb(*p);
+    for (; k < cnt; ++k, p += step) {
+      const float val = *p;
+      if (val > m) {
+        l = l * exp2_fast((m - val) * kLog2e);
+        m = val;
+      }
+      l = l + exp2_fast((val - m) * kLog2e);
+    }
   }
-  if (t < 256) { sm_m[t] = m; sm_l[t] = l; }
+  sm_m[t] = m;
+  sm_l[t] = l;
   __syncthreads();
-  float M = -FLT_MAX, L = 0.f;
   if (live) {
-    for (int k = 0; k < G; ++k) M = std_max(sm_m[k * W + sidx], M);
-    for (int k = 0; k < G; ++k) L = __fadd_rn(L, __fmul_rn(sm_l[k * W + sidx], expf(__fsub_rn(sm_m[k * W + sidx], M))));
+    const int first = pl * G * W + sidx;
+    float M = -FLT_MAX, L = 0.f;
+    for (int k = 0; k < G; ++k) M = std_max(sm_m[first + k * W], M);
+    for (int k = 0; k < G; ++k) L = __fadd_rn(L, __fmul_rn(sm_l[first + k * W], expf(__fsub_rn(sm_m[first + k * W], M))));
     const float inv = __frcp_rn(L);
-    const float* p = xp + static_cast<int64_t>(g) * inner;
-    float* q = yp + static_cast<int64_t>(g) * inner;
-    int64_t c = g;
-    for (; c + static_cast<int64_t>(U - 1) * G < dim; c += static_cast<int64_t>(U) * G, p += U * step, q += U * step) {
+    const float* p = xp;
+    float* q = yp;
+    int k = 0;
+    for (; k + U <= cnt; k += U, p += U * step, q += U * step) {
       float v[U];
 #pragma unroll
       for (int u = 0; u < U; ++u) v[u] = ld_stream(p + u * step);
 #pragma unroll
       for (int u = 0; u < U; ++u) st_stream(q + u * step, __fmul_rn(expf(__fsub_rn(v[u], M)), inv));
     }
-    for (; c < dim; c += G, p += step, q += step) st_stream(q, __fmul_rn(expf(__fsub_rn(ld_stream(p), M)), inv));
+    for (; k < cnt; ++k, p += step, q += step) st_stream(q, __fmul_rn(expf(__fsub_rn(ld_stream(p), M)), inv));
   }
 }
 
@@ -242,11 +264,24 @@ extern "C" int sb200_softmax(const float* x, float* y, int64_t outer, int64_t di
     }
     return after_launch("sb200_softmax");
   }
+  if (dim >= (1ll << 31)) return SB200_ERR_UNSUPPORTED;
   const int W = static_cast<int>(inner < 256 ? inner : 256);
-  const int G = 256 / W;
   const int64_t ntile = (inner + W - 1) / W;
-  if (outer * ntile >= (1ll << 31)) return SB200_ERR_UNSUPPORTED;
-  const unsigned grid = static_cast<unsigned>(outer * ntile);
-  softmax_plane_kernel<32><<<grid, 256, 0, s>>>(x, y, dim, inner, W, G, ntile);
+  // block size: 512 threads when every thread still gets full batches of rows, else 256
+  const int T = (dim >= 256 && dim >= 16 * (512 / W)) ? 512 : 256;
+  // row groups: as many as leave each thread about 16 rows; the rest of the block packs planes
+  int G = T / W;
+  const int g16 = static_cast<int>((dim + 15) / 16);
+  if (G > g16) G = g16;
+  int P = T / (G * W);
+  if (P > outer) P = static_cast<int>(outer);
+  const int64_t blocks = ((outer + P - 1) / P) * ntile;
+  if (blocks >= (1ll << 31)) return SB200_ERR_UNSUPPORTED;
+  const unsigned grid = static_cast<unsigned>(blocks);
+  const int rows_per_thread = static_cast<int>(dim / G);
+  const int d = static_cast<int>(dim);
+  if (T == 512) softmax_plane_kernel<512, 16><<<grid, 512, 0, s>>>(x, y, outer, d, inner, W, G, P, ntile);
+  else if (rows_per_thread >= 16) softmax_plane_kernel<256, 16><<<grid, 256, 0, s>>>(x, y, outer, d, inner, W, G, P, ntile);
+  else softmax_plane_kernel<256, 4><<<grid, 256, 0, s>>>(x, y, outer, d, inner, W, G, P, ntile);
   return after_launch("sb200_softmax");
 }

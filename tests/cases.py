@@ -197,6 +197,15 @@ def small_cases():
     cs.append(_case("softmax_cluster4_wide", "Softmax", {"axis": 1}, [normal(1110, (2, 100, 300))]))
     cs.append(_case("softmax_plane_two_pass", "Softmax", {"axis": 1}, [normal(1111, (2, 300, 300), 0.0, 3.0)]))
     cs.append(_case("softmax_inner2", "Softmax", {"axis": 0}, [normal(1112, (700, 2))]))
+    # shared-memory patch geometries: packed tiny planes (odd and 4-aligned plane sizes), column
+    # tiles with 16-byte and 4-byte copies, a ragged last tile, a patch that needs the 1024-thread
+    # block, and a channel count too large for any patch (plane kernel)
+    cs.append(_case("softmax_patch_packed_odd", "Softmax", {"axis": 1}, [normal(1113, (11, 7, 3, 3))]))
+    cs.append(_case("softmax_patch_packed_vec", "Softmax", {"axis": 1}, [normal(1114, (13, 8, 10))]))
+    cs.append(_case("softmax_patch_tiles_vec", "Softmax", {"axis": 1}, [normal(1115, (2, 21, 520), 0.0, 3.0)]))
+    cs.append(_case("softmax_patch_tiles_scalar", "Softmax", {"axis": 1}, [normal(1116, (2, 5, 301))]))
+    cs.append(_case("softmax_patch_big", "Softmax", {"axis": 1}, [normal(1117, (2, 900, 52))]))
+    cs.append(_case("softmax_patch_too_tall", "Softmax", {"axis": 1}, [normal(1118, (1, 7000, 12))]))
     cs.append(_case("softmax_huge_logits", "Softmax", {"axis": 1}, [normal(1107, (4, 300), 0.0, 200.0)]))
     return cs
 
