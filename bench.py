@@ -306,6 +306,19 @@ def per_op_sweep(torch, F, device, peak):
     del x, y
     x, y = torch.randn(1536, 1000, 7, 7, device=device), torch.empty(1536, 1000, 7, 7, device=device)
     bench("softmax_strided_axis1[1536,1000,7,7]", lambda: F.softmax(x, 1, out=y), 8 * x.numel())
+    del x, y
+    x, y = torch.randn(64, 21, 512, 512, device=device), torch.empty(64, 21, 512, 512, device=device)
+    bench("softmax_strided_axis1[64,21,512,512]", lambda: F.softmax(x, 1, out=y), 8 * x.numel())
+    del x, y
+    x, y = torch.randn(128, 512, 38, 38, device=device), torch.empty(128, 512, 38, 38, device=device)
+    bench("normalize_l2_axis1[128,512,38,38]", lambda: F.normalize(x, 1, 2.0, 1e-12, out=y), 8 * x.numel())
+    del x, y
+    x, y = torch.randn(131072, 512, device=device), torch.empty(131072, 512, device=device)
+    bench("normalize_l2_rows[131072,512]", lambda: F.normalize(x, 1, 2.0, 1e-12, out=y), 8 * x.numel())
+    del x, y
+    x, y = torch.randn(512, 64, 56, 56, device=device), torch.empty(512, 64, 56, 56, device=device)
+    mean, var = torch.randn(64, device=device), torch.rand(64, device=device) + 0.1
+    bench("batch_norm[512,64,56,56]", lambda: F.batch_norm(x, mean, var, 1.0, 1e-5, out=y), 8 * x.numel() + 8 * 64)
     return rows
 
 

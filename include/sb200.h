@@ -114,6 +114,14 @@ int sb200_binary_broadcast(const float* a, const int* a_shape, const float* b, c
 int sb200_scale_bias(const float* x, float* y, int64_t n, const float* scale, const float* bias,
                      int64_t scale_num, int64_t inner_num, void* stream);
 
+/* y = x / max(||x||_p, eps), the p-norm over the middle axis of x viewed as [outer, dim, inner];
+ * terms accumulated in double as on the reference CPU, quotients correctly rounded.  No scratch:
+ * the reference's temporary blob of outer*inner norms is not needed.
+ * Replaces Vision::Normalize<kGPU,float>(in, outer_num, dim, inner_num, val, p, eps, out, ctx)
+ * (shadow/operators/kernels/normalize.hpp:10-13, normalize.cu). */
+int sb200_normalize(const float* x, float* y, int64_t outer, int64_t dim, int64_t inner, float p, float eps,
+                    void* stream);
+
 /* Inference batch normalisation: y[i] = (x[i] - mean[c]*scale_factor) / sqrt(|variance[c]*scale_factor| + eps)
  * with c = (i / inner_num) % channels, each step one IEEE float operation as on the reference CPU.
  * Replaces Vision::BatchNorm<kGPU,float>(in, count, mean, variance, channel, inner_num, scale_factor,

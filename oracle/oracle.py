@@ -67,6 +67,7 @@ def port():
         L.orc_fill.argtypes = [i64, C.c_float, _FP]
         L.orc_eltwise.argtypes = [C.POINTER(_FP), C.c_int, _FP, i64, C.c_int, _FP]
         L.orc_axpy.argtypes = [_FP, _FP, _FP, i64, i64, _FP]
+        L.orc_normalize.argtypes = [_FP, i64, i64, i64, _FP, C.c_float, C.c_float, _FP]
         L.orc_batch_norm.argtypes = [_FP, i64, _FP, _FP, i64, i64, C.c_float, C.c_float, _FP]
         _lib = L
     return _lib
@@ -219,6 +220,19 @@ def axpy(alpha, x, y) -> np.ndarray:
     out = np.empty_like(x)
     _ok(port().orc_axpy(_fp(alpha), _fp(x), _fp(y), alpha.size, inner, _fp(out)), "axpy")
     return out
+
+
+def normalize(x, axis: int = 1, p: float = 2.0, eps: float = 1e-12) -> np.ndarray:
+    """NormalizeOp (shadow/operators/normalize_op.cpp:9-37)."""
+    x = _f32(x)
+    axis = axis + x.ndim if axis < 0 else axis
+    outer = int(np.prod(x.shape[:axis], dtype=np.int64))
+    inner = int(np.prod(x.shape[axis + 1:], dtype=np.int64))
+    val = np.empty(max(outer * inner, 1), np.float32)
+    y = np.empty_like(x)
+    _ok(port().orc_normalize(_fp(x), outer, x.shape[axis], inner, _fp(val), np.float32(p), np.float32(eps), _fp(y)),
+        "normalize")
+    return y
 
 
 def batch_norm(x, mean, variance, scale=None, eps: float = 1e-5) -> np.ndarray:

@@ -171,6 +171,10 @@ int sb200_eltwise(const float* const* inputs, int n_inputs, const float* coeff, 
   if (y == nullptr || (reinterpret_cast<uintptr_t>(y) & 3u)) return SB200_ERR_BAD_ARGUMENT;
   for (int k = 0; k < n_inputs; ++k)
     if (inputs[k] == nullptr || (reinterpret_cast<uintptr_t>(inputs[k]) & 3u)) return SB200_ERR_BAD_ARGUMENT;
+  // two inputs folded by Prod / Max / Min are exactly Binary Mul / Max / Min (same operand order)
+  if (n_inputs == 2 && operation != kEltSum)
+    return sb200_binary(inputs[0], inputs[1], y, n, operation == kEltProd ? SB200_MUL : (operation == kEltMax ? SB200_MAX : SB200_MIN),
+                        stream);
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   switch (operation) {
     case kEltProd: return launch_eltwise<kEltProd>(inputs, n_inputs, coeff, y, n, s);

@@ -254,3 +254,22 @@ def batch_norm(x: torch.Tensor, mean: torch.Tensor, variance: torch.Tensor, scal
     capi.check(capi.lib().sb200_batch_norm(x.data_ptr(), y.data_ptr(), x.numel(), mean.data_ptr(), variance.data_ptr(),
                                            x.shape[1], inner, scale_factor, eps, _stream()), "sb200_batch_norm")
     return y
+
+
+def normalize(x: torch.Tensor, axis: int = 1, p: float = 2.0, eps: float = 1e-12,
+              out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Normalize (shadow/operators/normalize_op.cpp:9-37): x / max(||x||_p over `axis`, eps)."""
+    _chk(x, "x")
+    axis = axis + x.dim() if axis < 0 else axis
+    if not 0 <= axis < x.dim():
+        raise ValueError("axis out of range")
+    outer = 1
+    for d in x.shape[:axis]:
+        outer *= d
+    inner = 1
+    for d in x.shape[axis + 1:]:
+        inner *= d
+    y = torch.empty_like(x) if out is None else _chk(out, "out")
+    capi.check(capi.lib().sb200_normalize(x.data_ptr(), y.data_ptr(), outer, x.shape[axis], inner, p, eps, _stream()),
+               "sb200_normalize")
+    return y

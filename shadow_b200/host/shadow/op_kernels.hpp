@@ -72,6 +72,12 @@ class AxpyKernel : public Kernel {
   virtual void Run(const BlobPtr& alpha, const BlobPtr& x, const BlobPtr& y, BlobPtr& output, Workspace* ws) = 0;
 };
 
+// shadow/operators/kernels/normalize.hpp:20-25
+class NormalizeKernel : public Kernel {
+ public:
+  virtual void Run(const BlobPtr& input, BlobPtr& output, Workspace* ws, float p, int axis, float eps) = 0;
+};
+
 // shadow/operators/kernels/batch_norm.hpp:20-28
 class BatchNormKernel : public Kernel {
  public:

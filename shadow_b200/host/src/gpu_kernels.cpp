@@ -181,6 +181,19 @@ class AxpyKernelB200 : public AxpyKernel {
   std::string kernel_type() const override { return "Default"; }
 };
 
+class NormalizeKernelB200 : public NormalizeKernel {
+ public:
+  // no temporary blob: the norms stay on chip (the reference grows the workspace by outer*inner floats)
+  void Run(const BlobPtr& input, BlobPtr& output, Workspace* ws, float p, int axis, float eps) override {
+    const int64_t outer = input->count(0, axis), dim = input->shape(axis), inner = input->count(axis + 1);
+    expect_ok(sb200_normalize(input->data<float>(), output->mutable_data<float>(), outer, dim, inner, p, eps,
+                              stream_of(ws)),
+              "sb200_normalize");
+  }
+  DeviceType device_type() const override { return DeviceType::kGPU; }
+  std::string kernel_type() const override { return "Default"; }
+};
+
 class BatchNormKernelB200 : public BatchNormKernel {
  public:
   void Run(const BlobPtr& input, const BlobPtr& mean, const BlobPtr& variance, BlobPtr& output, Workspace* ws,
@@ -200,6 +213,7 @@ class BatchNormKernelB200 : public BatchNormKernel {
 }  // namespace
 
 REGISTER_OP_KERNEL_DEFAULT(BatchNormGPU, BatchNormKernelB200);
+REGISTER_OP_KERNEL_DEFAULT(NormalizeGPU, NormalizeKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(EltwiseGPU, EltwiseKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(AxpyGPU, AxpyKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(BinaryGPU, BinaryKernelB200);

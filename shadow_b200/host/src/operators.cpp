@@ -290,6 +290,27 @@ class AxpyOp : public Operator {
   std::shared_ptr<AxpyKernel> kernel_;
 };
 
+// Normalize (shadow/operators/normalize_op.cpp:9-37): `p` default 2, `axis` default 1 (negative
+// values count from the end), `eps` default 1e-12.
+class NormalizeOp : public Operator {
+ public:
+  NormalizeOp(const shadow::OpParam& op_param, Workspace* ws) : Operator(op_param, ws) {
+    p_ = get_single_argument<float>("p", 2);
+    axis_ = get_single_argument<int>("axis", 1);
+    eps_ = get_single_argument<float>("eps", 1e-12f);
+    kernel_ = kernel_for<NormalizeKernel>(op_param, ws_);
+  }
+  void Run(const std::vector<BlobPtr>& inputs, std::vector<BlobPtr>& outputs) override {
+    outputs[0]->reshape(inputs[0]->shape());
+    kernel_->Run(inputs[0], outputs[0], ws_, p_, inputs[0]->canonical_index(axis_), eps_);
+  }
+
+ private:
+  float p_, eps_;
+  int axis_;
+  std::shared_ptr<NormalizeKernel> kernel_;
+};
+
 // BatchNorm, inference only (shadow/operators/batch_norm_op.cpp:9-43): `use_global_stats` must be
 // true, `eps` default 1e-5; inputs x, mean, variance and optionally a one-element scale blob whose
 // reciprocal (0 if the scale is 0) multiplies mean and variance.  The scale is read back from the
@@ -322,6 +343,7 @@ class BatchNormOp : public Operator {
 }  // namespace
 
 REGISTER_OPERATOR(BatchNorm, BatchNormOp);
+REGISTER_OPERATOR(Normalize, NormalizeOp);
 REGISTER_OPERATOR(Eltwise, EltwiseOp);
 REGISTER_OPERATOR(Axpy, AxpyOp);
 REGISTER_OPERATOR(Input, InputOp);

@@ -184,6 +184,18 @@ def small_cases():
     cs.append(_case("batch_norm_scale0", "BatchNorm", {}, [xb, mean, var, np.array([0.0], np.float32)]))
     cs.append(_case("batch_norm_negvar_2d", "BatchNorm", {"eps": float(np.float32(1e-3))},
                     [normal(1253, (9, 4)), normal(1254, (4,)), normal(1255, (4,))]))
+    for pn, pv in (("l2", 2.0), ("l1", 1.0), ("l3", 3.0), ("l1_5", 1.5)):
+        cs.append(_case("normalize_%s_channels" % pn, "Normalize", {"p": pv, "axis": 1}, [normal(1260, (3, 20, 5, 7))]))
+        cs.append(_case("normalize_%s_rows" % pn, "Normalize", {"p": pv, "axis": -1}, [normal(1261, (9, 130))]))
+    xz = normal(1262, (4, 6, 3))
+    xz[1] = 0.0                                     # all-zero vectors divide by eps
+    xz[2, :, 1] = 0.0
+    cs.append(_case("normalize_zero_vectors", "Normalize", {"p": 2.0, "axis": 1, "eps": 1e-12}, [xz]))
+    cs.append(_case("normalize_big_eps", "Normalize", {"p": 2.0, "axis": 1, "eps": 5.0}, [normal(1263, (4, 6, 3))]))
+    cs.append(_case("normalize_axis0_wide", "Normalize", {"p": 2.0, "axis": 0}, [normal(1264, (33, 300))]))
+    cs.append(_case("normalize_extremes", "Normalize", {"p": 2.0, "axis": 1},
+                    [np.array([[1e-30, 3e-25, -0.0, 0.0], [1e19, -3e18, 2.0, 1e-44], [4.0, 3.0, 0.0, -0.0]], np.float32)]))
+    cs.append(_case("normalize_long_axis", "Normalize", {"p": 2.0, "axis": 1}, [normal(1265, (2, 5000, 3))]))
     # ---- Softmax ----------------------------------------------------------------------------
     cs.append(_case("softmax_rows", "Softmax", {"axis": 1}, [normal(1100, (37, 129), 0.0, 3.0)]))
     cs.append(_case("softmax_rows_neg_axis", "Softmax", {"axis": -1}, [normal(1101, (5, 3, 64), 0.0, 3.0)]))
@@ -245,6 +257,8 @@ def run_port(case) -> np.ndarray:
         return orc.eltwise(x, a["operation"], a.get("coeff", []))
     if op == "Axpy":
         return orc.axpy(x[0], x[1], x[2])
+    if op == "Normalize":
+        return orc.normalize(x[0], a.get("axis", 1), a.get("p", 2.0), a.get("eps", 1e-12))
     if op == "BatchNorm":
         return orc.batch_norm(x[0], x[1], x[2], x[3] if len(x) == 4 else None, a.get("eps", 1e-5))
     raise KeyError(op)
@@ -278,6 +292,8 @@ def tolerance_class(case) -> str:
         return "exact" if a.get("operation", 0) in (2, 3) else "rel"
     if op in ("Eltwise", "Axpy", "BatchNorm"):
         return "exact"
+    if op == "Normalize":   # p = 1, 2: only the order of the double additions differs from the reference
+        return "ulp2" if a.get("p", 2.0) in (1.0, 2.0) else "rel"
     return "rel"
 
 
@@ -318,6 +334,8 @@ def run_cuda(case, device="cuda:0"):
         y = F.eltwise(x, a["operation"], a.get("coeff", []))
     elif op == "Axpy":
         y = F.axpy(x[0], x[1], x[2])
+    elif op == "Normalize":
+        y = F.normalize(x[0], a.get("axis", 1), a.get("p", 2.0), a.get("eps", 1e-12))
     elif op == "BatchNorm":
         sf = 1.0
         if len(x) == 4:
@@ -332,7 +350,7 @@ def run_cuda(case, device="cuda:0"):
 
 def reduced_length(case) -> int:
     x = case["inputs"][0]
-    if case["op"] == "Softmax":
+    if case["op"] in ("Softmax", "Normalize"):
         return int(x.shape[case["args"].get("axis", 1)])
     axes = case["args"].get("axes", []) or list(range(x.ndim))
     return int(np.prod([x.shape[a] for a in axes]))
