@@ -382,7 +382,9 @@ def run_b200_arm(args):
         safety = threading.Timer(180.0, os._exit, args=(3,))
         safety.daemon = True
         safety.start()
-        dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local_rank))
+        opts = dist.ProcessGroupNCCL.Options()
+        opts.is_high_priority_stream = True    # the 16-byte exchange must not queue behind a full-GPU kernel
+        dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local_rank), pg_options=opts)
     assert world == args.gpus or world == 1, "launch with torchrun --nproc-per-node %d" % args.gpus
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
@@ -402,13 +404,22 @@ def run_b200_arm(args):
 
     r_sum = torch.empty(1, dtype=torch.float32, device=device)
     r_max = torch.empty(1, dtype=torch.float32, device=device)
-    record = torch.empty(2, dtype=torch.float64, device=device)          # this rank's (sum, max) partials
-    gathered = torch.empty(2 * world, dtype=torch.float64, device=device)
+    # Steps are captured `chunk` at a time (the largest divisor of --steps up to 10), each with its
+    # own 16-byte record, so that the exchange of step i can run beside the Mul of step i+1.
+    chunk = 1
+    if world > 1 and not args.no_graph:
+        chunk = max(c for c in range(1, 11) if args.steps % c == 0)
+    records = torch.empty(chunk, 2, dtype=torch.float64, device=device)   # this rank's (sum, max) partials per step
+    gathers = torch.empty(chunk, 2 * world, dtype=torch.float64, device=device)
     total = numel(O_SHAPE)
+    side = torch.cuda.Stream(device=device, priority=-1) if world > 1 else None
 
-    def step(evs=None):
+    def step(evs=None, slot=0, overlap=False):
         """One pass of the chain.  With several ranks the two reductions share ONE collective: each
-        rank's double partials (sum, max) are all-gathered and merged locally in rank order."""
+        rank's double partials (sum, max) are all-gathered and merged locally in rank order.  With
+        `overlap` the collective and the merge go to a side stream that the caller joins later, so
+        the next step's Mul does not wait for them."""
+        record, gathered = records[slot], gathers[slot]
         def mark(i):
             if evs is not None:
                 evs[i].record()
@@ -423,9 +434,17 @@ def run_b200_arm(args):
             F.reduce_partial(O, RED_SUM, [], out=record[0:1])
             mark(2)
             F.reduce_partial(O, RED_MAX, [], out=record[1:2])
-            dist.all_gather_into_tensor(gathered, record)
-            F.reduce_combine(gathered, world, 2, 1, RED_SUM, total, out=r_sum)
-            F.reduce_combine(gathered[1:], world, 2, 1, RED_MAX, total, out=r_max)
+
+            def exchange():
+                dist.all_gather_into_tensor(gathered, record)
+                F.reduce_combine(gathered, world, 2, 1, RED_SUM, total, out=r_sum)
+                F.reduce_combine(gathered[1:], world, 2, 1, RED_MAX, total, out=r_max)
+            if overlap:
+                side.wait_stream(torch.cuda.current_stream())
+                with torch.cuda.stream(side):
+                    exchange()
+            else:
+                exchange()
         mark(3)
 
     for _ in range(max(args.warmup, 3)):
@@ -439,13 +458,17 @@ def run_b200_arm(args):
         graph = torch.cuda.CUDAGraph()
         launches_before = capi.launch_count()
         with torch.cuda.graph(graph):
-            step()
-        launches_per_step = capi.launch_count() - launches_before
+            for c in range(chunk):
+                step(slot=c, overlap=chunk > 1)
+            if chunk > 1:
+                torch.cuda.current_stream().wait_stream(side)   # join: every exchange of the chunk has finished
+        launches_per_step = (capi.launch_count() - launches_before) // chunk
         for _ in range(3):
             graph.replay()
         torch.cuda.synchronize()
 
-    def run_step():
+    def run_chunk():
+        """`chunk` steps (one graph replay), or one directly launched step."""
         if graph is not None:
             graph.replay()
         else:
@@ -458,8 +481,8 @@ def run_b200_arm(args):
     launches_before = capi.launch_count()
     with ClockSampler(local_rank) as clocks:
         start.record()
-        for k in range(args.steps):
-            run_step()
+        for k in range(args.steps // chunk):
+            run_chunk()
         end.record()
         torch.cuda.synchronize()
         ms_total = start.elapsed_time(end)
@@ -474,8 +497,8 @@ def run_b200_arm(args):
         extra = 0
         if ms_total < 250.0 and not args.no_clocks:
             extra = int(min(5000, (250.0 - ms_total) / max(ms_total / args.steps, 1e-3)))
-            for k in range(extra):
-                run_step()
+            for k in range(extra // chunk):
+                run_chunk()
             torch.cuda.synchronize()
     launches = (launches_per_step * args.steps) if graph is not None else (capi.launch_count() - launches_before)
     if dist is not None:
@@ -523,8 +546,9 @@ def run_b200_arm(args):
                                "ReduceSum all axes, ReduceMax all axes; dim 0 split over the ranks",
                    "l2": "inputs larger than L2 (each step streams >= 256 MiB per GPU; no flush interposed)",
                    "bytes_per_step": sum(bytes_job.values()),
-                   "collective": "one nccl all_gather of 16 B per rank per step (sum and max partials together)" if world > 1 else "none",
-                   "launch": "cuda graph replay" if graph is not None else "direct launches"},
+                   "collective": ("one nccl all_gather of 16 B per rank per step (sum and max partials together)"
+                                  + (", on a side stream beside the next step's Mul" if chunk > 1 else "")) if world > 1 else "none",
+                   "launch": ("cuda graph replay, %d steps per graph" % chunk) if graph is not None else "direct launches"},
         "frac_of_8tbs_per_gpu": round(value / world / NOMINAL_PEAK_GBS, 4),
         "roofline": roofline, "per_step_ops": per_step_ops,
         "e2e": None if args.no_e2e else {"value": round(e2e_value, 3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
