@@ -114,6 +114,21 @@ int sb200_binary_broadcast(const float* a, const int* a_shape, const float* b, c
 int sb200_scale_bias(const float* x, float* y, int64_t n, const float* scale, const float* bias,
                      int64_t scale_num, int64_t inner_num, void* stream);
 
+/* Row normalisation of x viewed as [rows, inner] (contiguous rows): mean = sum(x/inner),
+ * v = x - mean, var = sum(v*v/inner), y = v / sqrt(var + eps); then, unless affine_mode is 0,
+ * y*scale[k] + bias[k] with k = position in the row (affine_mode 1: LayerNorm) or the channel
+ * (affine_mode 2: row r belongs to group r % groups of channels_per_group channels of `spatial`
+ * elements each, inner == channels_per_group*spatial: GroupNorm; InstanceNorm is groups = channels,
+ * channels_per_group = 1).  Terms are accumulated in double as by the reference's CPU Sgemv.
+ * No scratch (the reference uses count + inner + 2*rows floats and six launches).
+ * Replaces the Default GPU kernels LayerNormKernelDefault<kGPU>::Run
+ * (shadow/operators/kernels/layer_norm.hpp:20-75) and GroupNormKernelDefault<kGPU>::Run
+ * (shadow/operators/kernels/group_norm.hpp:41-87), i.e. Blas::Set + Blas::BlasSgemv x2 +
+ * Vision::SubtractMeanAndSquare + Vision::DivideVariance + Vision::ScaleBias. */
+int sb200_row_norm(const float* x, float* y, int64_t rows, int64_t inner, float eps, const float* scale,
+                   const float* bias, int affine_mode, int64_t groups, int64_t channels_per_group,
+                   int64_t spatial, void* stream);
+
 /* y = x / max(||x||_p, eps), the p-norm over the middle axis of x viewed as [outer, dim, inner];
  * terms accumulated in double as on the reference CPU, quotients correctly rounded.  No scratch:
  * the reference's temporary blob of outer*inner norms is not needed.

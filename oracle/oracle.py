@@ -67,6 +67,7 @@ def port():
         L.orc_fill.argtypes = [i64, C.c_float, _FP]
         L.orc_eltwise.argtypes = [C.POINTER(_FP), C.c_int, _FP, i64, C.c_int, _FP]
         L.orc_axpy.argtypes = [_FP, _FP, _FP, i64, i64, _FP]
+        L.orc_row_norm.argtypes = [_FP, i64, i64, C.c_float, _FP, _FP, i64, i64, _FP]
         L.orc_normalize.argtypes = [_FP, i64, i64, i64, _FP, C.c_float, C.c_float, _FP]
         L.orc_batch_norm.argtypes = [_FP, i64, _FP, _FP, i64, i64, C.c_float, C.c_float, _FP]
         _lib = L
@@ -220,6 +221,31 @@ def axpy(alpha, x, y) -> np.ndarray:
     out = np.empty_like(x)
     _ok(port().orc_axpy(_fp(alpha), _fp(x), _fp(y), alpha.size, inner, _fp(out)), "axpy")
     return out
+
+
+def _row_norm(x, rows, inner, eps, scale, bias, scale_num, scale_inner):
+    y = np.empty_like(x)
+    sc = _f32(scale) if scale is not None else None     # kept alive across the call
+    bs = _f32(bias) if bias is not None else None
+    sp = _fp(sc) if sc is not None else None
+    bp = _fp(bs) if bs is not None else None
+    _ok(port().orc_row_norm(_fp(x), rows, inner, np.float32(eps), sp, bp, scale_num, scale_inner, _fp(y)), "row_norm")
+    return y
+
+
+def layer_norm(x, normalized_shape, scale=None, bias=None, eps: float = 1e-5) -> np.ndarray:
+    """LayerNormOp (shadow/operators/layer_norm_op.cpp:9-50)."""
+    x = _f32(x)
+    inner = int(np.prod(normalized_shape, dtype=np.int64))
+    return _row_norm(x, x.size // inner, inner, eps, scale, bias, inner, 1)
+
+
+def group_norm(x, group: int, scale=None, bias=None, eps: float = 1e-5) -> np.ndarray:
+    """GroupNormOp (shadow/operators/group_norm_op.cpp:9-45); InstanceNormOp is group == channels."""
+    x = _f32(x)
+    rows = x.shape[0] * group
+    spatial = int(np.prod(x.shape[2:], dtype=np.int64))
+    return _row_norm(x, rows, x.size // rows, eps, scale, bias, x.shape[1], spatial)
 
 
 def normalize(x, axis: int = 1, p: float = 2.0, eps: float = 1e-12) -> np.ndarray:

@@ -96,6 +96,23 @@ __device__ __forceinline__ float tanh_accurate(float x) {
   return (x == x) ? y : x;                        // NaN
 }
 
+// x / d, correctly rounded, without the division instruction.  `rcp` is the correctly rounded
+// reciprocal of d.  q0 = x*rcp is within an ulp of the quotient, the residual r = x - d*q0 is
+// exact in one fused multiply-add, and q0 + r*rcp rounds to the IEEE quotient (Markstein's
+// division step).  That argument needs every intermediate to stay a normal float, which holds
+// when |x| and d lie in [2^-60, 2^60] (`d_ok` covers d); anything else - zeros, denormals, huge
+// values, infinities, NaN - takes the division instruction.
+__device__ __forceinline__ float div_exact(float x, float d, float rcp, bool d_ok) {
+  const uint32_t ax = __float_as_uint(x) & 0x7fffffffu;
+  const uint32_t lo = (127u - 60u) << 23, hi = (127u + 60u) << 23;
+  if (d_ok && (ax - lo) <= (hi - lo)) {
+    const float q0 = __fmul_rn(x, rcp);
+    const float r = __fmaf_rn(-d, q0, x);
+    return __fmaf_rn(r, rcp, q0);
+  }
+  return __fdiv_rn(x, d);
+}
+
 // ---- functors -----------------------------------------------------------------------------------
 // std::max(a, b) == (a < b) ? b : a and std::min(a, b) == (b < a) ? b : a.
 __device__ __forceinline__ float std_max(float a, float b) { return (a < b) ? b : a; }

@@ -30,23 +30,6 @@ __device__ __forceinline__ double norm_term(float v, float p) {
   return static_cast<double>(powf(a, p));
 }
 
-// x / d, correctly rounded, without the division instruction.  `rcp` is the correctly rounded
-// reciprocal of d.  q0 = x*rcp is within an ulp of the quotient, the residual r = x - d*q0 is
-// exact in one fused multiply-add, and q0 + r*rcp rounds to the IEEE quotient (Markstein's
-// division step).  That argument needs every intermediate to stay a normal float, which holds
-// when |x| and d lie in [2^-60, 2^60] (`d_ok` covers d); anything else - zeros, denormals, huge
-// values, infinities, NaN - takes the division instruction.
-__device__ __forceinline__ float div_exact(float x, float d, float rcp, bool d_ok) {
-  const uint32_t ax = __float_as_uint(x) & 0x7fffffffu;
-  const uint32_t lo = (127u - 60u) << 23, hi = (127u + 60u) << 23;
-  if (d_ok && (ax - lo) <= (hi - lo)) {
-    const float q0 = __fmul_rn(x, rcp);
-    const float r = __fmaf_rn(-d, q0, x);
-    return __fmaf_rn(r, rcp, q0);
-  }
-  return __fdiv_rn(x, d);
-}
-
 template <int MODE, int kT, int kU>
 __global__ void __launch_bounds__(kT, 1024 / kT)
 normalize_plane_kernel(const float* x, float* y, int64_t outer, int dim, int64_t inner, int W, int G, int P,

@@ -273,3 +273,56 @@ def normalize(x: torch.Tensor, axis: int = 1, p: float = 2.0, eps: float = 1e-12
     capi.check(capi.lib().sb200_normalize(x.data_ptr(), y.data_ptr(), outer, x.shape[axis], inner, p, eps, _stream()),
                "sb200_normalize")
     return y
+
+
+def _row_norm(x, rows, inner, eps, scale, bias, mode, groups, cpg, spatial, out):
+    y = torch.empty_like(x) if out is None else _chk(out, "out")
+    sp = _chk(scale, "scale").data_ptr() if scale is not None else None
+    bp = _chk(bias, "bias").data_ptr() if bias is not None else None
+    capi.check(capi.lib().sb200_row_norm(x.data_ptr(), y.data_ptr(), rows, inner, eps, sp, bp, mode, groups, cpg, spatial,
+                                         _stream()), "sb200_row_norm")
+    return y
+
+
+def layer_norm(x: torch.Tensor, normalized_shape, scale: Optional[torch.Tensor] = None,
+               bias: Optional[torch.Tensor] = None, eps: float = 1e-5, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """LayerNorm (shadow/operators/layer_norm_op.cpp:9-50): statistics over the trailing
+    `normalized_shape` dims; scale and bias (both or neither) have that shape."""
+    _chk(x, "x")
+    k = len(normalized_shape)
+    if k < 1 or tuple(x.shape[x.dim() - k:]) != tuple(normalized_shape):
+        raise ValueError("normalized_shape must equal the trailing dims of x")
+    inner = 1
+    for d in normalized_shape:
+        inner *= d
+    if (scale is None) != (bias is None):
+        raise ValueError("scale and bias come together")
+    if scale is not None and (scale.numel() != inner or bias.numel() != inner):
+        raise ValueError("scale/bias must have normalized_shape")
+    return _row_norm(x, x.numel() // inner, inner, eps, scale, bias, 1 if scale is not None else 0, 1, 1, 1, out)
+
+
+def group_norm(x: torch.Tensor, group: int, scale: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+               eps: float = 1e-5, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """GroupNorm (shadow/operators/group_norm_op.cpp:9-45): statistics per (sample, group of
+    channels); scale and bias (both or neither) per channel.  InstanceNorm is group == channels."""
+    _chk(x, "x")
+    channel = x.shape[1]
+    if group < 1 or channel % group:
+        raise ValueError("channels must be divisible by group")
+    spatial = 1
+    for d in x.shape[2:]:
+        spatial *= d
+    cpg = channel // group
+    if (scale is None) != (bias is None):
+        raise ValueError("scale and bias come together")
+    if scale is not None and (scale.numel() != channel or bias.numel() != channel):
+        raise ValueError("scale/bias must have one value per channel")
+    return _row_norm(x, x.shape[0] * group, cpg * spatial, eps, scale, bias, 2 if scale is not None else 0, group, cpg,
+                     spatial, out)
+
+
+def instance_norm(x: torch.Tensor, scale: Optional[torch.Tensor] = None, bias: Optional[torch.Tensor] = None,
+                  eps: float = 1e-5, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """InstanceNorm (shadow/operators/instance_norm_op.cpp:9-40): GroupNorm with one channel per group."""
+    return group_norm(x, x.shape[1], scale, bias, eps, out)

@@ -72,6 +72,20 @@ class AxpyKernel : public Kernel {
   virtual void Run(const BlobPtr& alpha, const BlobPtr& x, const BlobPtr& y, BlobPtr& output, Workspace* ws) = 0;
 };
 
+// shadow/operators/kernels/group_norm.hpp:30-37 (also used by InstanceNorm with group = channels)
+class GroupNormKernel : public Kernel {
+ public:
+  virtual void Run(const BlobPtr& input, const BlobPtr& scale, const BlobPtr& bias, BlobPtr& output, Workspace* ws,
+                   int group, float eps) = 0;
+};
+
+// shadow/operators/kernels/layer_norm.hpp:8-16
+class LayerNormKernel : public Kernel {
+ public:
+  virtual void Run(const BlobPtr& input, const BlobPtr& scale, const BlobPtr& bias, BlobPtr& output, Workspace* ws,
+                   const VecInt& normalized_shape, float eps) = 0;
+};
+
 // shadow/operators/kernels/normalize.hpp:20-25
 class NormalizeKernel : public Kernel {
  public:

@@ -181,6 +181,49 @@ class AxpyKernelB200 : public AxpyKernel {
   std::string kernel_type() const override { return "Default"; }
 };
 
+// One fused launch and no temporary blobs (the reference grows the workspace by count + inner +
+// 2*rows floats and makes six launches).
+class GroupNormKernelB200 : public GroupNormKernel {
+ public:
+  void Run(const BlobPtr& input, const BlobPtr& scale, const BlobPtr& bias, BlobPtr& output, Workspace* ws, int group,
+           float eps) override {
+    const int64_t count = static_cast<int64_t>(input->count64());
+    const int64_t rows = static_cast<int64_t>(input->shape(0)) * group, inner = count / rows;
+    const bool affine = scale != nullptr && bias != nullptr;
+    const int channel = input->shape(1);
+    if (affine) {
+      CHECK_EQ(scale->count(), channel);
+      CHECK_EQ(bias->count(), channel);
+    }
+    expect_ok(sb200_row_norm(input->data<float>(), output->mutable_data<float>(), rows, inner, eps,
+                             affine ? scale->data<float>() : nullptr, affine ? bias->data<float>() : nullptr,
+                             affine ? 2 : 0, group, channel / group, input->count(2), stream_of(ws)),
+              "sb200_row_norm");
+  }
+  DeviceType device_type() const override { return DeviceType::kGPU; }
+  std::string kernel_type() const override { return "Default"; }
+};
+
+class LayerNormKernelB200 : public LayerNormKernel {
+ public:
+  void Run(const BlobPtr& input, const BlobPtr& scale, const BlobPtr& bias, BlobPtr& output, Workspace* ws,
+           const VecInt& normalized_shape, float eps) override {
+    const int64_t inner = input->count(input->num_axes() - static_cast<int>(normalized_shape.size()));
+    const int64_t rows = static_cast<int64_t>(input->count64()) / inner;
+    const bool affine = scale != nullptr && bias != nullptr;
+    if (affine) {
+      CHECK(scale->shape() == normalized_shape);
+      CHECK(bias->shape() == normalized_shape);
+    }
+    expect_ok(sb200_row_norm(input->data<float>(), output->mutable_data<float>(), rows, inner, eps,
+                             affine ? scale->data<float>() : nullptr, affine ? bias->data<float>() : nullptr,
+                             affine ? 1 : 0, 1, 1, 1, stream_of(ws)),
+              "sb200_row_norm");
+  }
+  DeviceType device_type() const override { return DeviceType::kGPU; }
+  std::string kernel_type() const override { return "Default"; }
+};
+
 class NormalizeKernelB200 : public NormalizeKernel {
  public:
   // no temporary blob: the norms stay on chip (the reference grows the workspace by outer*inner floats)
@@ -214,6 +257,8 @@ class BatchNormKernelB200 : public BatchNormKernel {
 
 REGISTER_OP_KERNEL_DEFAULT(BatchNormGPU, BatchNormKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(NormalizeGPU, NormalizeKernelB200);
+REGISTER_OP_KERNEL_DEFAULT(GroupNormGPU, GroupNormKernelB200);
+REGISTER_OP_KERNEL_DEFAULT(LayerNormGPU, LayerNormKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(EltwiseGPU, EltwiseKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(AxpyGPU, AxpyKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(BinaryGPU, BinaryKernelB200);

@@ -290,6 +290,86 @@ class AxpyOp : public Operator {
   std::shared_ptr<AxpyKernel> kernel_;
 };
 
+// GroupNorm (shadow/operators/group_norm_op.cpp:9-45): `group` default 1, `eps` default 1e-5; one
+// input, or three (x, per-channel scale, per-channel bias).
+class GroupNormOp : public Operator {
+ public:
+  GroupNormOp(const shadow::OpParam& op_param, Workspace* ws) : Operator(op_param, ws) {
+    group_ = get_single_argument<int>("group", 1);
+    eps_ = get_single_argument<float>("eps", 1e-5f);
+    kernel_ = kernel_for<GroupNormKernel>(op_param, ws_);
+  }
+  void Run(const std::vector<BlobPtr>& inputs, std::vector<BlobPtr>& outputs) override {
+    outputs[0]->reshape(inputs[0]->shape());
+    CHECK_EQ(inputs[0]->shape(1) % group_, 0);
+    if (inputs.size() == 1) {
+      kernel_->Run(inputs[0], nullptr, nullptr, outputs[0], ws_, group_, eps_);
+    } else {
+      CHECK_EQ(inputs.size(), 3u);
+      kernel_->Run(inputs[0], inputs[1], inputs[2], outputs[0], ws_, group_, eps_);
+    }
+  }
+
+ private:
+  int group_;
+  float eps_;
+  std::shared_ptr<GroupNormKernel> kernel_;
+};
+
+// InstanceNorm (shadow/operators/instance_norm_op.cpp:9-40): the GroupNorm kernel with one channel
+// per group.
+class InstanceNormOp : public Operator {
+ public:
+  InstanceNormOp(const shadow::OpParam& op_param, Workspace* ws) : Operator(op_param, ws) {
+    eps_ = get_single_argument<float>("eps", 1e-5f);
+    kernel_ = std::dynamic_pointer_cast<GroupNormKernel>(CreateKernel("GroupNorm", ws_->Ctx()->device_type()));
+    CHECK_NOTNULL(kernel_);
+  }
+  void Run(const std::vector<BlobPtr>& inputs, std::vector<BlobPtr>& outputs) override {
+    outputs[0]->reshape(inputs[0]->shape());
+    const int channel = inputs[0]->shape(1);
+    if (inputs.size() == 1) {
+      kernel_->Run(inputs[0], nullptr, nullptr, outputs[0], ws_, channel, eps_);
+    } else {
+      CHECK_EQ(inputs.size(), 3u);
+      kernel_->Run(inputs[0], inputs[1], inputs[2], outputs[0], ws_, channel, eps_);
+    }
+  }
+
+ private:
+  float eps_;
+  std::shared_ptr<GroupNormKernel> kernel_;
+};
+
+// LayerNorm (shadow/operators/layer_norm_op.cpp:9-50): `normalized_shape` (required) must equal
+// the trailing dims of the input; `eps` default 1e-5; one input, or three (x, scale, bias).
+class LayerNormOp : public Operator {
+ public:
+  LayerNormOp(const shadow::OpParam& op_param, Workspace* ws) : Operator(op_param, ws) {
+    normalized_shape_ = get_repeated_argument<int>("normalized_shape");
+    CHECK(!normalized_shape_.empty());
+    eps_ = get_single_argument<float>("eps", 1e-5f);
+    kernel_ = kernel_for<LayerNormKernel>(op_param, ws_);
+  }
+  void Run(const std::vector<BlobPtr>& inputs, std::vector<BlobPtr>& outputs) override {
+    const auto& input = inputs[0];
+    outputs[0]->reshape(input->shape());
+    const int k = static_cast<int>(normalized_shape_.size());
+    for (int n = 0; n < k; ++n) CHECK_EQ(input->shape(n - k), normalized_shape_[n]);
+    if (inputs.size() == 1) {
+      kernel_->Run(input, nullptr, nullptr, outputs[0], ws_, normalized_shape_, eps_);
+    } else {
+      CHECK_EQ(inputs.size(), 3u);
+      kernel_->Run(input, inputs[1], inputs[2], outputs[0], ws_, normalized_shape_, eps_);
+    }
+  }
+
+ private:
+  float eps_;
+  VecInt normalized_shape_;
+  std::shared_ptr<LayerNormKernel> kernel_;
+};
+
 // Normalize (shadow/operators/normalize_op.cpp:9-37): `p` default 2, `axis` default 1 (negative
 // values count from the end), `eps` default 1e-12.
 class NormalizeOp : public Operator {
@@ -344,6 +424,9 @@ class BatchNormOp : public Operator {
 
 REGISTER_OPERATOR(BatchNorm, BatchNormOp);
 REGISTER_OPERATOR(Normalize, NormalizeOp);
+REGISTER_OPERATOR(GroupNorm, GroupNormOp);
+REGISTER_OPERATOR(InstanceNorm, InstanceNormOp);
+REGISTER_OPERATOR(LayerNorm, LayerNormOp);
 REGISTER_OPERATOR(Eltwise, EltwiseOp);
 REGISTER_OPERATOR(Axpy, AxpyOp);
 REGISTER_OPERATOR(Input, InputOp);

@@ -196,6 +196,23 @@ def small_cases():
     cs.append(_case("normalize_extremes", "Normalize", {"p": 2.0, "axis": 1},
                     [np.array([[1e-30, 3e-25, -0.0, 0.0], [1e19, -3e18, 2.0, 1e-44], [4.0, 3.0, 0.0, -0.0]], np.float32)]))
     cs.append(_case("normalize_long_axis", "Normalize", {"p": 2.0, "axis": 1}, [normal(1265, (2, 5000, 3))]))
+    xg = normal(1270, (3, 12, 5, 7), 0.5, 2.0)
+    gs, gb = normal(1271, (12,), 1.0, 0.2), normal(1272, (12,), 0.0, 0.2)
+    cs.append(_case("group_norm_g1", "GroupNorm", {"group": 1}, [xg]))
+    cs.append(_case("group_norm_g4_affine", "GroupNorm", {"group": 4, "eps": float(np.float32(1e-3))}, [xg, gs, gb]))
+    cs.append(_case("group_norm_g12", "GroupNorm", {"group": 12}, [xg]))
+    cs.append(_case("group_norm_vec_rows", "GroupNorm", {"group": 2}, [normal(1273, (2, 8, 4, 4)), normal(1274, (8,)), normal(1275, (8,))]))
+    cs.append(_case("instance_norm", "InstanceNorm", {}, [xg]))
+    cs.append(_case("instance_norm_affine", "InstanceNorm", {}, [xg, gs, gb]))
+    xl = normal(1276, (4, 9, 130), -1.0, 3.0)
+    cs.append(_case("layer_norm_last", "LayerNorm", {"normalized_shape": [130]}, [xl]))
+    cs.append(_case("layer_norm_last_affine", "LayerNorm", {"normalized_shape": [130]}, [xl, normal(1277, (130,)), normal(1278, (130,))]))
+    cs.append(_case("layer_norm_two_dims", "LayerNorm", {"normalized_shape": [9, 130], "eps": float(np.float32(1e-6))},
+                    [xl, normal(1279, (9, 130)), normal(1280, (9, 130))]))
+    cs.append(_case("layer_norm_wide_row", "LayerNorm", {"normalized_shape": [4096]}, [normal(1281, (3, 4096))]))
+    cs.append(_case("layer_norm_long_row", "LayerNorm", {"normalized_shape": [40000]}, [normal(1282, (2, 40000), 2.0, 1.0)]))
+    cs.append(_case("layer_norm_constant_rows", "LayerNorm", {"normalized_shape": [16]},
+                    [np.tile(np.array([[3.5], [0.0], [-2.25]], np.float32), (1, 16))]))
     # ---- Softmax ----------------------------------------------------------------------------
     cs.append(_case("softmax_rows", "Softmax", {"axis": 1}, [normal(1100, (37, 129), 0.0, 3.0)]))
     cs.append(_case("softmax_rows_neg_axis", "Softmax", {"axis": -1}, [normal(1101, (5, 3, 64), 0.0, 3.0)]))
@@ -257,6 +274,15 @@ def run_port(case) -> np.ndarray:
         return orc.eltwise(x, a["operation"], a.get("coeff", []))
     if op == "Axpy":
         return orc.axpy(x[0], x[1], x[2])
+    if op == "GroupNorm":
+        return orc.group_norm(x[0], a.get("group", 1), x[1] if len(x) == 3 else None, x[2] if len(x) == 3 else None,
+                              a.get("eps", 1e-5))
+    if op == "InstanceNorm":
+        return orc.group_norm(x[0], x[0].shape[1], x[1] if len(x) == 3 else None, x[2] if len(x) == 3 else None,
+                              a.get("eps", 1e-5))
+    if op == "LayerNorm":
+        return orc.layer_norm(x[0], a["normalized_shape"], x[1] if len(x) == 3 else None, x[2] if len(x) == 3 else None,
+                              a.get("eps", 1e-5))
     if op == "Normalize":
         return orc.normalize(x[0], a.get("axis", 1), a.get("p", 2.0), a.get("eps", 1e-12))
     if op == "BatchNorm":
@@ -292,6 +318,8 @@ def tolerance_class(case) -> str:
         return "exact" if a.get("operation", 0) in (2, 3) else "rel"
     if op in ("Eltwise", "Axpy", "BatchNorm"):
         return "exact"
+    if op in ("GroupNorm", "InstanceNorm", "LayerNorm"):
+        return "rownorm"
     if op == "Normalize":   # p = 1, 2: only the order of the double additions differs from the reference
         return "ulp2" if a.get("p", 2.0) in (1.0, 2.0) else "rel"
     return "rel"
@@ -334,6 +362,14 @@ def run_cuda(case, device="cuda:0"):
         y = F.eltwise(x, a["operation"], a.get("coeff", []))
     elif op == "Axpy":
         y = F.axpy(x[0], x[1], x[2])
+    elif op == "GroupNorm":
+        y = F.group_norm(x[0], a.get("group", 1), x[1] if len(x) == 3 else None, x[2] if len(x) == 3 else None,
+                         a.get("eps", 1e-5))
+    elif op == "InstanceNorm":
+        y = F.instance_norm(x[0], x[1] if len(x) == 3 else None, x[2] if len(x) == 3 else None, a.get("eps", 1e-5))
+    elif op == "LayerNorm":
+        y = F.layer_norm(x[0], a["normalized_shape"], x[1] if len(x) == 3 else None, x[2] if len(x) == 3 else None,
+                         a.get("eps", 1e-5))
     elif op == "Normalize":
         y = F.normalize(x[0], a.get("axis", 1), a.get("p", 2.0), a.get("eps", 1e-12))
     elif op == "BatchNorm":
@@ -375,6 +411,32 @@ def assert_parity(case, got: np.ndarray, want: np.ndarray):
         g, w = got.astype(np.float64).ravel(), want.astype(np.float64).ravel()
         tol = 2 * np.spacing(np.abs(want.ravel()).astype(np.float32)).astype(np.float64) + np.abs(0.5 * x) * 2.0 ** -24
         assert np.all(np.abs(g - w) <= tol), "%s: |err| above 2 ulp + |x/2|*2^-24" % case["name"]
+    elif cls == "rownorm":
+        # mean and variance are double sums rounded to float; a different order of the additions can
+        # move either by one float ulp.  One ulp of the mean shifts every centred value of the row by
+        # that much ABSOLUTELY (x - mean cancels), so the bar is absolute per row:
+        # 2^-22 * max|x| / sqrt(var + eps) (times |scale|), plus 2^-22 relative.
+        x = case["inputs"][0].astype(np.float64)
+        a = case["args"]
+        if case["op"] == "LayerNorm":
+            inner = int(np.prod(a["normalized_shape"]))
+        else:
+            group = a.get("group", 1) if case["op"] == "GroupNorm" else x.shape[1]
+            inner = x.size // (x.shape[0] * group)
+        rows = x.reshape(-1, inner)
+        sd = np.sqrt(rows.var(axis=1) + a.get("eps", 1e-5))
+        row_tol = (2.0 ** -22) * np.abs(rows).max(axis=1) / sd
+        tol = np.repeat(row_tol, inner)
+        if len(case["inputs"]) == 3:
+            sc = np.abs(case["inputs"][1].astype(np.float64)).ravel()
+            if case["op"] == "LayerNorm":
+                tol = tol * np.tile(sc, x.size // sc.size)
+            else:
+                spatial = int(np.prod(x.shape[2:]))
+                tol = tol * np.tile(np.repeat(sc, spatial), x.shape[0])
+        g, w = got.astype(np.float64).ravel(), want.astype(np.float64).ravel()
+        assert np.all(np.abs(g - w) <= tol + (2.0 ** -22) * np.abs(w)), "%s: max excess %g" % (
+            case["name"], float(np.max(np.abs(g - w) - tol - (2.0 ** -22) * np.abs(w))))
     elif cls == "ulp2":
         d = orc.ulp_distance(got, want)
         assert int(d.max()) <= 2, "%s: max ulp %d" % (case["name"], int(d.max()))
