@@ -114,6 +114,17 @@ int sb200_binary_broadcast(const float* a, const int* a_shape, const float* b, c
 int sb200_scale_bias(const float* x, float* y, int64_t n, const float* scale, const float* bias,
                      int64_t scale_num, int64_t inner_num, void* stream);
 
+/* SSD-style L2 normalisation of x[batch, channels, spatial].  across_spatial != 0: one norm per
+ * sample, y = x * (1 / sqrt(sum(x*x) + eps)); else one norm per (sample, position) over the
+ * channels, y = x / (float)sqrt(sum(x*x) + eps) with the square root taken in double.  Squares are
+ * float products accumulated in double.  scale (may be NULL): one value when channel_shared != 0,
+ * else one per channel; multiplied in last.  It is read on the device, so no host copy of the
+ * shared scale is needed.  No scratch.
+ * Replaces SSDNormalizeKernelDefault<kGPU>::Run (shadow/operators/kernels/ssd_normalize.hpp:33-82):
+ * Blas::Square + BlasSasum/Mul per sample or Vision::SSDNormalize + BlasSscal / Vision::Scale. */
+int sb200_ssd_normalize(const float* x, float* y, int64_t batch, int64_t channels, int64_t spatial,
+                        int across_spatial, float eps, const float* scale, int channel_shared, void* stream);
+
 /* Row normalisation of x viewed as [rows, inner] (contiguous rows): mean = sum(x/inner),
  * v = x - mean, var = sum(v*v/inner), y = v / sqrt(var + eps); then, unless affine_mode is 0,
  * y*scale[k] + bias[k] with k = position in the row (affine_mode 1: LayerNorm) or the channel

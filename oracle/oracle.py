@@ -67,6 +67,7 @@ def port():
         L.orc_fill.argtypes = [i64, C.c_float, _FP]
         L.orc_eltwise.argtypes = [C.POINTER(_FP), C.c_int, _FP, i64, C.c_int, _FP]
         L.orc_axpy.argtypes = [_FP, _FP, _FP, i64, i64, _FP]
+        L.orc_ssd_normalize.argtypes = [_FP, i64, i64, i64, C.c_int, C.c_float, _FP, C.c_int, _FP, _FP]
         L.orc_row_norm.argtypes = [_FP, i64, i64, C.c_float, _FP, _FP, i64, i64, _FP]
         L.orc_normalize.argtypes = [_FP, i64, i64, i64, _FP, C.c_float, C.c_float, _FP]
         L.orc_batch_norm.argtypes = [_FP, i64, _FP, _FP, i64, i64, C.c_float, C.c_float, _FP]
@@ -221,6 +222,18 @@ def axpy(alpha, x, y) -> np.ndarray:
     out = np.empty_like(x)
     _ok(port().orc_axpy(_fp(alpha), _fp(x), _fp(y), alpha.size, inner, _fp(out)), "axpy")
     return out
+
+
+def ssd_normalize(x, scale=None, across_spatial: bool = True, channel_shared: bool = True, eps: float = 1e-5) -> np.ndarray:
+    """SSDNormalizeOp (shadow/operators/ssd_normalize_op.cpp:9-45)."""
+    x = _f32(x)
+    spatial = int(np.prod(x.shape[2:], dtype=np.int64))
+    val = np.empty(max(x.shape[0] * spatial, 1), np.float32)
+    y = np.empty_like(x)
+    sc = _f32(scale) if scale is not None else None
+    _ok(port().orc_ssd_normalize(_fp(x), x.shape[0], x.shape[1], spatial, int(across_spatial), np.float32(eps),
+                                 _fp(sc) if sc is not None else None, int(channel_shared), _fp(val), _fp(y)), "ssd_normalize")
+    return y
 
 
 def _row_norm(x, rows, inner, eps, scale, bias, scale_num, scale_inner):

@@ -20,20 +20,27 @@
 namespace sb200 {
 namespace {
 
-enum { kNormL1 = 1, kNormL2 = 2, kNormLp = 0 };
+// kSsdChannel / kSsdSpatial: SSDNormalize (sum of float squares in double; see sb200_ssd_normalize)
+enum { kNormL1 = 1, kNormL2 = 2, kNormLp = 0, kSsdChannel = 3, kSsdSpatial = 4 };
+enum { kScaleNone = 0, kScaleShared = 1, kScaleChannel = 2 };
+
+struct SsdScale {
+  const float* scale;      // one value (shared) or one per channel
+  FastDiv32 div_spatial;   // kSsdSpatial: channel of flattened position r is r / spatial
+};
 
 template <int MODE>
 __device__ __forceinline__ double norm_term(float v, float p) {
   const float a = fabsf(v);
   if (MODE == kNormL1) return static_cast<double>(a);
-  if (MODE == kNormL2) return static_cast<double>(__fmul_rn(a, a));
+  if (MODE == kNormL2 || MODE == kSsdChannel || MODE == kSsdSpatial) return static_cast<double>(__fmul_rn(a, a));
   return static_cast<double>(powf(a, p));
 }
 
-template <int MODE, int kT, int kU>
+template <int MODE, int kT, int kU, int SCALE>
 __global__ void __launch_bounds__(kT, 1024 / kT)
 normalize_plane_kernel(const float* x, float* y, int64_t outer, int dim, int64_t inner, int W, int G, int P,
-                       int64_t ntile, float p, float eps) {
+                       int64_t ntile, float p, float eps, const __grid_constant__ SsdScale ssd) {
   __shared__ double sm_acc[kT];
   const int t = threadIdx.x;
   const int sidx = t % W, pg = t / W;
@@ -66,12 +73,29 @@ normalize_plane_kernel(const float* x, float* y, int64_t outer, int dim, int64_t
   const int first = pl * G * W + sidx;
   double sum = 0.0;
   for (int k = 0; k < G; ++k) sum += sm_acc[first + k * W];
-  float val = static_cast<float>(sum);
-  if (MODE == kNormL2) val = __fsqrt_rn(val);
-  if (MODE == kNormLp) val = powf(val, __fdiv_rn(1.f, p));
-  const float d = (val < eps) ? eps : val;   // std::max(val, eps)
+  float d, factor = 0.f;
+  if (MODE == kSsdChannel) {
+    d = static_cast<float>(sqrt(sum + static_cast<double>(eps)));
+  } else if (MODE == kSsdSpatial) {
+    d = __fsqrt_rn(__fadd_rn(static_cast<float>(sum), eps));
+    factor = __fdiv_rn(1.f, d);
+  } else {
+    float val = static_cast<float>(sum);
+    if (MODE == kNormL2) val = __fsqrt_rn(val);
+    if (MODE == kNormLp) val = powf(val, __fdiv_rn(1.f, p));
+    d = (val < eps) ? eps : val;   // std::max(val, eps)
+  }
   const bool d_ok = (d >= 0x1p-60f) && (d <= 0x1p60f);
   const float rcp = __frcp_rn(d);
+  const float shared_scale = (SCALE == kScaleShared) ? __ldg(ssd.scale) : 1.f;
+  // row index r of the value -> output
+  auto finish = [&](float v, int r) {
+    float o = (MODE == kSsdSpatial) ? __fmul_rn(v, factor) : div_exact(v, d, rcp, d_ok);
+    if (SCALE == kScaleShared) o = __fmul_rn(o, shared_scale);
+    if (SCALE == kScaleChannel)
+      o = __fmul_rn(o, __ldg(ssd.scale + (MODE == kSsdSpatial ? ssd.div_spatial.div(static_cast<uint32_t>(r)) : static_cast<uint32_t>(r))));
+    return o;
+  };
   const float* q = xp;
   float* o = yp;
   int k = 0;
@@ -80,9 +104,43 @@ normalize_plane_kernel(const float* x, float* y, int64_t outer, int dim, int64_t
 #pragma unroll
     for (int u = 0; u < kU; ++u) v[u] = ld_stream(q + u * step);
 #pragma unroll
-    for (int u = 0; u < kU; ++u) st_stream(o + u * step, div_exact(v[u], d, rcp, d_ok));
+    for (int u = 0; u < kU; ++u) st_stream(o + u * step, finish(v[u], g + (k + u) * G));
   }
-  for (; k < cnt; ++k, q += step, o += step) st_stream(o, div_exact(ld_stream(q), d, rcp, d_ok));
+  for (; k < cnt; ++k, q += step, o += step) st_stream(o, finish(ld_stream(q), g + k * G));
+}
+
+struct PlaneGeo {
+  int64_t outer, inner, ntile;
+  int dim, W, G, P, T;
+  unsigned grid;
+};
+
+int plan_plane(int64_t outer, int64_t dim, int64_t inner, PlaneGeo* q) {
+  if (dim >= (1ll << 31)) return SB200_ERR_UNSUPPORTED;
+  q->outer = outer, q->inner = inner, q->dim = static_cast<int>(dim);
+  q->W = static_cast<int>(inner < 256 ? inner : 256);
+  q->ntile = (inner + q->W - 1) / q->W;
+  // 512-thread blocks when every thread still gets full batches of rows, else 256
+  q->T = (dim >= 256 && dim >= 16 * (512 / q->W)) ? 512 : 256;
+  // row groups: as many as leave each thread about 16 rows; the rest of the block packs planes
+  int G = q->T / q->W;
+  const int g16 = static_cast<int>((dim + 15) / 16);
+  if (G > g16) G = g16;
+  int P = q->T / (G * q->W);
+  if (P > outer) P = static_cast<int>(outer);
+  q->G = G, q->P = P;
+  const int64_t blocks = ((outer + P - 1) / P) * q->ntile;
+  if (blocks >= (1ll << 31)) return SB200_ERR_UNSUPPORTED;
+  q->grid = static_cast<unsigned>(blocks);
+  return SB200_OK;
+}
+
+template <int MODE, int SCALE>
+void launch_plane(const float* x, float* y, const PlaneGeo& q, float p, float eps, const SsdScale& ssd, cudaStream_t s) {
+  if (q.T == 512)
+    normalize_plane_kernel<MODE, 512, 16, SCALE><<<q.grid, 512, 0, s>>>(x, y, q.outer, q.dim, q.inner, q.W, q.G, q.P, q.ntile, p, eps, ssd);
+  else
+    normalize_plane_kernel<MODE, 256, 8, SCALE><<<q.grid, 256, 0, s>>>(x, y, q.outer, q.dim, q.inner, q.W, q.G, q.P, q.ntile, p, eps, ssd);
 }
 
 }  // namespace
@@ -98,26 +156,38 @@ extern "C" int sb200_normalize(const float* x, float* y, int64_t outer, int64_t 
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 3u) return SB200_ERR_BAD_ARGUMENT;
   if (dim >= (1ll << 31) || outer * dim > (1ll << 40) / inner) return SB200_ERR_UNSUPPORTED;
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  const int W = static_cast<int>(inner < 256 ? inner : 256);
-  const int64_t ntile = (inner + W - 1) / W;
-  // 512-thread blocks when every thread still gets full batches of rows, else 256
-  const int T = (dim >= 256 && dim >= 16 * (512 / W)) ? 512 : 256;
-  // row groups: as many as leave each thread about 16 rows; the rest of the block packs planes
-  int G = T / W;
-  const int g16 = static_cast<int>((dim + 15) / 16);
-  if (G > g16) G = g16;
-  int P = T / (G * W);
-  if (P > outer) P = static_cast<int>(outer);
-  const int64_t blocks = ((outer + P - 1) / P) * ntile;
-  if (blocks >= (1ll << 31)) return SB200_ERR_UNSUPPORTED;
-  const unsigned grid = static_cast<unsigned>(blocks);
-  const int d = static_cast<int>(dim);
-#define SB200_NORM(MODE)                                                                                       \
-  if (T == 512) normalize_plane_kernel<MODE, 512, 16><<<grid, 512, 0, s>>>(x, y, outer, d, inner, W, G, P, ntile, p, eps); \
-  else normalize_plane_kernel<MODE, 256, 8><<<grid, 256, 0, s>>>(x, y, outer, d, inner, W, G, P, ntile, p, eps);
-  if (p == 1.f) { SB200_NORM(kNormL1) }
-  else if (p == 2.f) { SB200_NORM(kNormL2) }
-  else { SB200_NORM(kNormLp) }
-#undef SB200_NORM
+  PlaneGeo geo;
+  const int rc = plan_plane(outer, dim, inner, &geo);
+  if (rc != SB200_OK) return rc;
+  const SsdScale none{nullptr, FastDiv32()};
+  if (p == 1.f) launch_plane<kNormL1, kScaleNone>(x, y, geo, p, eps, none, s);
+  else if (p == 2.f) launch_plane<kNormL2, kScaleNone>(x, y, geo, p, eps, none, s);
+  else launch_plane<kNormLp, kScaleNone>(x, y, geo, p, eps, none, s);
   return after_launch("sb200_normalize");
+}
+
+extern "C" int sb200_ssd_normalize(const float* x, float* y, int64_t batch, int64_t channels, int64_t spatial,
+                                   int across_spatial, float eps, const float* scale, int channel_shared, void* stream) {
+  if (batch < 0 || channels < 1 || spatial < 1) return SB200_ERR_BAD_ARGUMENT;
+  if (batch == 0) return SB200_OK;
+  if (x == nullptr || y == nullptr) return SB200_ERR_BAD_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(scale)) & 3u)
+    return SB200_ERR_BAD_ARGUMENT;
+  if (channels * spatial >= (1ll << 31)) return SB200_ERR_UNSUPPORTED;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  PlaneGeo geo;
+  // across_spatial: one norm per sample over all of [channels, spatial] (a row of the [batch, C*S]
+  // view); else one norm per (sample, position) over the channels
+  const int rc = across_spatial ? plan_plane(batch, channels * spatial, 1, &geo) : plan_plane(batch, channels, spatial, &geo);
+  if (rc != SB200_OK) return rc;
+  const SsdScale ssd{scale, FastDiv32(static_cast<uint32_t>(spatial))};
+  const int sm = scale == nullptr ? kScaleNone : (channel_shared ? kScaleShared : kScaleChannel);
+#define SB200_SSD(MODE)                                                                  \
+  if (sm == kScaleNone) launch_plane<MODE, kScaleNone>(x, y, geo, 2.f, eps, ssd, s);      \
+  else if (sm == kScaleShared) launch_plane<MODE, kScaleShared>(x, y, geo, 2.f, eps, ssd, s); \
+  else launch_plane<MODE, kScaleChannel>(x, y, geo, 2.f, eps, ssd, s);
+  if (across_spatial) { SB200_SSD(kSsdSpatial) }
+  else { SB200_SSD(kSsdChannel) }
+#undef SB200_SSD
+  return after_launch("sb200_ssd_normalize");
 }

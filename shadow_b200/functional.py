@@ -326,3 +326,24 @@ def instance_norm(x: torch.Tensor, scale: Optional[torch.Tensor] = None, bias: O
                   eps: float = 1e-5, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """InstanceNorm (shadow/operators/instance_norm_op.cpp:9-40): GroupNorm with one channel per group."""
     return group_norm(x, x.shape[1], scale, bias, eps, out)
+
+
+def ssd_normalize(x: torch.Tensor, scale: Optional[torch.Tensor] = None, across_spatial: bool = True,
+                  channel_shared: bool = True, eps: float = 1e-5, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """SSDNormalize (shadow/operators/ssd_normalize_op.cpp:9-45)."""
+    _chk(x, "x")
+    if x.dim() < 2:
+        raise ValueError("x needs a channel axis")
+    spatial = 1
+    for d in x.shape[2:]:
+        spatial *= d
+    if scale is not None:
+        _chk(scale, "scale")
+        if scale.numel() != (1 if channel_shared else x.shape[1]):
+            raise ValueError("scale must hold one value (channel_shared) or one per channel")
+    y = torch.empty_like(x) if out is None else _chk(out, "out")
+    capi.check(capi.lib().sb200_ssd_normalize(x.data_ptr(), y.data_ptr(), x.shape[0], x.shape[1], spatial,
+                                              1 if across_spatial else 0, eps,
+                                              scale.data_ptr() if scale is not None else None,
+                                              1 if channel_shared else 0, _stream()), "sb200_ssd_normalize")
+    return y

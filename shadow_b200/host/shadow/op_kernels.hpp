@@ -72,6 +72,13 @@ class AxpyKernel : public Kernel {
   virtual void Run(const BlobPtr& alpha, const BlobPtr& x, const BlobPtr& y, BlobPtr& output, Workspace* ws) = 0;
 };
 
+// shadow/operators/kernels/ssd_normalize.hpp:24-30
+class SSDNormalizeKernel : public Kernel {
+ public:
+  virtual void Run(const BlobPtr& input, const BlobPtr& scale, BlobPtr& output, Workspace* ws, bool across_spatial,
+                   bool channel_shared, float eps) = 0;
+};
+
 // shadow/operators/kernels/group_norm.hpp:30-37 (also used by InstanceNorm with group = channels)
 class GroupNormKernel : public Kernel {
  public:

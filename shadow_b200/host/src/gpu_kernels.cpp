@@ -181,6 +181,22 @@ class AxpyKernelB200 : public AxpyKernel {
   std::string kernel_type() const override { return "Default"; }
 };
 
+// One launch; the shared scale is read on the device (the reference copies it to the host first).
+class SSDNormalizeKernelB200 : public SSDNormalizeKernel {
+ public:
+  void Run(const BlobPtr& input, const BlobPtr& scale, BlobPtr& output, Workspace* ws, bool across_spatial,
+           bool channel_shared, float eps) override {
+    const int channel = input->shape(1);
+    if (scale != nullptr) CHECK_EQ(scale->count(), channel_shared ? 1 : channel);
+    expect_ok(sb200_ssd_normalize(input->data<float>(), output->mutable_data<float>(), input->shape(0), channel,
+                                  input->count(2), across_spatial ? 1 : 0, eps,
+                                  scale != nullptr ? scale->data<float>() : nullptr, channel_shared ? 1 : 0, stream_of(ws)),
+              "sb200_ssd_normalize");
+  }
+  DeviceType device_type() const override { return DeviceType::kGPU; }
+  std::string kernel_type() const override { return "Default"; }
+};
+
 // One fused launch and no temporary blobs (the reference grows the workspace by count + inner +
 // 2*rows floats and makes six launches).
 class GroupNormKernelB200 : public GroupNormKernel {
@@ -257,6 +273,7 @@ class BatchNormKernelB200 : public BatchNormKernel {
 
 REGISTER_OP_KERNEL_DEFAULT(BatchNormGPU, BatchNormKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(NormalizeGPU, NormalizeKernelB200);
+REGISTER_OP_KERNEL_DEFAULT(SSDNormalizeGPU, SSDNormalizeKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(GroupNormGPU, GroupNormKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(LayerNormGPU, LayerNormKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(EltwiseGPU, EltwiseKernelB200);

@@ -290,6 +290,32 @@ class AxpyOp : public Operator {
   std::shared_ptr<AxpyKernel> kernel_;
 };
 
+// SSDNormalize (shadow/operators/ssd_normalize_op.cpp:9-45): `across_spatial` default true,
+// `channel_shared` default true, `eps` default 1e-5; one input, or two (x, scale).
+class SSDNormalizeOp : public Operator {
+ public:
+  SSDNormalizeOp(const shadow::OpParam& op_param, Workspace* ws) : Operator(op_param, ws) {
+    across_spatial_ = get_single_argument<bool>("across_spatial", true);
+    channel_shared_ = get_single_argument<bool>("channel_shared", true);
+    eps_ = get_single_argument<float>("eps", 1e-5f);
+    kernel_ = kernel_for<SSDNormalizeKernel>(op_param, ws_);
+  }
+  void Run(const std::vector<BlobPtr>& inputs, std::vector<BlobPtr>& outputs) override {
+    outputs[0]->reshape(inputs[0]->shape());
+    if (inputs.size() == 1) {
+      kernel_->Run(inputs[0], nullptr, outputs[0], ws_, across_spatial_, channel_shared_, eps_);
+    } else {
+      CHECK_EQ(inputs.size(), 2u);
+      kernel_->Run(inputs[0], inputs[1], outputs[0], ws_, across_spatial_, channel_shared_, eps_);
+    }
+  }
+
+ private:
+  float eps_;
+  bool across_spatial_, channel_shared_;
+  std::shared_ptr<SSDNormalizeKernel> kernel_;
+};
+
 // GroupNorm (shadow/operators/group_norm_op.cpp:9-45): `group` default 1, `eps` default 1e-5; one
 // input, or three (x, per-channel scale, per-channel bias).
 class GroupNormOp : public Operator {
@@ -424,6 +450,7 @@ class BatchNormOp : public Operator {
 
 REGISTER_OPERATOR(BatchNorm, BatchNormOp);
 REGISTER_OPERATOR(Normalize, NormalizeOp);
+REGISTER_OPERATOR(SSDNormalize, SSDNormalizeOp);
 REGISTER_OPERATOR(GroupNorm, GroupNormOp);
 REGISTER_OPERATOR(InstanceNorm, InstanceNormOp);
 REGISTER_OPERATOR(LayerNorm, LayerNormOp);

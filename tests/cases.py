@@ -196,6 +196,18 @@ def small_cases():
     cs.append(_case("normalize_extremes", "Normalize", {"p": 2.0, "axis": 1},
                     [np.array([[1e-30, 3e-25, -0.0, 0.0], [1e19, -3e18, 2.0, 1e-44], [4.0, 3.0, 0.0, -0.0]], np.float32)]))
     cs.append(_case("normalize_long_axis", "Normalize", {"p": 2.0, "axis": 1}, [normal(1265, (2, 5000, 3))]))
+    xs = normal(1290, (3, 20, 5, 7))
+    cs.append(_case("ssd_normalize_defaults", "SSDNormalize", {}, [xs]))
+    cs.append(_case("ssd_normalize_across_shared", "SSDNormalize", {"across_spatial": True, "channel_shared": True},
+                    [xs, np.array([20.0], np.float32)]))
+    cs.append(_case("ssd_normalize_across_channel", "SSDNormalize", {"across_spatial": True, "channel_shared": False},
+                    [xs, uniform(1291, (20,), 0.5, 25.0)]))
+    cs.append(_case("ssd_normalize_position_channel", "SSDNormalize", {"across_spatial": False, "channel_shared": False,
+                                                                         "eps": float(np.float32(1e-10))},
+                    [xs, uniform(1292, (20,), 0.5, 25.0)]))
+    cs.append(_case("ssd_normalize_position_shared", "SSDNormalize", {"across_spatial": False, "channel_shared": True},
+                    [xs, np.array([0.5], np.float32)]))
+    cs.append(_case("ssd_normalize_position_noscale", "SSDNormalize", {"across_spatial": False}, [normal(1293, (2, 300, 38))]))
     xg = normal(1270, (3, 12, 5, 7), 0.5, 2.0)
     gs, gb = normal(1271, (12,), 1.0, 0.2), normal(1272, (12,), 0.0, 0.2)
     cs.append(_case("group_norm_g1", "GroupNorm", {"group": 1}, [xg]))
@@ -274,6 +286,9 @@ def run_port(case) -> np.ndarray:
         return orc.eltwise(x, a["operation"], a.get("coeff", []))
     if op == "Axpy":
         return orc.axpy(x[0], x[1], x[2])
+    if op == "SSDNormalize":
+        return orc.ssd_normalize(x[0], x[1] if len(x) == 2 else None, a.get("across_spatial", True),
+                                 a.get("channel_shared", True), a.get("eps", 1e-5))
     if op == "GroupNorm":
         return orc.group_norm(x[0], a.get("group", 1), x[1] if len(x) == 3 else None, x[2] if len(x) == 3 else None,
                               a.get("eps", 1e-5))
@@ -320,6 +335,8 @@ def tolerance_class(case) -> str:
         return "exact"
     if op in ("GroupNorm", "InstanceNorm", "LayerNorm"):
         return "rownorm"
+    if op == "SSDNormalize":   # only the order of the double additions differs from the reference
+        return "ulp2"
     if op == "Normalize":   # p = 1, 2: only the order of the double additions differs from the reference
         return "ulp2" if a.get("p", 2.0) in (1.0, 2.0) else "rel"
     return "rel"
@@ -362,6 +379,9 @@ def run_cuda(case, device="cuda:0"):
         y = F.eltwise(x, a["operation"], a.get("coeff", []))
     elif op == "Axpy":
         y = F.axpy(x[0], x[1], x[2])
+    elif op == "SSDNormalize":
+        y = F.ssd_normalize(x[0], x[1] if len(x) == 2 else None, a.get("across_spatial", True),
+                            a.get("channel_shared", True), a.get("eps", 1e-5))
     elif op == "GroupNorm":
         y = F.group_norm(x[0], a.get("group", 1), x[1] if len(x) == 3 else None, x[2] if len(x) == 3 else None,
                          a.get("eps", 1e-5))
