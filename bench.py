@@ -319,6 +319,18 @@ def per_op_sweep(torch, F, device, peak):
     x, y = torch.randn(512, 64, 56, 56, device=device), torch.empty(512, 64, 56, 56, device=device)
     mean, var = torch.randn(64, device=device), torch.rand(64, device=device) + 0.1
     bench("batch_norm[512,64,56,56]", lambda: F.batch_norm(x, mean, var, 1.0, 1e-5, out=y), 8 * x.numel() + 8 * 64)
+    gs, gb = torch.randn(64, device=device), torch.randn(64, device=device)
+    bench("group_norm_g8_affine[512,64,56,56]", lambda: F.group_norm(x, 8, gs, gb, 1e-5, out=y), 8 * x.numel() + 8 * 64)
+    bench("instance_norm[512,64,56,56]", lambda: F.instance_norm(x, None, None, 1e-5, out=y), 8 * x.numel())
+    del x, y
+    x, y = torch.randn(32768, 4096, device=device), torch.empty(32768, 4096, device=device)
+    ls, lb = torch.randn(4096, device=device), torch.randn(4096, device=device)
+    bench("layer_norm_affine[32768,4096]", lambda: F.layer_norm(x, [4096], ls, lb, 1e-5, out=y), 8 * x.numel() + 8 * 4096)
+    del x, y
+    x, y = torch.randn(128, 512, 38, 38, device=device), torch.empty(128, 512, 38, 38, device=device)
+    sc = torch.full((512,), 20.0, device=device)
+    bench("ssd_normalize_per_position[128,512,38,38]", lambda: F.ssd_normalize(x, sc, False, False, 1e-10, out=y),
+          8 * x.numel() + 4 * 512)
     return rows
 
 
