@@ -114,6 +114,43 @@ int sb200_binary_broadcast(const float* a, const int* a_shape, const float* b, c
 int sb200_scale_bias(const float* x, float* y, int64_t n, const float* scale, const float* bias,
                      int64_t scale_num, int64_t inner_num, void* stream);
 
+/* ---- data movement ---------------------------------------------------------------------------
+ * Concat / Stack: y viewed as [outer, sum(widths)] receives, side by side in every row, the rows of
+ * n_inputs tensors viewed as [outer, widths[k]] (Concat on `axis`: outer = count(0, axis),
+ * widths[k] = shape_k(axis) * count(axis + 1); Stack: widths[k] = count(axis) of an input).
+ * `inputs` and `widths` are HOST arrays.  One launch per 16 inputs instead of one per input.
+ * Replaces Vision::Concat<kGPU,float> / Vision::Stack<kGPU,float> called once per input
+ * (shadow/operators/kernels/concat.hpp:30-47, stack.hpp:29-42). */
+int sb200_concat(const float* const* inputs, const int64_t* widths, int n_inputs, float* y, int64_t outer,
+                 void* stream);
+
+/* Slice: the inverse - x viewed as [outer, sum(widths)] is split into n_outputs tensors
+ * [outer, widths[k]].  `outputs` and `widths` are HOST arrays.
+ * Replaces Vision::Slice<kGPU,float> called once per output (shadow/operators/kernels/slice.hpp:30-48). */
+int sb200_slice(const float* x, float* const* outputs, const int64_t* widths, int n_outputs, int64_t outer,
+                void* stream);
+
+/* Permute: y has shape in_shape[order[0]], in_shape[order[1]], ...; y[...] = x[...] with the axes
+ * reordered.  in_shape and order are HOST arrays; no index tables are uploaded.  x != y.
+ * Replaces Vision::Permute<kGPU,float>(in, count, num_axes, order, old_steps, new_steps, out, ctx)
+ * and the three temp blobs of PermuteKernelDefault::Run (shadow/operators/kernels/permute.hpp:27-58). */
+int sb200_permute(const float* x, float* y, const int* in_shape, const int* order, int num_axes, void* stream);
+
+/* Gather along one axis: x viewed as [outer, gather_dim, inner], y as [outer, num_indexes, inner],
+ * y[o, k, :] = x[o, indexes[k], :].  `indexes` is a DEVICE array of int.  An index outside
+ * [0, gather_dim) yields zeros (the reference reads out of bounds).
+ * Replaces Vision::Gather<kGPU,float>(in, indexes, num_indexes, gather_dim, inner_num, count, out, ctx)
+ * (shadow/operators/kernels/gather.hpp:24-33). */
+int sb200_gather(const float* x, const int* indexes, int64_t num_indexes, int64_t outer, int64_t gather_dim,
+                 int64_t inner, float* y, void* stream);
+
+/* Pad the last two axes: x viewed as [planes, in_h, in_w], paddings = {top, bottom, left, right}
+ * (HOST array; negative values crop), y as [planes, in_h + top + bottom, in_w + left + right];
+ * positions outside the input hold `value`.  One pass over y (the reference fills y, then copies rows).
+ * Replaces PadKernelDefault<kGPU>::Run = Blas::Set + Vision::Pad (shadow/operators/kernels/pad.hpp:27-44). */
+int sb200_pad(const float* x, float* y, int64_t planes, int in_h, int in_w, const int* paddings, float value,
+              void* stream);
+
 /* SSD-style L2 normalisation of x[batch, channels, spatial].  across_spatial != 0: one norm per
  * sample, y = x * (1 / sqrt(sum(x*x) + eps)); else one norm per (sample, position) over the
  * channels, y = x / (float)sqrt(sum(x*x) + eps) with the square root taken in double.  Squares are

@@ -67,6 +67,11 @@ def port():
         L.orc_fill.argtypes = [i64, C.c_float, _FP]
         L.orc_eltwise.argtypes = [C.POINTER(_FP), C.c_int, _FP, i64, C.c_int, _FP]
         L.orc_axpy.argtypes = [_FP, _FP, _FP, i64, i64, _FP]
+        IP = C.POINTER(C.c_int)
+        L.orc_copy_part.argtypes = [_FP, _FP, i64, i64, i64, i64, C.c_int]
+        L.orc_permute.argtypes = [_FP, IP, IP, C.c_int, _FP]
+        L.orc_gather.argtypes = [_FP, IP, i64, i64, i64, i64, _FP]
+        L.orc_pad.argtypes = [_FP, i64, i64, i64, i64, IP, C.c_float, _FP]
         L.orc_ssd_normalize.argtypes = [_FP, i64, i64, i64, C.c_int, C.c_float, _FP, C.c_int, _FP, _FP]
         L.orc_row_norm.argtypes = [_FP, i64, i64, C.c_float, _FP, _FP, i64, i64, _FP]
         L.orc_normalize.argtypes = [_FP, i64, i64, i64, _FP, C.c_float, C.c_float, _FP]
@@ -222,6 +227,90 @@ def axpy(alpha, x, y) -> np.ndarray:
     out = np.empty_like(x)
     _ok(port().orc_axpy(_fp(alpha), _fp(x), _fp(y), alpha.size, inner, _fp(out)), "axpy")
     return out
+
+
+def _ints(v):
+    a = np.ascontiguousarray(np.asarray(v, dtype=np.int32))
+    return a, a.ctypes.data_as(C.POINTER(C.c_int))
+
+
+def concat(inputs, axis: int = 1) -> np.ndarray:
+    """ConcatOp + ConcatKernelDefault (shadow/operators/concat_op.cpp:9-45, kernels/concat.hpp:30-47)."""
+    xs = [_f32(t) for t in inputs]
+    axis = axis + xs[0].ndim if axis < 0 else axis
+    shape = list(xs[0].shape)
+    shape[axis] = sum(t.shape[axis] for t in xs)
+    y = np.empty(shape, np.float32)
+    num = int(np.prod(shape[:axis], dtype=np.int64))
+    inner = int(np.prod(shape[axis + 1:], dtype=np.int64))
+    off = 0
+    for t in xs:
+        _ok(port().orc_copy_part(_fp(t), _fp(y), num, t.shape[axis] * inner, shape[axis] * inner, off * inner, 1), "concat")
+        off += t.shape[axis]
+    return y
+
+
+def stack(inputs, axis: int = 0) -> np.ndarray:
+    """StackOp + StackKernelDefault (shadow/operators/stack_op.cpp:9-40, kernels/stack.hpp:29-42)."""
+    xs = [_f32(t) for t in inputs]
+    axis = axis + xs[0].ndim + 1 if axis < 0 else axis
+    shape = list(xs[0].shape)
+    shape.insert(axis, len(xs))
+    y = np.empty(shape, np.float32)
+    num = int(np.prod(shape[:axis], dtype=np.int64))
+    size = int(np.prod(shape[axis + 1:], dtype=np.int64))
+    for n, t in enumerate(xs):
+        _ok(port().orc_copy_part(_fp(t), _fp(y), num, size, len(xs) * size, n * size, 1), "stack")
+    return y
+
+
+def slice_(x, axis: int, sizes) -> list:
+    """SliceOp + SliceKernelDefault (shadow/operators/slice_op.cpp:9-60, kernels/slice.hpp:30-48)."""
+    x = _f32(x)
+    axis = axis + x.ndim if axis < 0 else axis
+    num = int(np.prod(x.shape[:axis], dtype=np.int64))
+    inner = int(np.prod(x.shape[axis + 1:], dtype=np.int64))
+    outs, off = [], 0
+    for sz in sizes:
+        shape = list(x.shape)
+        shape[axis] = sz
+        y = np.empty(shape, np.float32)
+        _ok(port().orc_copy_part(_fp(y), _fp(x), num, sz * inner, x.shape[axis] * inner, off * inner, 0), "slice")
+        outs.append(y)
+        off += sz
+    return outs
+
+
+def permute(x, order) -> np.ndarray:
+    """PermuteOp (shadow/operators/permute_op.cpp:9-35)."""
+    x = _f32(x)
+    y = np.empty([x.shape[a] for a in order], np.float32)
+    sh, shp = _ints(x.shape)
+    od, odp = _ints(order)
+    _ok(port().orc_permute(_fp(x), shp, odp, x.ndim, _fp(y)), "permute")
+    return y
+
+
+def gather(x, indexes, axis: int = 0) -> np.ndarray:
+    """GatherOp (shadow/operators/gather_op.cpp:9-50)."""
+    x = _f32(x)
+    axis = axis + x.ndim if axis < 0 else axis
+    idx, idxp = _ints(indexes)
+    shape = list(x.shape)
+    shape[axis] = idx.size
+    y = np.empty(shape, np.float32)
+    _ok(port().orc_gather(_fp(x), idxp, idx.size, x.shape[axis], int(np.prod(x.shape[axis + 1:], dtype=np.int64)), y.size,
+                          _fp(y)), "gather")
+    return y
+
+
+def pad(x, paddings, value: float = 0.0) -> np.ndarray:
+    """PadOp (shadow/operators/pad_op.cpp:9-40)."""
+    x = _f32(x)
+    pd, pdp = _ints(paddings)
+    y = np.empty([x.shape[0], x.shape[1], x.shape[2] + pd[0] + pd[1], x.shape[3] + pd[2] + pd[3]], np.float32)
+    _ok(port().orc_pad(_fp(x), x.shape[0], x.shape[1], x.shape[2], x.shape[3], pdp, np.float32(value), _fp(y)), "pad")
+    return y
 
 
 def ssd_normalize(x, scale=None, across_spatial: bool = True, channel_shared: bool = True, eps: float = 1e-5) -> np.ndarray:

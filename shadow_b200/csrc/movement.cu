@@ -1,0 +1,327 @@
+// Data-movement operators: Concat / Stack (several tensors -> one), Slice (one -> several),
+// Permute, Gather, Pad.  Pure byte movement, HBM-bound: 8 algorithmic bytes per element (one
+// read, one write), except Pad whose border is write-only.
+//
+// Concat, Stack and Slice are one geometry: a "wide" tensor [outer, total] whose rows are the
+// concatenation of the rows of N "parts" [outer, width_k].  The reference launches one strided
+// copy per part; here one launch moves all parts (up to 16 per launch, longer lists chained).
+// Permute collapses dimensions that stay adjacent, then uses a shared-memory tile transpose when
+// what is left is a (batched) 2-D transpose and an index-arithmetic gather otherwise; no index
+// tables are uploaded (the reference copies three int arrays to the device per call).
+#include "common.cuh"
+
+namespace sb200 {
+namespace {
+
+constexpr int kThreads = 256;
+constexpr int kMaxParts = 16;
+constexpr int kMaxDims = SB200_MAX_AXES;
+
+struct Parts {
+  float* ptr[kMaxParts];        // part base pointers (const-cast for sources)
+  int64_t width[kMaxParts];     // elements per row of the part
+  int64_t offset[kMaxParts];    // column of the wide row where the part starts
+  int64_t first_block[kMaxParts + 1];   // wide kernel: prefix sum of blocks per part
+  int64_t tiles_per_row[kMaxParts];
+  int n;
+};
+
+// Wide parts: a block moves one tile of kTile units of one row of one part.  TO_WIDE: parts ->
+// wide tensor (Concat, Stack); else wide tensor -> parts (Slice).
+constexpr int kTileUnits = kThreads * 4;
+
+template <bool TO_WIDE, bool VEC>
+__global__ void __launch_bounds__(kThreads)
+parts_tile_kernel(const __grid_constant__ Parts p, float* wide, int64_t total) {
+  constexpr int W = VEC ? 4 : 1;
+  int k = 0;
+#pragma unroll
+  for (int i = 1; i < kMaxParts; ++i)
+    if (i < p.n && static_cast<int64_t>(blockIdx.x) >= p.first_block[i]) k = i;
+  const int64_t local = static_cast<int64_t>(blockIdx.x) - p.first_block[k];
+  const int64_t row = local / p.tiles_per_row[k], tile = local - row * p.tiles_per_row[k];
+  const int64_t width_u = p.width[k] / W;
+  float* part_row = p.ptr[k] + row * p.width[k];
+  float* wide_row = wide + row * total + p.offset[k];
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    const int64_t c = tile * kTileUnits + u * kThreads + threadIdx.x;
+    if (c >= width_u) continue;
+    if (VEC) {
+      if (TO_WIDE) st_stream(reinterpret_cast<float4*>(wide_row) + c, ld_stream(reinterpret_cast<const float4*>(part_row) + c));
+      else st_stream(reinterpret_cast<float4*>(part_row) + c, ld_stream(reinterpret_cast<const float4*>(wide_row) + c));
+    } else {
+      if (TO_WIDE) st_stream(wide_row + c, ld_stream(part_row + c));
+      else st_stream(part_row + c, ld_stream(wide_row + c));
+    }
+  }
+}
+
+// Narrow parts (rows of a few elements, e.g. a Stack on the last axis): one thread per element of
+// the wide tensor, the part found by a search over the (at most 16) offsets.
+template <bool TO_WIDE>
+__global__ void __launch_bounds__(kThreads)
+parts_elem_kernel(const __grid_constant__ Parts p, float* wide, int64_t total, int64_t count) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  if (i >= count) return;
+  const int64_t row = i / total, c = i - row * total;
+  int k = 0;
+#pragma unroll
+  for (int j = 1; j < kMaxParts; ++j)
+    if (j < p.n && c >= p.offset[j]) k = j;
+  if (c < p.offset[0] || c >= p.offset[k] + p.width[k]) return;   // a column owned by a part of another launch
+  float* q = p.ptr[k] + row * p.width[k] + (c - p.offset[k]);
+  if (TO_WIDE) wide[i] = *q;
+  else *q = wide[i];
+}
+
+template <bool TO_WIDE>
+int run_parts(float* const* parts, const int64_t* widths, int n_parts, float* wide, int64_t outer, cudaStream_t s,
+              const char* what) {
+  int64_t total = 0;
+  for (int k = 0; k < n_parts; ++k) {
+    if (parts[k] == nullptr || widths[k] < 1 || (reinterpret_cast<uintptr_t>(parts[k]) & 3u)) return SB200_ERR_BAD_ARGUMENT;
+    total += widths[k];
+  }
+  if (outer > 0 && total > (1ll << 40) / outer) return SB200_ERR_UNSUPPORTED;
+  int64_t offset = 0;
+  for (int first = 0; first < n_parts; first += kMaxParts) {
+    Parts p;
+    p.n = (n_parts - first < kMaxParts) ? n_parts - first : kMaxParts;
+    bool vec = aligned16(wide) && (total % 4 == 0);
+    int64_t max_width = 0, blocks = 0;
+    for (int k = 0; k < kMaxParts; ++k) {
+      const bool live = k < p.n;
+      p.ptr[k] = live ? parts[first + k] : nullptr;
+      p.width[k] = live ? widths[first + k] : 0;
+      p.offset[k] = offset;
+      if (live) {
+        vec = vec && aligned16(p.ptr[k]) && (p.width[k] % 4 == 0) && (offset % 4 == 0);
+        if (p.width[k] > max_width) max_width = p.width[k];
+        offset += p.width[k];
+      }
+    }
+    if (max_width >= 512) {
+      const int w = vec ? 4 : 1;
+      for (int k = 0; k < kMaxParts; ++k) {
+        p.first_block[k] = blocks;
+        p.tiles_per_row[k] = k < p.n ? (p.width[k] / w + kTileUnits - 1) / kTileUnits : 1;
+        if (k < p.n) blocks += p.tiles_per_row[k] * outer;
+      }
+      p.first_block[kMaxParts] = blocks;
+      if (blocks >= (1ll << 31)) return SB200_ERR_UNSUPPORTED;
+      if (vec) parts_tile_kernel<TO_WIDE, true><<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(p, wide, total);
+      else parts_tile_kernel<TO_WIDE, false><<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(p, wide, total);
+    } else {
+      const int64_t count = outer * total;
+      blocks = (count + kThreads - 1) / kThreads;
+      if (blocks >= (1ll << 31)) return SB200_ERR_UNSUPPORTED;
+      parts_elem_kernel<TO_WIDE><<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(p, wide, total, count);
+    }
+    const int rc = after_launch(what);
+    if (rc != SB200_OK) return rc;
+  }
+  return SB200_OK;
+}
+
+// ---- Permute ------------------------------------------------------------------------------------
+struct PermGeom {
+  int nd;
+  FastDiv32 out_div[kMaxDims];   // divisor = output step of dim j (elements)
+  uint32_t out_step[kMaxDims];
+  int64_t in_step[kMaxDims];     // input step of the dim that output dim j comes from
+};
+
+// out[i] = in[sum_j (i / out_step_j % ...) * in_step_j]: consecutive threads write consecutive
+// outputs; reads are as scattered as the permutation makes them.
+__global__ void __launch_bounds__(kThreads)
+permute_gather_kernel(const float* __restrict__ x, float* y, int64_t count, const __grid_constant__ PermGeom g) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  if (i >= count) return;
+  uint32_t rem = static_cast<uint32_t>(i);
+  int64_t src = 0;
+#pragma unroll
+  for (int j = 0; j < kMaxDims; ++j) {
+    if (j < g.nd) {
+      const uint32_t q = g.out_div[j].div(rem);
+      rem -= q * g.out_step[j];
+      src += static_cast<int64_t>(q) * g.in_step[j];
+    }
+  }
+  y[i] = __ldg(x + src);
+}
+
+// Batched transpose [B, R, C] -> [B, C, R] through a 32x33 shared tile: both the reads and the
+// writes are 128-byte row segments.
+__global__ void __launch_bounds__(256)
+transpose_tile_kernel(const float* __restrict__ x, float* y, int64_t R, int64_t C, int64_t tiles_c, int64_t tiles_rc) {
+  __shared__ float tile[32][33];
+  const int64_t b = blockIdx.x / tiles_rc, t = blockIdx.x - b * tiles_rc;
+  const int64_t tr = t / tiles_c, tc = t - tr * tiles_c;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const float* xb = x + b * R * C;
+  float* yb = y + b * R * C;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int64_t r = tr * 32 + ty + k * 8, c = tc * 32 + tx;
+    if (r < R && c < C) tile[ty + k * 8][tx] = ld_stream(xb + r * C + c);
+  }
+  __syncthreads();
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int64_t c = tc * 32 + ty + k * 8, r = tr * 32 + tx;
+    if (r < R && c < C) st_stream(yb + c * R + r, tile[tx][ty + k * 8]);
+  }
+}
+
+// ---- Gather, Pad --------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kThreads)
+gather_kernel(const float* __restrict__ x, const int* __restrict__ indexes, float* y, int64_t count, int64_t num_indexes,
+              int64_t gather_dim, int64_t inner) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  if (i >= count) return;
+  const int64_t r = i / inner, col = i - r * inner;   // r = outer * num_indexes + which index
+  const int64_t o = r / num_indexes, which = r - o * num_indexes;
+  const int64_t gi = __ldg(indexes + which);
+  // an index outside [0, gather_dim) would read outside the tensor: it yields 0 instead
+  y[i] = (gi >= 0 && gi < gather_dim) ? __ldg(x + (o * gather_dim + gi) * inner + col) : 0.f;
+}
+
+__global__ void __launch_bounds__(kThreads)
+pad_kernel(const float* __restrict__ x, float* y, int64_t count, int in_h, int in_w, int out_h, int out_w, int top,
+           int left, float value) {
+  const int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  if (i >= count) return;
+  const int64_t row = i / out_w;
+  const int ow = static_cast<int>(i - row * out_w);
+  const int64_t plane = row / out_h;
+  const int oh = static_cast<int>(row - plane * out_h);
+  const int h = oh - top, w = ow - left;
+  float v = value;
+  if (h >= 0 && h < in_h && w >= 0 && w < in_w) v = ld_stream(x + (plane * in_h + h) * in_w + w);
+  st_stream(y + i, v);
+}
+
+}  // namespace
+}  // namespace sb200
+
+using namespace sb200;
+
+extern "C" {
+
+int sb200_concat(const float* const* inputs, const int64_t* widths, int n_inputs, float* y, int64_t outer,
+                 void* stream) {
+  if (inputs == nullptr || widths == nullptr || n_inputs < 1 || n_inputs > 4096 || outer < 0) return SB200_ERR_BAD_ARGUMENT;
+  if (outer == 0) return SB200_OK;
+  if (y == nullptr || (reinterpret_cast<uintptr_t>(y) & 3u)) return SB200_ERR_BAD_ARGUMENT;
+  return run_parts<true>(const_cast<float* const*>(inputs), widths, n_inputs, y, outer, static_cast<cudaStream_t>(stream),
+                         "sb200_concat");
+}
+
+int sb200_slice(const float* x, float* const* outputs, const int64_t* widths, int n_outputs, int64_t outer,
+                void* stream) {
+  if (outputs == nullptr || widths == nullptr || n_outputs < 1 || n_outputs > 4096 || outer < 0) return SB200_ERR_BAD_ARGUMENT;
+  if (outer == 0) return SB200_OK;
+  if (x == nullptr || (reinterpret_cast<uintptr_t>(x) & 3u)) return SB200_ERR_BAD_ARGUMENT;
+  return run_parts<false>(outputs, widths, n_outputs, const_cast<float*>(x), outer, static_cast<cudaStream_t>(stream),
+                          "sb200_slice");
+}
+
+int sb200_permute(const float* x, float* y, const int* in_shape, const int* order, int num_axes, void* stream) {
+  if (in_shape == nullptr || order == nullptr || num_axes < 1 || num_axes > kMaxDims) return SB200_ERR_BAD_ARGUMENT;
+  bool seen[kMaxDims] = {false};
+  int64_t count = 1;
+  for (int d = 0; d < num_axes; ++d) {
+    if (order[d] < 0 || order[d] >= num_axes || seen[order[d]] || in_shape[d] < 0) return SB200_ERR_BAD_ARGUMENT;
+    seen[order[d]] = true;
+    count *= in_shape[d];
+    if (count >= (1ll << 32)) return SB200_ERR_UNSUPPORTED;   // 32-bit index arithmetic in the kernels
+  }
+  if (count == 0) return SB200_OK;
+  if (x == nullptr || y == nullptr || x == y) return SB200_ERR_BAD_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 3u) return SB200_ERR_BAD_ARGUMENT;
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  // input steps; then the output dims in order, dropping extent-1 dims and merging output dims
+  // whose input dims are adjacent and in order
+  int64_t in_step[kMaxDims];
+  int64_t step = 1;
+  for (int d = num_axes - 1; d >= 0; --d) { in_step[d] = step; step *= in_shape[d]; }
+  int64_t ext[kMaxDims], src_step[kMaxDims];
+  int nd = 0;
+  for (int j = 0; j < num_axes; ++j) {
+    const int d = order[j];
+    if (in_shape[d] == 1) continue;
+    if (nd > 0 && src_step[nd - 1] == in_step[d] * in_shape[d]) {   // previous output dim is the input dim just outside d
+      ext[nd - 1] *= in_shape[d];
+      src_step[nd - 1] = in_step[d];
+    } else {
+      ext[nd] = in_shape[d], src_step[nd] = in_step[d], ++nd;
+    }
+  }
+  if (nd <= 1) {   // the permutation keeps the memory order
+    cudaError_t e = cudaMemcpyAsync(y, x, static_cast<size_t>(count) * 4, cudaMemcpyDeviceToDevice, s);
+    if (e != cudaSuccess) return cuda_failure(e, "sb200_permute(copy)");
+    return SB200_OK;
+  }
+  // batched 2-D transpose: output dims (B,) C, R read with steps (R*C,) 1, C
+  const bool t2 = nd == 2 && src_step[0] == 1 && src_step[1] == ext[0];
+  const bool t3 = nd == 3 && src_step[0] == ext[1] * ext[2] && src_step[1] == 1 && src_step[2] == ext[1];
+  if (t2 || t3) {
+    const int64_t B = t3 ? ext[0] : 1, C = t3 ? ext[1] : ext[0], R = t3 ? ext[2] : ext[1];
+    const int64_t tiles_c = (C + 31) / 32, tiles_r = (R + 31) / 32;
+    const int64_t blocks = B * tiles_c * tiles_r;
+    if (blocks < (1ll << 31)) {
+      transpose_tile_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(x, y, R, C, tiles_c, tiles_c * tiles_r);
+      return after_launch("sb200_permute");
+    }
+  }
+  PermGeom g;
+  g.nd = nd;
+  int64_t ostep = 1;
+  for (int j = nd - 1; j >= 0; --j) {
+    g.out_step[j] = static_cast<uint32_t>(ostep);
+    g.out_div[j] = FastDiv32(static_cast<uint32_t>(ostep));
+    g.in_step[j] = src_step[j];
+    ostep *= ext[j];
+  }
+  for (int j = nd; j < kMaxDims; ++j) { g.out_step[j] = 1; g.out_div[j] = FastDiv32(1); g.in_step[j] = 0; }
+  const int64_t blocks = (count + kThreads - 1) / kThreads;
+  permute_gather_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(x, y, count, g);
+  return after_launch("sb200_permute");
+}
+
+int sb200_gather(const float* x, const int* indexes, int64_t num_indexes, int64_t outer, int64_t gather_dim,
+                 int64_t inner, float* y, void* stream) {
+  if (num_indexes < 1 || outer < 0 || gather_dim < 1 || inner < 1) return SB200_ERR_BAD_ARGUMENT;
+  if (outer == 0) return SB200_OK;
+  if (x == nullptr || y == nullptr || indexes == nullptr || x == y) return SB200_ERR_BAD_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y) | reinterpret_cast<uintptr_t>(indexes)) & 3u)
+    return SB200_ERR_BAD_ARGUMENT;
+  if (outer * num_indexes > (1ll << 40) / inner || outer * gather_dim > (1ll << 40) / inner) return SB200_ERR_UNSUPPORTED;
+  const int64_t count = outer * num_indexes * inner;
+  const int64_t blocks = (count + kThreads - 1) / kThreads;
+  if (blocks >= (1ll << 31)) return SB200_ERR_UNSUPPORTED;
+  gather_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(x, indexes, y, count, num_indexes,
+                                                                                                  gather_dim, inner);
+  return after_launch("sb200_gather");
+}
+
+int sb200_pad(const float* x, float* y, int64_t planes, int in_h, int in_w, const int* paddings, float value,
+              void* stream) {
+  if (paddings == nullptr || planes < 0 || in_h < 1 || in_w < 1) return SB200_ERR_BAD_ARGUMENT;
+  const int64_t out_h = static_cast<int64_t>(in_h) + paddings[0] + paddings[1];
+  const int64_t out_w = static_cast<int64_t>(in_w) + paddings[2] + paddings[3];
+  if (out_h < 1 || out_w < 1 || out_h >= (1ll << 31) || out_w >= (1ll << 31)) return SB200_ERR_BAD_ARGUMENT;
+  if (planes == 0) return SB200_OK;
+  if (x == nullptr || y == nullptr || x == y) return SB200_ERR_BAD_ARGUMENT;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 3u) return SB200_ERR_BAD_ARGUMENT;
+  if (planes > (1ll << 40) / (out_h * out_w)) return SB200_ERR_UNSUPPORTED;
+  const int64_t count = planes * out_h * out_w;
+  const int64_t blocks = (count + kThreads - 1) / kThreads;
+  if (blocks >= (1ll << 31)) return SB200_ERR_UNSUPPORTED;
+  pad_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      x, y, count, in_h, in_w, static_cast<int>(out_h), static_cast<int>(out_w), paddings[0], paddings[2], value);
+  return after_launch("sb200_pad");
+}
+
+}  // extern "C"

@@ -8,6 +8,7 @@ Inputs must be contiguous float32 CUDA tensors; there is no CPU path.
 """
 from __future__ import annotations
 
+import ctypes
 from typing import Optional, Sequence
 
 import torch
@@ -346,4 +347,106 @@ def ssd_normalize(x: torch.Tensor, scale: Optional[torch.Tensor] = None, across_
                                               1 if across_spatial else 0, eps,
                                               scale.data_ptr() if scale is not None else None,
                                               1 if channel_shared else 0, _stream()), "sb200_ssd_normalize")
+    return y
+
+
+def _prod(dims) -> int:
+    n = 1
+    for d in dims:
+        n *= int(d)
+    return n
+
+
+def concat(inputs, axis: int = 1, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Concat (shadow/operators/concat_op.cpp:9-45)."""
+    first = _chk(inputs[0], "inputs[0]")
+    axis = axis + first.dim() if axis < 0 else axis
+    shape = list(first.shape)
+    for t in inputs[1:]:
+        _chk(t, "input")
+        if t.dim() != first.dim() or any(t.shape[d] != shape[d] for d in range(first.dim()) if d != axis):
+            raise ValueError("inputs must agree except on the concat axis")
+        shape[axis] += t.shape[axis]
+    y = torch.empty(shape, dtype=torch.float32, device=first.device) if out is None else _chk(out, "out")
+    inner = _prod(first.shape[axis + 1:])
+    ptrs = (ctypes.c_void_p * len(inputs))(*[t.data_ptr() for t in inputs])
+    widths = (ctypes.c_int64 * len(inputs))(*[t.shape[axis] * inner for t in inputs])
+    capi.check(capi.lib().sb200_concat(ptrs, widths, len(inputs), y.data_ptr(), _prod(first.shape[:axis]), _stream()),
+               "sb200_concat")
+    return y
+
+
+def stack(inputs, axis: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Stack (shadow/operators/stack_op.cpp:9-40)."""
+    first = _chk(inputs[0], "inputs[0]")
+    axis = axis + first.dim() + 1 if axis < 0 else axis
+    for t in inputs[1:]:
+        if _chk(t, "input").shape != first.shape:
+            raise ValueError("inputs must share one shape")
+    shape = list(first.shape)
+    shape.insert(axis, len(inputs))
+    y = torch.empty(shape, dtype=torch.float32, device=first.device) if out is None else _chk(out, "out")
+    width = _prod(first.shape[axis:])
+    ptrs = (ctypes.c_void_p * len(inputs))(*[t.data_ptr() for t in inputs])
+    widths = (ctypes.c_int64 * len(inputs))(*[width] * len(inputs))
+    capi.check(capi.lib().sb200_concat(ptrs, widths, len(inputs), y.data_ptr(), _prod(first.shape[:axis]), _stream()),
+               "sb200_concat")
+    return y
+
+
+def slice_(x: torch.Tensor, axis: int, sizes) -> list:
+    """Slice (shadow/operators/slice_op.cpp:9-60): split `axis` into pieces of the given sizes."""
+    _chk(x, "x")
+    axis = axis + x.dim() if axis < 0 else axis
+    if sum(sizes) != x.shape[axis] or min(sizes) < 1:
+        raise ValueError("sizes must be positive and add up to the axis extent")
+    inner = _prod(x.shape[axis + 1:])
+    outs = []
+    for sz in sizes:
+        shape = list(x.shape)
+        shape[axis] = sz
+        outs.append(torch.empty(shape, dtype=torch.float32, device=x.device))
+    ptrs = (ctypes.c_void_p * len(outs))(*[t.data_ptr() for t in outs])
+    widths = (ctypes.c_int64 * len(outs))(*[sz * inner for sz in sizes])
+    capi.check(capi.lib().sb200_slice(x.data_ptr(), ptrs, widths, len(outs), _prod(x.shape[:axis]), _stream()), "sb200_slice")
+    return outs
+
+
+def permute(x: torch.Tensor, order, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Permute (shadow/operators/permute_op.cpp:9-35)."""
+    _chk(x, "x")
+    if sorted(order) != list(range(x.dim())):
+        raise ValueError("order must be a permutation of the axes")
+    shape = [x.shape[a] for a in order]
+    y = torch.empty(shape, dtype=torch.float32, device=x.device) if out is None else _chk(out, "out")
+    ishape = (ctypes.c_int * x.dim())(*x.shape)
+    iorder = (ctypes.c_int * x.dim())(*order)
+    capi.check(capi.lib().sb200_permute(x.data_ptr(), y.data_ptr(), ishape, iorder, x.dim(), _stream()), "sb200_permute")
+    return y
+
+
+def gather(x: torch.Tensor, indexes: torch.Tensor, axis: int = 0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Gather (shadow/operators/gather_op.cpp:9-50); `indexes` is a 1-d int32 device tensor."""
+    _chk(x, "x")
+    if indexes.dtype != torch.int32 or indexes.dim() != 1 or not indexes.is_cuda or not indexes.is_contiguous():
+        raise TypeError("indexes must be a contiguous 1-d int32 CUDA tensor")
+    axis = axis + x.dim() if axis < 0 else axis
+    shape = list(x.shape)
+    shape[axis] = indexes.numel()
+    y = torch.empty(shape, dtype=torch.float32, device=x.device) if out is None else _chk(out, "out")
+    capi.check(capi.lib().sb200_gather(x.data_ptr(), indexes.data_ptr(), indexes.numel(), _prod(x.shape[:axis]), x.shape[axis],
+                                       _prod(x.shape[axis + 1:]), y.data_ptr(), _stream()), "sb200_gather")
+    return y
+
+
+def pad(x: torch.Tensor, paddings, value: float = 0.0, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Pad (shadow/operators/pad_op.cpp:9-40): paddings = [top, bottom, left, right] on axes 2 and 3."""
+    _chk(x, "x")
+    if x.dim() != 4 or len(paddings) != 4:
+        raise ValueError("x must be 4-d and paddings hold four values")
+    shape = [x.shape[0], x.shape[1], x.shape[2] + paddings[0] + paddings[1], x.shape[3] + paddings[2] + paddings[3]]
+    y = torch.empty(shape, dtype=torch.float32, device=x.device) if out is None else _chk(out, "out")
+    pads = (ctypes.c_int * 4)(*paddings)
+    capi.check(capi.lib().sb200_pad(x.data_ptr(), y.data_ptr(), x.shape[0] * x.shape[1], x.shape[2], x.shape[3], pads, value,
+                                    _stream()), "sb200_pad")
     return y

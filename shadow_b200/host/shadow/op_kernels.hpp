@@ -72,6 +72,36 @@ class AxpyKernel : public Kernel {
   virtual void Run(const BlobPtr& alpha, const BlobPtr& x, const BlobPtr& y, BlobPtr& output, Workspace* ws) = 0;
 };
 
+// shadow/operators/kernels/concat.hpp:19-24, stack.hpp:18-23
+class ConcatKernel : public Kernel {
+ public:
+  virtual void Run(const std::vector<BlobPtr>& inputs, BlobPtr& output, Workspace* ws, int axis) = 0;
+};
+class StackKernel : public Kernel {
+ public:
+  virtual void Run(const std::vector<BlobPtr>& inputs, BlobPtr& output, Workspace* ws, int axis) = 0;
+};
+// shadow/operators/kernels/slice.hpp:19-25
+class SliceKernel : public Kernel {
+ public:
+  virtual void Run(const BlobPtr& input, std::vector<BlobPtr>& outputs, Workspace* ws, int axis) = 0;
+};
+// shadow/operators/kernels/permute.hpp:18-23
+class PermuteKernel : public Kernel {
+ public:
+  virtual void Run(const BlobPtr& input, BlobPtr& output, Workspace* ws, const VecInt& order_value) = 0;
+};
+// shadow/operators/kernels/gather.hpp:16-22
+class GatherKernel : public Kernel {
+ public:
+  virtual void Run(const BlobPtr& input, const BlobPtr& indexes, BlobPtr& output, Workspace* ws, int axis) = 0;
+};
+// shadow/operators/kernels/pad.hpp:18-24
+class PadKernel : public Kernel {
+ public:
+  virtual void Run(const BlobPtr& input, BlobPtr& output, Workspace* ws, const VecInt& paddings, float value) = 0;
+};
+
 // shadow/operators/kernels/ssd_normalize.hpp:24-30
 class SSDNormalizeKernel : public Kernel {
  public:

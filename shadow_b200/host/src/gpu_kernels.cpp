@@ -181,6 +181,95 @@ class AxpyKernelB200 : public AxpyKernel {
   std::string kernel_type() const override { return "Default"; }
 };
 
+// ---- data movement: one launch moves every part (the reference launches once per input/output)
+class ConcatKernelB200 : public ConcatKernel {
+ public:
+  void Run(const std::vector<BlobPtr>& inputs, BlobPtr& output, Workspace* ws, int axis) override {
+    std::vector<const float*> ptrs;
+    std::vector<int64_t> widths;
+    const int64_t inner = output->count(axis + 1);
+    for (const auto& in : inputs) {
+      ptrs.push_back(in->data<float>());
+      widths.push_back(in->shape(axis) * inner);
+    }
+    expect_ok(sb200_concat(ptrs.data(), widths.data(), static_cast<int>(ptrs.size()), output->mutable_data<float>(),
+                           output->count(0, axis), stream_of(ws)),
+              "sb200_concat");
+  }
+  DeviceType device_type() const override { return DeviceType::kGPU; }
+  std::string kernel_type() const override { return "Default"; }
+};
+
+class StackKernelB200 : public StackKernel {
+ public:
+  void Run(const std::vector<BlobPtr>& inputs, BlobPtr& output, Workspace* ws, int axis) override {
+    std::vector<const float*> ptrs;
+    const int64_t size = output->count(axis + 1);
+    for (const auto& in : inputs) ptrs.push_back(in->data<float>());
+    std::vector<int64_t> widths(ptrs.size(), size);
+    expect_ok(sb200_concat(ptrs.data(), widths.data(), static_cast<int>(ptrs.size()), output->mutable_data<float>(),
+                           output->count(0, axis), stream_of(ws)),
+              "sb200_concat");
+  }
+  DeviceType device_type() const override { return DeviceType::kGPU; }
+  std::string kernel_type() const override { return "Default"; }
+};
+
+class SliceKernelB200 : public SliceKernel {
+ public:
+  void Run(const BlobPtr& input, std::vector<BlobPtr>& outputs, Workspace* ws, int axis) override {
+    std::vector<float*> ptrs;
+    std::vector<int64_t> widths;
+    const int64_t inner = input->count(axis + 1);
+    for (auto& out : outputs) {
+      ptrs.push_back(out->mutable_data<float>());
+      widths.push_back(out->shape(axis) * inner);
+    }
+    expect_ok(sb200_slice(input->data<float>(), ptrs.data(), widths.data(), static_cast<int>(ptrs.size()),
+                          input->count(0, axis), stream_of(ws)),
+              "sb200_slice");
+  }
+  DeviceType device_type() const override { return DeviceType::kGPU; }
+  std::string kernel_type() const override { return "Default"; }
+};
+
+class PermuteKernelB200 : public PermuteKernel {
+ public:
+  // shapes and order stay on the host: no temporary blobs
+  void Run(const BlobPtr& input, BlobPtr& output, Workspace* ws, const VecInt& order_value) override {
+    expect_ok(sb200_permute(input->data<float>(), output->mutable_data<float>(), input->shape().data(), order_value.data(),
+                            input->num_axes(), stream_of(ws)),
+              "sb200_permute");
+  }
+  DeviceType device_type() const override { return DeviceType::kGPU; }
+  std::string kernel_type() const override { return "Default"; }
+};
+
+class GatherKernelB200 : public GatherKernel {
+ public:
+  void Run(const BlobPtr& input, const BlobPtr& indexes, BlobPtr& output, Workspace* ws, int axis) override {
+    expect_ok(sb200_gather(input->data<float>(), indexes->data<int>(), indexes->count(), input->count(0, axis),
+                           input->shape(axis), input->count(axis + 1), output->mutable_data<float>(), stream_of(ws)),
+              "sb200_gather");
+  }
+  DeviceType device_type() const override { return DeviceType::kGPU; }
+  std::string kernel_type() const override { return "Default"; }
+};
+
+class PadKernelB200 : public PadKernel {
+ public:
+  void Run(const BlobPtr& input, BlobPtr& output, Workspace* ws, const VecInt& paddings, float value) override {
+    CHECK_EQ(input->num_axes(), 4);
+    CHECK_EQ(paddings.size(), 4u);
+    expect_ok(sb200_pad(input->data<float>(), output->mutable_data<float>(),
+                        static_cast<int64_t>(input->shape(0)) * input->shape(1), input->shape(2), input->shape(3),
+                        paddings.data(), value, stream_of(ws)),
+              "sb200_pad");
+  }
+  DeviceType device_type() const override { return DeviceType::kGPU; }
+  std::string kernel_type() const override { return "Default"; }
+};
+
 // One launch; the shared scale is read on the device (the reference copies it to the host first).
 class SSDNormalizeKernelB200 : public SSDNormalizeKernel {
  public:
@@ -273,6 +362,12 @@ class BatchNormKernelB200 : public BatchNormKernel {
 
 REGISTER_OP_KERNEL_DEFAULT(BatchNormGPU, BatchNormKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(NormalizeGPU, NormalizeKernelB200);
+REGISTER_OP_KERNEL_DEFAULT(ConcatGPU, ConcatKernelB200);
+REGISTER_OP_KERNEL_DEFAULT(StackGPU, StackKernelB200);
+REGISTER_OP_KERNEL_DEFAULT(SliceGPU, SliceKernelB200);
+REGISTER_OP_KERNEL_DEFAULT(PermuteGPU, PermuteKernelB200);
+REGISTER_OP_KERNEL_DEFAULT(GatherGPU, GatherKernelB200);
+REGISTER_OP_KERNEL_DEFAULT(PadGPU, PadKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(SSDNormalizeGPU, SSDNormalizeKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(GroupNormGPU, GroupNormKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(LayerNormGPU, LayerNormKernelB200);

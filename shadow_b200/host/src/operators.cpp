@@ -290,6 +290,331 @@ class AxpyOp : public Operator {
   std::shared_ptr<AxpyKernel> kernel_;
 };
 
+// ---- zero-copy shape operators: the output aliases the input's memory (Blob::share_data) --------
+// Reshape (shadow/operators/reshape_op.cpp:9-80): the dims [axis, axis + num_axes) of the input are
+// replaced by `shape`, where 0 keeps the input's extent at that position and one -1 is inferred.
+class ReshapeOp : public Operator {
+ public:
+  ReshapeOp(const shadow::OpParam& op_param, Workspace* ws) : Operator(op_param, ws) {
+    axis_ = get_single_argument<int>("axis", 0);
+    num_axes_ = get_single_argument<int>("num_axes", -1);
+    CHECK_GE(num_axes_, -1);
+    shape_ = get_repeated_argument<int>("shape");
+  }
+  void Run(const std::vector<BlobPtr>& inputs, std::vector<BlobPtr>& outputs) override {
+    const auto& input = inputs[0];
+    auto& output = outputs[0];
+    CHECK_NE(input, output);
+    const int start = input->canonical_index(axis_);
+    CHECK_GE(start, 0);
+    CHECK_LT(start, input->num_axes());
+    const int end = num_axes_ == -1 ? input->num_axes() : start + num_axes_;
+    CHECK_LE(end, input->num_axes());
+    VecInt out_shape;
+    for (int d = 0; d < start; ++d) out_shape.push_back(input->shape(d));
+    int inferred = -1;
+    long long known = 1;
+    for (size_t k = 0; k < shape_.size(); ++k) {
+      int dim = shape_[k];
+      if (dim == 0) {
+        CHECK_GT(input->num_axes(), start + static_cast<int>(k));
+        dim = input->shape(start + static_cast<int>(k));
+      }
+      if (dim == -1) {
+        CHECK_EQ(inferred, -1);
+        inferred = start + static_cast<int>(k);
+      } else {
+        known *= dim;
+      }
+      out_shape.push_back(dim);
+    }
+    for (int d = end; d < input->num_axes(); ++d) out_shape.push_back(input->shape(d));
+    if (inferred >= 0) {
+      known *= input->count(0, start);
+      known *= input->count(end);
+      CHECK_EQ(0, input->count() % known);
+      out_shape[inferred] = static_cast<int>(input->count() / known);
+    }
+    output->share_data(input->data<void>(), out_shape);
+    CHECK_EQ(output->count(), input->count());
+  }
+
+ private:
+  int axis_, num_axes_;
+  VecInt shape_;
+};
+
+// Flatten (shadow/operators/flatten_op.cpp:9-45): dims [axis, end_axis] become one; `axis` default 1,
+// `end_axis` default -1 = last.
+class FlattenOp : public Operator {
+ public:
+  FlattenOp(const shadow::OpParam& op_param, Workspace* ws) : Operator(op_param, ws) {
+    axis_ = get_single_argument<int>("axis", 1);
+    CHECK_GE(axis_, 0);
+    end_axis_ = get_single_argument<int>("end_axis", -1);
+  }
+  void Run(const std::vector<BlobPtr>& inputs, std::vector<BlobPtr>& outputs) override {
+    const auto& input = inputs[0];
+    auto& output = outputs[0];
+    CHECK_NE(input, output);
+    const int n = input->num_axes();
+    if (end_axis_ == -1) end_axis_ = n - 1;
+    CHECK_LT(end_axis_, n);
+    CHECK_LE(axis_, end_axis_);
+    VecInt out_shape;
+    for (int d = 0; d < axis_; ++d) out_shape.push_back(input->shape(d));
+    out_shape.push_back(input->count(axis_, end_axis_ + 1));
+    for (int d = end_axis_ + 1; d < n; ++d) out_shape.push_back(input->shape(d));
+    output->share_data(input->data<void>(), out_shape);
+    CHECK_EQ(output->count(), input->count());
+  }
+
+ private:
+  int axis_, end_axis_;
+};
+
+// Squeeze (shadow/operators/squeeze_op.cpp:9-55): drops the listed axes (each must have extent 1),
+// or every extent-1 axis when `axes` is empty.
+class SqueezeOp : public Operator {
+ public:
+  SqueezeOp(const shadow::OpParam& op_param, Workspace* ws) : Operator(op_param, ws) {
+    axes_ = get_repeated_argument<int>("axes");
+  }
+  void Run(const std::vector<BlobPtr>& inputs, std::vector<BlobPtr>& outputs) override {
+    const auto& input = inputs[0];
+    auto& output = outputs[0];
+    CHECK_NE(input, output);
+    VecInt out_shape;
+    for (int n = 0; n < input->num_axes(); ++n) {
+      const int dim = input->shape(n);
+      const bool listed = std::find(axes_.begin(), axes_.end(), n) != axes_.end();
+      if (axes_.empty()) {
+        if (dim > 1) out_shape.push_back(dim);
+        else CHECK_EQ(dim, 1);
+      } else if (listed) {
+        CHECK_EQ(dim, 1);
+      } else {
+        out_shape.push_back(dim);
+      }
+    }
+    output->share_data(input->data<void>(), out_shape);
+    CHECK_EQ(output->count(), input->count());
+  }
+
+ private:
+  VecInt axes_;
+};
+
+// Unsqueeze (shadow/operators/unsqueeze_op.cpp:9-45): inserts extent-1 axes at the listed output
+// positions (negative positions count from the end of the output).
+class UnsqueezeOp : public Operator {
+ public:
+  UnsqueezeOp(const shadow::OpParam& op_param, Workspace* ws) : Operator(op_param, ws) {
+    axes_ = get_repeated_argument<int>("axes");
+  }
+  void Run(const std::vector<BlobPtr>& inputs, std::vector<BlobPtr>& outputs) override {
+    const auto& input = inputs[0];
+    auto& output = outputs[0];
+    CHECK_NE(input, output);
+    const int n = input->num_axes();
+    VecInt out_shape(n + axes_.size(), 0);
+    for (int axis : axes_) out_shape[axis < 0 ? axis + n + 1 : axis] = 1;
+    int d = 0;
+    for (auto& dim : out_shape)
+      if (dim == 0) dim = input->shape(d++);
+    CHECK_EQ(d, n);
+    output->share_data(input->data<void>(), out_shape);
+    CHECK_EQ(output->count(), input->count());
+  }
+
+ private:
+  VecInt axes_;
+};
+
+// ---- data movement -------------------------------------------------------------------------------
+// Concat (shadow/operators/concat_op.cpp:9-45): `axis` default 1; inputs agree on every other axis.
+class ConcatOp : public Operator {
+ public:
+  ConcatOp(const shadow::OpParam& op_param, Workspace* ws) : Operator(op_param, ws) {
+    axis_ = get_single_argument<int>("axis", 1);
+    kernel_ = kernel_for<ConcatKernel>(op_param, ws_);
+  }
+  void Run(const std::vector<BlobPtr>& inputs, std::vector<BlobPtr>& outputs) override {
+    CHECK_GE(inputs.size(), 2u);
+    axis_ = inputs[0]->canonical_index(axis_);
+    auto shape = inputs[0]->shape();
+    const int n = inputs[0]->num_axes();
+    for (size_t k = 1; k < inputs.size(); ++k) {
+      CHECK_EQ(n, inputs[k]->num_axes()) << "Inputs must have the same axes!";
+      for (int d = 0; d < n; ++d)
+        if (d != axis_) CHECK_EQ(shape[d], inputs[k]->shape(d)) << "Inputs must have the same shape, except at concat_axis!";
+      shape[axis_] += inputs[k]->shape(axis_);
+    }
+    outputs[0]->reshape(shape);
+    kernel_->Run(inputs, outputs[0], ws_, axis_);
+  }
+
+ private:
+  int axis_;
+  std::shared_ptr<ConcatKernel> kernel_;
+};
+
+// Slice (shadow/operators/slice_op.cpp:9-60): `axis` default 1; `slice_point` lists the cut
+// positions (strictly increasing); without it the axis is split evenly over the outputs.
+class SliceOp : public Operator {
+ public:
+  SliceOp(const shadow::OpParam& op_param, Workspace* ws) : Operator(op_param, ws) {
+    axis_ = get_single_argument<int>("axis", 1);
+    slice_point_ = get_repeated_argument<int>("slice_point");
+    kernel_ = kernel_for<SliceKernel>(op_param, ws_);
+  }
+  void Run(const std::vector<BlobPtr>& inputs, std::vector<BlobPtr>& outputs) override {
+    CHECK_GE(outputs.size(), 2u);
+    const auto& input = inputs[0];
+    axis_ = input->canonical_index(axis_);
+    const int pieces = static_cast<int>(outputs.size()), extent = input->shape(axis_);
+    VecInt sizes;
+    if (slice_point_.empty()) {
+      CHECK_EQ(extent % pieces, 0);
+      sizes.assign(pieces, extent / pieces);
+    } else {
+      CHECK_EQ(static_cast<int>(slice_point_.size()), pieces - 1);
+      int prev = 0;
+      for (int point : slice_point_) {
+        CHECK_GT(point, prev);
+        sizes.push_back(point - prev);
+        prev = point;
+      }
+      CHECK_GT(extent, prev);
+      sizes.push_back(extent - prev);
+    }
+    int total = 0;
+    auto shape = input->shape();
+    for (int k = 0; k < pieces; ++k) {
+      shape[axis_] = sizes[k];
+      outputs[k]->reshape(shape);
+      total += outputs[k]->count();
+    }
+    CHECK_EQ(total, input->count());
+    kernel_->Run(input, outputs, ws_, axis_);
+  }
+
+ private:
+  int axis_;
+  VecInt slice_point_;
+  std::shared_ptr<SliceKernel> kernel_;
+};
+
+// Stack (shadow/operators/stack_op.cpp:9-40): a new axis of extent #inputs at `axis` (default 0,
+// negative values count from the end of the output).
+class StackOp : public Operator {
+ public:
+  StackOp(const shadow::OpParam& op_param, Workspace* ws) : Operator(op_param, ws) {
+    axis_ = get_single_argument<int>("axis", 0);
+    kernel_ = kernel_for<StackKernel>(op_param, ws_);
+  }
+  void Run(const std::vector<BlobPtr>& inputs, std::vector<BlobPtr>& outputs) override {
+    CHECK_GE(inputs.size(), 2u);
+    const int n = inputs[0]->num_axes();
+    CHECK(axis_ >= -(n + 1) && axis_ < n + 1) << "axis out of bound.";
+    if (axis_ < 0) axis_ += n + 1;
+    auto shape = inputs[0]->shape();
+    shape.insert(shape.begin() + axis_, static_cast<int>(inputs.size()));
+    outputs[0]->reshape(shape);
+    kernel_->Run(inputs, outputs[0], ws_, axis_);
+  }
+
+ private:
+  int axis_;
+  std::shared_ptr<StackKernel> kernel_;
+};
+
+// Permute (shadow/operators/permute_op.cpp:9-35): `order` lists, per output axis, the input axis.
+class PermuteOp : public Operator {
+ public:
+  PermuteOp(const shadow::OpParam& op_param, Workspace* ws) : Operator(op_param, ws) {
+    order_ = get_repeated_argument<int>("order");
+    kernel_ = kernel_for<PermuteKernel>(op_param, ws_);
+  }
+  void Run(const std::vector<BlobPtr>& inputs, std::vector<BlobPtr>& outputs) override {
+    const auto& input = inputs[0];
+    CHECK_NE(input, outputs[0]);
+    CHECK_EQ(input->num_axes(), static_cast<int>(order_.size()));
+    VecInt shape;
+    for (int axis : order_) shape.push_back(input->shape(axis));
+    outputs[0]->reshape(shape);
+    kernel_->Run(input, outputs[0], ws_, order_);
+  }
+
+ private:
+  VecInt order_;
+  std::shared_ptr<PermuteKernel> kernel_;
+};
+
+// Gather (shadow/operators/gather_op.cpp:9-50): `axis` default 0; the indexes come from the
+// `indexes` argument (uploaded into a temporary int blob) or from a second, 1-d int input.
+class GatherOp : public Operator {
+ public:
+  GatherOp(const shadow::OpParam& op_param, Workspace* ws) : Operator(op_param, ws) {
+    axis_ = get_single_argument<int>("axis", 0);
+    indexes_ = get_repeated_argument<int>("indexes");
+    kernel_ = kernel_for<GatherKernel>(op_param, ws_);
+  }
+  void Run(const std::vector<BlobPtr>& inputs, std::vector<BlobPtr>& outputs) override {
+    const auto& input = inputs[0];
+    CHECK_NE(input, outputs[0]);
+    axis_ = input->canonical_index(axis_);
+    BlobPtr indexes;
+    if (indexes_.empty()) {
+      CHECK_EQ(inputs.size(), 2u);
+      indexes = inputs[1];
+      CHECK_EQ(indexes->num_axes(), 1);
+    } else {
+      const int n = static_cast<int>(indexes_.size());
+      ws_->GrowTempBuffer(n * sizeof(int));
+      indexes = ws_->CreateTempBlob({n}, DataType::kI32);
+      indexes->set_data<int>(indexes_.data(), indexes->count());
+    }
+    const int n = indexes->count();
+    CHECK_GT(n, 0);
+    auto shape = input->shape();
+    shape[axis_] = n;
+    outputs[0]->reshape(shape);
+    kernel_->Run(input, indexes, outputs[0], ws_, axis_);
+  }
+
+ private:
+  int axis_;
+  VecInt indexes_;
+  std::shared_ptr<GatherKernel> kernel_;
+};
+
+// Pad (shadow/operators/pad_op.cpp:9-40): `paddings` = [top, bottom, left, right] on axes 2 and 3,
+// `value` default 0.
+class PadOp : public Operator {
+ public:
+  PadOp(const shadow::OpParam& op_param, Workspace* ws) : Operator(op_param, ws) {
+    paddings_ = get_repeated_argument<int>("paddings");
+    CHECK_EQ(paddings_.size(), 4u);
+    value_ = get_single_argument<float>("value", 0);
+    kernel_ = kernel_for<PadKernel>(op_param, ws_);
+  }
+  void Run(const std::vector<BlobPtr>& inputs, std::vector<BlobPtr>& outputs) override {
+    const auto& input = inputs[0];
+    CHECK_NE(input, outputs[0]);
+    auto shape = input->shape();
+    shape[2] = input->shape(2) + paddings_[0] + paddings_[1];
+    shape[3] = input->shape(3) + paddings_[2] + paddings_[3];
+    outputs[0]->reshape(shape);
+    kernel_->Run(input, outputs[0], ws_, paddings_, value_);
+  }
+
+ private:
+  float value_;
+  VecInt paddings_;
+  std::shared_ptr<PadKernel> kernel_;
+};
+
 // SSDNormalize (shadow/operators/ssd_normalize_op.cpp:9-45): `across_spatial` default true,
 // `channel_shared` default true, `eps` default 1e-5; one input, or two (x, scale).
 class SSDNormalizeOp : public Operator {
@@ -450,6 +775,16 @@ class BatchNormOp : public Operator {
 
 REGISTER_OPERATOR(BatchNorm, BatchNormOp);
 REGISTER_OPERATOR(Normalize, NormalizeOp);
+REGISTER_OPERATOR(Reshape, ReshapeOp);
+REGISTER_OPERATOR(Flatten, FlattenOp);
+REGISTER_OPERATOR(Squeeze, SqueezeOp);
+REGISTER_OPERATOR(Unsqueeze, UnsqueezeOp);
+REGISTER_OPERATOR(Concat, ConcatOp);
+REGISTER_OPERATOR(Slice, SliceOp);
+REGISTER_OPERATOR(Stack, StackOp);
+REGISTER_OPERATOR(Permute, PermuteOp);
+REGISTER_OPERATOR(Gather, GatherOp);
+REGISTER_OPERATOR(Pad, PadOp);
 REGISTER_OPERATOR(SSDNormalize, SSDNormalizeOp);
 REGISTER_OPERATOR(GroupNorm, GroupNormOp);
 REGISTER_OPERATOR(InstanceNorm, InstanceNormOp);

@@ -40,8 +40,11 @@ def normal(seed, shape, mean=0.0, std=1.0):
     return rng(seed).normal(mean, std, size=shape).astype(np.float32)
 
 
-def _case(name, op, args, inputs):
-    return {"name": name, "op": op, "args": args, "inputs": [np.ascontiguousarray(x, np.float32) for x in inputs]}
+def _case(name, op, args, inputs, n_tops=1):
+    c = {"name": name, "op": op, "args": args, "inputs": [np.ascontiguousarray(x, np.float32) for x in inputs]}
+    if n_tops != 1:
+        c["n_tops"] = n_tops   # several outputs: results are compared flattened, one after another
+    return c
 
 
 def special_pairs():
@@ -196,6 +199,41 @@ def small_cases():
     cs.append(_case("normalize_extremes", "Normalize", {"p": 2.0, "axis": 1},
                     [np.array([[1e-30, 3e-25, -0.0, 0.0], [1e19, -3e18, 2.0, 1e-44], [4.0, 3.0, 0.0, -0.0]], np.float32)]))
     cs.append(_case("normalize_long_axis", "Normalize", {"p": 2.0, "axis": 1}, [normal(1265, (2, 5000, 3))]))
+    # ---- shape and data-movement operators (bit-exact byte movement) --------------------------
+    xm = normal(1300, (2, 6, 5, 4))
+    cs.append(_case("reshape_infer", "Reshape", {"shape": [0, -1, 10]}, [xm]))
+    cs.append(_case("reshape_sub_range", "Reshape", {"axis": 1, "num_axes": 2, "shape": [3, 10]}, [xm]))
+    cs.append(_case("flatten_default", "Flatten", {}, [xm]))
+    cs.append(_case("flatten_range", "Flatten", {"axis": 0, "end_axis": 1}, [xm]))
+    cs.append(_case("squeeze_all", "Squeeze", {}, [normal(1301, (1, 3, 1, 5))]))
+    cs.append(_case("squeeze_listed", "Squeeze", {"axes": [2]}, [normal(1301, (1, 3, 1, 5))]))
+    cs.append(_case("unsqueeze", "Unsqueeze", {"axes": [0, -1]}, [normal(1302, (3, 5))]))
+    cs.append(_case("concat_axis1", "Concat", {"axis": 1}, [xm, normal(1303, (2, 1, 5, 4)), normal(1304, (2, 9, 5, 4))]))
+    cs.append(_case("concat_last_axis_narrow", "Concat", {"axis": -1}, [normal(1305, (7, 3, 4)), normal(1306, (7, 3, 2))]))
+    cs.append(_case("concat_axis0_wide", "Concat", {"axis": 0}, [normal(1307, (3, 700)), normal(1308, (2, 700))]))
+    cs.append(_case("concat_wide_unaligned", "Concat", {"axis": 1}, [normal(1309, (3, 601)), normal(1310, (3, 515))]))
+    cs.append(_case("concat_20_inputs", "Concat", {"axis": 1}, [normal(1320 + k, (2, 1 + k % 3, 3)) for k in range(20)]))
+    cs.append(_case("stack_axis0", "Stack", {"axis": 0}, [normal(1340, (4, 5)), normal(1341, (4, 5)), normal(1342, (4, 5))]))
+    cs.append(_case("stack_last", "Stack", {"axis": -1}, [normal(1343, (4, 5)), normal(1344, (4, 5))]))
+    cs.append(_case("stack_mid_wide", "Stack", {"axis": 1}, [normal(1345, (2, 3, 256)), normal(1346, (2, 3, 256))]))
+    cs.append(_case("slice_even", "Slice", {"axis": 1}, [xm], n_tops=3))
+    cs.append(_case("slice_points", "Slice", {"axis": 2, "slice_point": [1, 4]}, [xm], n_tops=3))
+    cs.append(_case("slice_axis0_wide", "Slice", {"axis": 0, "slice_point": [2]}, [normal(1347, (5, 800))], n_tops=2))
+    cs.append(_case("permute_nchw_nhwc", "Permute", {"order": [0, 2, 3, 1]}, [normal(1350, (2, 37, 5, 9))]))
+    cs.append(_case("permute_nhwc_nchw", "Permute", {"order": [0, 3, 1, 2]}, [normal(1351, (2, 5, 9, 37))]))
+    cs.append(_case("permute_transpose_2d", "Permute", {"order": [1, 0]}, [normal(1352, (70, 33))]))
+    cs.append(_case("permute_general", "Permute", {"order": [2, 0, 3, 1]}, [normal(1353, (3, 4, 5, 6))]))
+    cs.append(_case("permute_identity", "Permute", {"order": [0, 1, 2]}, [normal(1354, (3, 4, 5))]))
+    cs.append(_case("permute_unit_dims", "Permute", {"order": [1, 0, 3, 2]}, [normal(1355, (1, 8, 1, 6))]))
+    cs.append(_case("permute_5d", "Permute", {"order": [4, 1, 0, 3, 2]}, [normal(1356, (2, 3, 4, 5, 6))]))
+    cs.append(_case("gather_axis0", "Gather", {"axis": 0, "indexes": [3, 0, 0, 2]}, [normal(1360, (5, 7))]))
+    cs.append(_case("gather_axis1", "Gather", {"axis": 1, "indexes": [5, 1]}, [xm]))
+    cs.append(_case("gather_last", "Gather", {"axis": -1, "indexes": [3, 3, 0]}, [xm]))
+    cs.append(_case("pad_grow", "Pad", {"paddings": [1, 2, 3, 0], "value": 2.5}, [xm]))
+    cs.append(_case("pad_zero_value_default", "Pad", {"paddings": [0, 0, 2, 2]}, [xm]))
+    cs.append(_case("pad_crop", "Pad", {"paddings": [-1, -2, -1, 0]}, [xm]))
+    cs.append(_case("pad_mixed", "Pad", {"paddings": [2, -1, -2, 3], "value": -1.0}, [xm]))
+    cs.append(_case("pad_none", "Pad", {"paddings": [0, 0, 0, 0]}, [xm]))
     xs = normal(1290, (3, 20, 5, 7))
     cs.append(_case("ssd_normalize_defaults", "SSDNormalize", {}, [xs]))
     cs.append(_case("ssd_normalize_across_shared", "SSDNormalize", {"across_spatial": True, "channel_shared": True},
@@ -251,6 +289,62 @@ def small_cases():
     return cs
 
 
+def _shape_op(op, a, shape):
+    """Output shape of the zero-copy operators (Reshape / Flatten / Squeeze / Unsqueeze)."""
+    shape = list(shape)
+    n = len(shape)
+    if op == "Reshape":
+        start = a.get("axis", 0) % n
+        end = n if a.get("num_axes", -1) == -1 else start + a["num_axes"]
+        new = [shape[start + k] if d == 0 else d for k, d in enumerate(a["shape"])]
+        out = shape[:start] + new + shape[end:]
+        if -1 in out:
+            known = int(np.prod([d for d in out if d != -1], dtype=np.int64))
+            out[out.index(-1)] = int(np.prod(shape, dtype=np.int64)) // known
+        return out
+    if op == "Flatten":
+        ax, end = a.get("axis", 1), a.get("end_axis", -1)
+        end = n - 1 if end == -1 else end
+        return shape[:ax] + [int(np.prod(shape[ax:end + 1], dtype=np.int64))] + shape[end + 1:]
+    if op == "Squeeze":
+        axes = a.get("axes", [])
+        return [d for k, d in enumerate(shape) if (d > 1 if not axes else k not in axes)]
+    axes = [ax + n + 1 if ax < 0 else ax for ax in a["axes"]]
+    out, it = [], iter(shape)
+    for k in range(n + len(axes)):
+        out.append(1 if k in axes else next(it))
+    return out
+
+
+def _slice_sizes(a, extent, n_tops):
+    pts = a.get("slice_point", [])
+    if not pts:
+        return [extent // n_tops] * n_tops
+    edges = [0] + list(pts) + [extent]
+    return [edges[k + 1] - edges[k] for k in range(n_tops)]
+
+
+def _movement(case, impl, back):
+    """Shape / data-movement cases on `impl` (the oracle module or shadow_b200.functional); `back`
+    turns a result into a numpy array.  None when the case is not one of these operators."""
+    op, a, x = case["op"], dict(case["args"]), case["_args_inputs"] if "_args_inputs" in case else case["inputs"]
+    if op in ("Reshape", "Flatten", "Squeeze", "Unsqueeze"):
+        return back(x[0]).reshape(_shape_op(op, a, case["inputs"][0].shape))
+    if op == "Concat":
+        return back(impl.concat(x, a.get("axis", 1)))
+    if op == "Stack":
+        return back(impl.stack(x, a.get("axis", 0)))
+    if op == "Slice":
+        axis = a.get("axis", 1) % case["inputs"][0].ndim
+        outs = impl.slice_(x[0], axis, _slice_sizes(a, case["inputs"][0].shape[axis], case["n_tops"]))
+        return np.concatenate([back(o).ravel() for o in outs])
+    if op == "Permute":
+        return back(impl.permute(x[0], a["order"]))
+    if op == "Pad":
+        return back(impl.pad(x[0], a["paddings"], a.get("value", 0.0)))
+    return None
+
+
 def run_port(case) -> np.ndarray:
     """Evaluate a case with the C restatement + Python front-end rules."""
     op, a, x = case["op"], dict(case["args"]), case["inputs"]
@@ -286,6 +380,9 @@ def run_port(case) -> np.ndarray:
         return orc.eltwise(x, a["operation"], a.get("coeff", []))
     if op == "Axpy":
         return orc.axpy(x[0], x[1], x[2])
+    mv = _movement(case, orc, lambda v: v)
+    if mv is not None:
+        return mv
     if op == "SSDNormalize":
         return orc.ssd_normalize(x[0], x[1] if len(x) == 2 else None, a.get("across_spatial", True),
                                  a.get("channel_shared", True), a.get("eps", 1e-5))
@@ -298,6 +395,8 @@ def run_port(case) -> np.ndarray:
     if op == "LayerNorm":
         return orc.layer_norm(x[0], a["normalized_shape"], x[1] if len(x) == 3 else None, x[2] if len(x) == 3 else None,
                               a.get("eps", 1e-5))
+    if op == "Gather":
+        return orc.gather(x[0], a["indexes"], a.get("axis", 0))
     if op == "Normalize":
         return orc.normalize(x[0], a.get("axis", 1), a.get("p", 2.0), a.get("eps", 1e-12))
     if op == "BatchNorm":
@@ -311,10 +410,17 @@ def run_net(library, case, backend="Native", device_id=0):
     names = ["in%d" % i for i in range(len(case["inputs"]))]
     net = Net(library, case["name"])
     net.input({n: (x.shape if x.ndim else (1,)) for n, x in zip(names, case["inputs"])})
-    net.op(case["op"], names, ["out"], **case["args"])
-    net.load(backend, device_id=device_id, out_blobs=["out"])
+    n_tops = case.get("n_tops", 1)
+    if n_tops == 1:
+        net.op(case["op"], names, ["out"], **case["args"])
+        net.load(backend, device_id=device_id, out_blobs=["out"])
+        net.forward(dict(zip(names, case["inputs"])))
+        return net.blob("out")
+    tops = ["out%d" % k for k in range(n_tops)]       # several outputs: returned flattened, one after another
+    net.op(case["op"], names, tops, **case["args"])
+    net.load(backend, device_id=device_id, out_blobs=tops)
     net.forward(dict(zip(names, case["inputs"])))
-    return net.blob("out")
+    return np.concatenate([net.blob(t).ravel() for t in tops])
 
 
 def tolerance_class(case) -> str:
@@ -331,7 +437,8 @@ def tolerance_class(case) -> str:
         return "exact"
     if op == "Reduce":
         return "exact" if a.get("operation", 0) in (2, 3) else "rel"
-    if op in ("Eltwise", "Axpy", "BatchNorm"):
+    if op in ("Eltwise", "Axpy", "BatchNorm", "Reshape", "Flatten", "Squeeze", "Unsqueeze", "Concat", "Stack", "Slice",
+              "Permute", "Gather", "Pad"):
         return "exact"
     if op in ("GroupNorm", "InstanceNorm", "LayerNorm"):
         return "rownorm"
@@ -379,6 +486,11 @@ def run_cuda(case, device="cuda:0"):
         y = F.eltwise(x, a["operation"], a.get("coeff", []))
     elif op == "Axpy":
         y = F.axpy(x[0], x[1], x[2])
+    elif op in ("Reshape", "Flatten", "Squeeze", "Unsqueeze", "Concat", "Stack", "Slice", "Permute", "Pad"):
+        torch.cuda.synchronize()
+        return _movement(dict(case, _args_inputs=x), F, lambda t: t.cpu().numpy())
+    elif op == "Gather":
+        y = F.gather(x[0], torch.tensor(a["indexes"], dtype=torch.int32, device=device), a.get("axis", 0))
     elif op == "SSDNormalize":
         y = F.ssd_normalize(x[0], x[1] if len(x) == 2 else None, a.get("across_spatial", True),
                             a.get("channel_shared", True), a.get("eps", 1e-5))
