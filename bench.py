@@ -331,6 +331,19 @@ def per_op_sweep(torch, F, device, peak):
     sc = torch.full((512,), 20.0, device=device)
     bench("ssd_normalize_per_position[128,512,38,38]", lambda: F.ssd_normalize(x, sc, False, False, 1e-10, out=y),
           8 * x.numel() + 4 * 512)
+    del x, y
+    x = torch.randn(128, 256, 56, 56, device=device)
+    y = torch.empty(128, 56, 56, 256, device=device)
+    bench("permute_nchw_to_nhwc[128,256,56,56]", lambda: F.permute(x, [0, 2, 3, 1], out=y), 8 * x.numel())
+    y2 = torch.empty(56, 128, 56, 256, device=device)
+    bench("permute_general_2031[128,256,56,56]", lambda: F.permute(x, [2, 0, 3, 1], out=y2), 8 * x.numel())
+    del x, y, y2
+    a, b = torch.randn(256, 64, 56, 56, device=device), torch.randn(256, 96, 56, 56, device=device)
+    y = torch.empty(256, 160, 56, 56, device=device)
+    bench("concat_axis1[256,64+96,56,56]", lambda: F.concat([a, b], 1, out=y), 8 * y.numel())
+    del a, b
+    yp = torch.empty(256, 160, 58, 58, device=device)
+    bench("pad_1_1_1_1[256,160,56,56]", lambda: F.pad(y, [1, 1, 1, 1], 0.0, out=yp), 4 * (y.numel() + yp.numel()))
     return rows
 
 
