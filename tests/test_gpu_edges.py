@@ -131,3 +131,80 @@ def test_in_place_calls():
     cases.assert_parity({"name": "s", "op": "Softmax", "args": {"axis": 1}, "inputs": [x]}, t.cpu().numpy(), orc.softmax(x, 1))
     t = dev(x); F.softmax(t, 3, out=t)
     cases.assert_parity({"name": "s", "op": "Softmax", "args": {"axis": 3}, "inputs": [x]}, t.cpu().numpy(), orc.softmax(x, 3))
+
+
+@pytest.mark.parametrize("offset", [0, 1, 2, 3])
+def test_unaligned_normalisation_family(offset):
+    """BatchNorm / Normalize / SSDNormalize / LayerNorm / GroupNorm / InstanceNorm on sub-buffers that
+    start 0-3 floats past a 16-byte boundary: scalar fall-backs, guard bands intact."""
+    from shadow_b200 import functional as F
+    torch = _torch()
+    x = cases.normal(80 + offset, (3, 8, 4, 6), 0.3, 1.5)
+    dx, _ = _view(x, offset)
+    dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).cuda()   # noqa: E731
+    g, bt = cases.normal(81, (8,), 1.0, 0.2), cases.normal(82, (8,))
+    var = cases.uniform(83, (8,), 0.2, 2.0)
+
+    def check(name, op, args, inputs, fn):
+        want = cases.run_port({"name": name, "op": op, "args": args, "inputs": inputs})
+        out, buf = _view(np.zeros_like(x), (offset + 1) % 4)
+        fn(out)
+        torch.cuda.synchronize()
+        cases.assert_parity({"name": name, "op": op, "args": args, "inputs": inputs}, out.cpu().numpy(), want)
+        assert _guards_intact(buf, (offset + 1) % 4, x.size), name
+
+    check("bn", "BatchNorm", {}, [x, bt, var], lambda o: F.batch_norm(dx, dev(bt), dev(var), 1.0, 1e-5, out=o))
+    for p in (1.0, 2.0):
+        for axis in (1, 3):
+            check("norm", "Normalize", {"p": p, "axis": axis}, [x], lambda o: F.normalize(dx, axis, p, 1e-12, out=o))
+    check("ssd_pos", "SSDNormalize", {"across_spatial": False, "channel_shared": False}, [x, g],
+          lambda o: F.ssd_normalize(dx, dev(g), False, False, 1e-5, out=o))
+    check("ssd_all", "SSDNormalize", {"across_spatial": True, "channel_shared": True}, [x, g[:1]],
+          lambda o: F.ssd_normalize(dx, dev(g[:1]), True, True, 1e-5, out=o))
+    check("gn", "GroupNorm", {"group": 2}, [x, g, bt], lambda o: F.group_norm(dx, 2, dev(g), dev(bt), 1e-5, out=o))
+    check("in", "InstanceNorm", {}, [x], lambda o: F.instance_norm(dx, None, None, 1e-5, out=o))
+    ls, lb = cases.normal(84, (4, 6)), cases.normal(85, (4, 6))
+    check("ln", "LayerNorm", {"normalized_shape": [4, 6]}, [x, ls, lb],
+          lambda o: F.layer_norm(dx, [4, 6], dev(ls), dev(lb), 1e-5, out=o))
+
+
+@pytest.mark.parametrize("offset", [0, 1, 2])
+def test_unaligned_data_movement(offset):
+    from shadow_b200 import functional as F
+    torch = _torch()
+    a, b = cases.normal(90, (3, 5, 8, 12)), cases.normal(91, (3, 2, 8, 12))
+    da, _ = _view(a, offset)
+    db, _ = _view(b, (offset + 2) % 4)
+    want = np.concatenate([a, b], 1)
+    out, buf = _view(np.zeros_like(want), offset)
+    F.concat([da, db], 1, out=out)
+    assert orc.bit_equal(out.cpu().numpy(), want) and _guards_intact(buf, offset, want.size)
+    wide_a, wide_b = cases.normal(92, (2, 1000)), cases.normal(93, (2, 600))
+    dwa, _ = _view(wide_a, offset)
+    dwb, _ = _view(wide_b, 0)
+    want = np.concatenate([wide_a, wide_b], 1)
+    out, buf = _view(np.zeros_like(want), offset)
+    F.concat([dwa, dwb], 1, out=out)                                  # tile kernel, scalar units when offset != 0
+    assert orc.bit_equal(out.cpu().numpy(), want) and _guards_intact(buf, offset, want.size)
+    pieces = F.slice_(out, 1, [1000, 600])
+    assert orc.bit_equal(pieces[0].cpu().numpy(), wide_a) and orc.bit_equal(pieces[1].cpu().numpy(), wide_b)
+    want = a.transpose(0, 2, 3, 1)
+    out, buf = _view(np.zeros(want.shape, np.float32), offset)
+    F.permute(da, [0, 2, 3, 1], out=out)
+    assert orc.bit_equal(out.cpu().numpy(), np.ascontiguousarray(want)) and _guards_intact(buf, offset, want.size)
+    want = a.transpose(3, 1, 0, 2)
+    out, buf = _view(np.zeros(want.shape, np.float32), offset)
+    F.permute(da, [3, 1, 0, 2], out=out)
+    assert orc.bit_equal(out.cpu().numpy(), np.ascontiguousarray(want)) and _guards_intact(buf, offset, want.size)
+    want = np.pad(a, ((0, 0), (0, 0), (2, 1), (0, 3)), constant_values=-7.0)
+    out, buf = _view(np.zeros(want.shape, np.float32), offset)
+    F.pad(da, [2, 1, 0, 3], -7.0, out=out)
+    assert orc.bit_equal(out.cpu().numpy(), want) and _guards_intact(buf, offset, want.size)
+    idx = torch.tensor([4, 0, 4, 1], dtype=torch.int32, device="cuda")
+    want = a[:, [4, 0, 4, 1]]
+    out, buf = _view(np.zeros(want.shape, np.float32), offset)
+    F.gather(da, idx, 1, out=out)
+    assert orc.bit_equal(out.cpu().numpy(), np.ascontiguousarray(want)) and _guards_intact(buf, offset, want.size)
+    bad = torch.tensor([9, -1, 2], dtype=torch.int32, device="cuda")   # out-of-range indexes give zeros, no fault
+    got = F.gather(da, bad, 1).cpu().numpy()
+    assert np.all(got[:, 0] == 0) and np.all(got[:, 1] == 0) and orc.bit_equal(got[:, 2], a[:, 2])
