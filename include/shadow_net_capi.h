@@ -60,6 +60,10 @@ int SHADOW_CAPI(net_add_op)(void* net, const char* type, const char* name, int n
 int SHADOW_CAPI(net_add_blob)(void* net, const char* name, int ndim, const int* shape,
                               const float* data);
 
+/* Replace the NetParam under construction by the one IO::ReadProtoFromText parses from `text`
+ * (the protobuf-free model text format, shadow/util/io.hpp:47-52, shadow/core/parser.cpp:1844-1917). */
+int SHADOW_CAPI(net_parse_text)(void* net, const char* text);
+
 /* Network::LoadXModel with backend arguments backend_type / device_id and the net
  * argument out_blob (mandatory, shadow/backends/native/native.cpp:186-188). */
 int SHADOW_CAPI(net_load)(void* net, const char* backend_type, int device_id, int n_out,

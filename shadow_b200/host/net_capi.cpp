@@ -9,6 +9,7 @@
 
 #include "core/helper.hpp"
 #include "core/network.hpp"
+#include "util/io.hpp"
 
 #include <cstring>
 #include <exception>
@@ -122,6 +123,16 @@ int SHADOW_CAPI(net_add_blob)(void* net, const char* name, int ndim, const int* 
     if (data != nullptr) {
       for (size_t i = 0; i < count; ++i) blob->add_data_f(data[i]);
     }
+  });
+}
+
+int SHADOW_CAPI(net_parse_text)(void* net, const char* text) {
+  return guarded([&] {
+    auto* handle = static_cast<NetHandle*>(net);
+    if (handle == nullptr || text == nullptr) throw std::runtime_error("net_parse_text: null argument");
+    shadow::NetParam parsed;
+    if (!Shadow::IO::ReadProtoFromText(text, &parsed)) throw std::runtime_error("net_parse_text: the text could not be parsed");
+    handle->param = parsed;
   });
 }
 

@@ -508,6 +508,16 @@ class Network {
   std::shared_ptr<Backend> backend_;
 };
 
+// ---------------------------------------------------------------------------------------------
+// Model text format (shadow/util/io.hpp:47-52 in a build without protobuf; format in
+// shadow/core/parser.cpp:1034-1917).  Throws (CHECK) on malformed text or on an operator type
+// this library does not have; ReadProtoFromTextFile returns false when the file cannot be opened.
+// ---------------------------------------------------------------------------------------------
+namespace IO {
+bool ReadProtoFromText(const std::string& proto_text, shadow::NetParam* proto);
+bool ReadProtoFromTextFile(const std::string& proto_file, shadow::NetParam* proto);
+}  // namespace IO
+
 }  // namespace Shadow
 
 #endif  // SHADOW_B200_HOST_SHADOW_API_HPP_

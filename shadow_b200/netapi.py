@@ -42,6 +42,7 @@ class NetLibrary:
                                   C.POINTER(C.c_char_p), C.POINTER(C.c_int), C.POINTER(C.c_int),
                                   C.POINTER(C.c_double), C.POINTER(C.c_char_p)])
         f("net_add_blob", C.c_int, [C.c_void_p, C.c_char_p, C.c_int, C.POINTER(C.c_int), C.c_void_p])
+        f("net_parse_text", C.c_int, [C.c_void_p, C.c_char_p])
         f("net_load", C.c_int, [C.c_void_p, C.c_char_p, C.c_int, C.c_int, C.POINTER(C.c_char_p)])
         f("net_forward", C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_char_p), C.POINTER(C.c_void_p)])
         f("net_blob_shape", C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_int), C.c_int])
@@ -86,6 +87,37 @@ def encode_args(args: Mapping[str, object]):
             else:
                 kinds.append(ARG_V_I), values.extend(float(int(v)) for v in seq)
     return names, kinds, counts, values, strings
+
+
+def _text_value(val) -> str:
+    """`type, [values]` of one argument in the model text format."""
+    if isinstance(val, (bool, np.bool_, int, np.integer)):
+        return "s_i, [%d]" % int(val)
+    if isinstance(val, (float, np.floating)):
+        return "s_f, [%s]" % repr(float(np.float32(val)))
+    if isinstance(val, str):
+        return "s_s, [%s]" % val
+    seq = list(val)
+    if seq and all(isinstance(v, str) for v in seq):
+        return "v_s, [%s]" % " # ".join(seq)
+    if seq and any(isinstance(v, (float, np.floating)) for v in seq):
+        return "v_f, [%s]" % " # ".join(repr(float(np.float32(v))) for v in seq)
+    return "v_i, [%s]" % " # ".join(str(int(v)) for v in seq)
+
+
+def model_text(net_name: str, ops, net_args: Mapping[str, object] | None = None, blobs=()) -> str:
+    """Serialise a graph in the reference's protobuf-free model text format
+    (shadow/core/parser.cpp:1844-1917; written on the reference side by
+    python/converter/shadow/transformer.py).  `ops` holds (type, name, bottoms, tops, args) tuples,
+    `blobs` (name, type, shape) tuples.  Floats are written with enough digits to round-trip float32."""
+    def arg_list(args):
+        return "; ".join("{%s, %s}" % (k, _text_value(v)) for k, v in args.items())
+    lines = ["[%s]" % net_name, "[%s]" % arg_list(net_args or {}),
+             "[%s]" % "; ".join("{%s, %s, [%s]}" % (n, t, " # ".join(str(int(d)) for d in shp)) for n, t, shp in blobs)]
+    for op_type, name, bottoms, tops, args in ops:
+        lines.append("[%s] | [%s] | [%d %d %d] | [%s] | [%s] | [%s]" % (
+            op_type, name, len(bottoms), len(tops), len(args), "; ".join(bottoms), "; ".join(tops), arg_list(args)))
+    return "\n".join(lines)
 
 
 class Net:
@@ -136,6 +168,12 @@ class Net:
         shape = (C.c_int * max(arr.ndim, 1))(*arr.shape)
         rc = self.L.net_add_blob(self.h, name.encode(), arr.ndim, shape, arr.ctypes.data_as(C.c_void_p))
         self.L.check(rc, "net_add_blob(%s)" % name)
+        return self
+
+    def parse_text(self, text: str) -> "Net":
+        """Replace the net under construction by the one parsed from the model text format
+        (IO::ReadProtoFromText, shadow/util/io.hpp:47-52)."""
+        self.L.check(self.L.net_parse_text(self.h, text.encode()), "net_parse_text")
         return self
 
     def load(self, backend_type: str = "Native", device_id: int = 0, out_blobs: Sequence[str] = ()) -> "Net":
