@@ -151,6 +151,17 @@ int sb200_gather(const float* x, const int* indexes, int64_t num_indexes, int64_
 int sb200_pad(const float* x, float* y, int64_t planes, int in_h, int in_w, const int* paddings, float value,
               void* stream);
 
+/* Max (pool_type 0) or average (1) pooling of x viewed as [planes, in_dhw] into y [planes, out_dhw];
+ * in_dhw, out_dhw, kernel, stride, pad are HOST arrays of three ints (depth, height, width; 2-D
+ * pooling passes depth 1, kernel 1, stride 1, pad 0).  The window of an output starts at
+ * index*stride - pad and ends at min(start + kernel, in + pad); the average divides by that size
+ * before clipping to the tensor.  The caller supplies out_dhw (the operator front-end's rounding
+ * rule decides it).
+ * Replaces Vision::Pooling2D<kGPU,float> and Vision::Pooling3D<kGPU,float>
+ * (shadow/operators/kernels/pooling.hpp:10-27, pooling.cu). */
+int sb200_pooling(const float* x, float* y, int64_t planes, const int* in_dhw, const int* out_dhw, const int* kernel,
+                  const int* stride, const int* pad, int pool_type, void* stream);
+
 /* SSD-style L2 normalisation of x[batch, channels, spatial].  across_spatial != 0: one norm per
  * sample, y = x * (1 / sqrt(sum(x*x) + eps)); else one norm per (sample, position) over the
  * channels, y = x / (float)sqrt(sum(x*x) + eps) with the square root taken in double.  Squares are

@@ -68,6 +68,7 @@ def port():
         L.orc_eltwise.argtypes = [C.POINTER(_FP), C.c_int, _FP, i64, C.c_int, _FP]
         L.orc_axpy.argtypes = [_FP, _FP, _FP, i64, i64, _FP]
         IP = C.POINTER(C.c_int)
+        L.orc_pooling.argtypes = [_FP, i64, IP, IP, IP, IP, IP, C.c_int, _FP]
         L.orc_copy_part.argtypes = [_FP, _FP, i64, i64, i64, i64, C.c_int]
         L.orc_permute.argtypes = [_FP, IP, IP, C.c_int, _FP]
         L.orc_gather.argtypes = [_FP, IP, i64, i64, i64, i64, _FP]
@@ -310,6 +311,31 @@ def pad(x, paddings, value: float = 0.0) -> np.ndarray:
     pd, pdp = _ints(paddings)
     y = np.empty([x.shape[0], x.shape[1], x.shape[2] + pd[0] + pd[1], x.shape[3] + pd[2] + pd[3]], np.float32)
     _ok(port().orc_pad(_fp(x), x.shape[0], x.shape[1], x.shape[2], x.shape[3], pdp, np.float32(value), _fp(y)), "pad")
+    return y
+
+
+def pooling(x, pool: int = 0, kernel_size=(), stride=(1,), pad=(0,), global_pooling: bool = False,
+            full_pooling: bool = True) -> np.ndarray:
+    """PoolingOp (shadow/operators/pooling_op.cpp:7-100): output size ceil/floor((dim + 2*pad - kernel)/stride) + 1
+    in float arithmetic."""
+    x = _f32(x)
+    ns = x.ndim - 2
+    if global_pooling:
+        kernel_size, stride, pad = list(x.shape[2:]), [1], [0]
+    expand = lambda v: [int(v[0])] * ns if len(v) == 1 else [int(t) for t in v]   # noqa: E731
+    k, s, p = expand(list(kernel_size)), expand(list(stride)), expand(list(pad))
+    out_sp = []
+    for n in range(ns):
+        q = np.float32(np.float32(x.shape[2 + n]) + np.float32(2.0) * np.float32(p[n]) - np.float32(k[n])) / np.float32(s[n])
+        out_sp.append(int(np.ceil(q) if full_pooling else np.floor(q)) + 1)
+    lead = 3 - ns
+    y = np.empty(list(x.shape[:2]) + out_sp, np.float32)
+    a_in, p_in = _ints([1] * lead + list(x.shape[2:]))
+    a_out, p_out = _ints([1] * lead + out_sp)
+    a_k, p_k = _ints([1] * lead + k)
+    a_s, p_s = _ints([1] * lead + s)
+    a_p, p_p = _ints([0] * lead + p)
+    _ok(port().orc_pooling(_fp(x), x.shape[0] * x.shape[1], p_in, p_out, p_k, p_s, p_p, pool, _fp(y)), "pooling")
     return y
 
 

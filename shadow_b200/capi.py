@@ -65,6 +65,7 @@ def lib() -> C.CDLL:
             "sb200_permute": (i32, [vp, vp, vp, vp, i32, vp]),
             "sb200_gather": (i32, [vp, vp, i64, i64, i64, i64, vp, vp]),
             "sb200_pad": (i32, [vp, vp, i64, i32, i32, vp, f32, vp]),
+            "sb200_pooling": (i32, [vp, vp, i64, vp, vp, vp, vp, vp, i32, vp]),
             "sb200_ssd_normalize": (i32, [vp, vp, i64, i64, i64, i32, f32, vp, i32, vp]),
             "sb200_row_norm": (i32, [vp, vp, i64, i64, f32, vp, vp, i32, i64, i64, i64, vp]),
         }
@@ -79,7 +80,7 @@ EXPORTED = ["sb200_status_string", "sb200_last_cuda_error", "sb200_device_sm_cou
             "sb200_fill", "sb200_unary", "sb200_activate", "sb200_prelu", "sb200_binary_scalar",
             "sb200_binary", "sb200_binary_broadcast", "sb200_scale_bias", "sb200_reduce_scratch_bytes",
             "sb200_reduce", "sb200_reduce_static", "sb200_reduce_partial", "sb200_reduce_finalize", "sb200_reduce_combine", "sb200_softmax", "sb200_eltwise", "sb200_axpy", "sb200_batch_norm", "sb200_normalize", "sb200_ssd_normalize", "sb200_row_norm",
-            "sb200_concat", "sb200_slice", "sb200_permute", "sb200_gather", "sb200_pad"]
+            "sb200_concat", "sb200_slice", "sb200_permute", "sb200_gather", "sb200_pad", "sb200_pooling"]
 
 
 def status_string(status: int) -> str:

@@ -450,3 +450,34 @@ def pad(x: torch.Tensor, paddings, value: float = 0.0, out: Optional[torch.Tenso
     capi.check(capi.lib().sb200_pad(x.data_ptr(), y.data_ptr(), x.shape[0] * x.shape[1], x.shape[2], x.shape[3], pads, value,
                                     _stream()), "sb200_pad")
     return y
+
+
+def pooling_out_size(dim: int, kernel: int, stride: int, pad: int, full_pooling: bool) -> int:
+    """shadow/operators/pooling_op.cpp:7-16: ceil (full_pooling) or floor of (dim + 2*pad - kernel)/stride, plus 1,
+    evaluated in float as the reference does."""
+    import numpy as np
+    q = np.float32(np.float32(dim) + np.float32(2.0) * np.float32(pad) - np.float32(kernel)) / np.float32(stride)
+    return int(np.ceil(q) if full_pooling else np.floor(q)) + 1
+
+
+def pooling(x: torch.Tensor, pool: int = 0, kernel_size=(), stride=(1,), pad=(0,), global_pooling: bool = False,
+            full_pooling: bool = True, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """Pooling (shadow/operators/pooling_op.cpp:27-100): pool 0 = max, 1 = average, over the 2 or 3
+    axes after (batch, channel); one-element kernel_size / stride / pad apply to every axis."""
+    _chk(x, "x")
+    ns = x.dim() - 2
+    if ns not in (2, 3):
+        raise ValueError("Only support 2D or 3D Pooling")
+    if global_pooling:
+        kernel_size, stride, pad = list(x.shape[2:]), [1], [0]
+    expand = lambda v: [int(v[0])] * ns if len(v) == 1 else [int(t) for t in v]   # noqa: E731
+    k, s, p = expand(list(kernel_size)), expand(list(stride)), expand(list(pad))
+    if not (len(k) == len(s) == len(p) == ns):
+        raise ValueError("kernel_size / stride / pad need one value or one per spatial axis")
+    out_sp = [pooling_out_size(x.shape[2 + n], k[n], s[n], p[n], full_pooling) for n in range(ns)]
+    y = torch.empty(list(x.shape[:2]) + out_sp, dtype=torch.float32, device=x.device) if out is None else _chk(out, "out")
+    lead = 3 - ns
+    arr = lambda v, fill: (ctypes.c_int * 3)(*([fill] * lead + list(v)))   # noqa: E731
+    capi.check(capi.lib().sb200_pooling(x.data_ptr(), y.data_ptr(), x.shape[0] * x.shape[1], arr(x.shape[2:], 1), arr(out_sp, 1),
+                                        arr(k, 1), arr(s, 1), arr(p, 0), pool, _stream()), "sb200_pooling")
+    return y

@@ -102,6 +102,16 @@ class PadKernel : public Kernel {
   virtual void Run(const BlobPtr& input, BlobPtr& output, Workspace* ws, const VecInt& paddings, float value) = 0;
 };
 
+// shadow/operators/kernels/pooling.hpp:29-42
+class PoolingKernel : public Kernel {
+ public:
+  virtual void Run(const BlobPtr& input, BlobPtr& output, Workspace* ws, int pool_type, int kernel_size_h, int kernel_size_w,
+                   int stride_h, int stride_w, int pad_h, int pad_w, bool full_pooling) = 0;
+  virtual void Run(const BlobPtr& input, BlobPtr& output, Workspace* ws, int pool_type, int kernel_size_d, int kernel_size_h,
+                   int kernel_size_w, int stride_d, int stride_h, int stride_w, int pad_d, int pad_h, int pad_w,
+                   bool full_pooling) = 0;
+};
+
 // shadow/operators/kernels/ssd_normalize.hpp:24-30
 class SSDNormalizeKernel : public Kernel {
  public:

@@ -270,6 +270,30 @@ class PadKernelB200 : public PadKernel {
   std::string kernel_type() const override { return "Default"; }
 };
 
+class PoolingKernelB200 : public PoolingKernel {
+ public:
+  void Run(const BlobPtr& input, BlobPtr& output, Workspace* ws, int pool_type, int kernel_size_h, int kernel_size_w,
+           int stride_h, int stride_w, int pad_h, int pad_w, bool) override {
+    const int in[3] = {1, input->shape(2), input->shape(3)}, out[3] = {1, output->shape(2), output->shape(3)};
+    const int k[3] = {1, kernel_size_h, kernel_size_w}, st[3] = {1, stride_h, stride_w}, pd[3] = {0, pad_h, pad_w};
+    expect_ok(sb200_pooling(input->data<float>(), output->mutable_data<float>(),
+                            static_cast<int64_t>(input->shape(0)) * input->shape(1), in, out, k, st, pd, pool_type, stream_of(ws)),
+              "sb200_pooling");
+  }
+  void Run(const BlobPtr& input, BlobPtr& output, Workspace* ws, int pool_type, int kernel_size_d, int kernel_size_h,
+           int kernel_size_w, int stride_d, int stride_h, int stride_w, int pad_d, int pad_h, int pad_w, bool) override {
+    const int in[3] = {input->shape(2), input->shape(3), input->shape(4)};
+    const int out[3] = {output->shape(2), output->shape(3), output->shape(4)};
+    const int k[3] = {kernel_size_d, kernel_size_h, kernel_size_w}, st[3] = {stride_d, stride_h, stride_w};
+    const int pd[3] = {pad_d, pad_h, pad_w};
+    expect_ok(sb200_pooling(input->data<float>(), output->mutable_data<float>(),
+                            static_cast<int64_t>(input->shape(0)) * input->shape(1), in, out, k, st, pd, pool_type, stream_of(ws)),
+              "sb200_pooling");
+  }
+  DeviceType device_type() const override { return DeviceType::kGPU; }
+  std::string kernel_type() const override { return "Default"; }
+};
+
 // One launch; the shared scale is read on the device (the reference copies it to the host first).
 class SSDNormalizeKernelB200 : public SSDNormalizeKernel {
  public:
@@ -368,6 +392,7 @@ REGISTER_OP_KERNEL_DEFAULT(SliceGPU, SliceKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(PermuteGPU, PermuteKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(GatherGPU, GatherKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(PadGPU, PadKernelB200);
+REGISTER_OP_KERNEL_DEFAULT(PoolingGPU, PoolingKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(SSDNormalizeGPU, SSDNormalizeKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(GroupNormGPU, GroupNormKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(LayerNormGPU, LayerNormKernelB200);

@@ -3,6 +3,7 @@
 // defaults and failure conditions follow shadow/operators/{binary,unary,activate,scale,reduce,
 // softmax,input}_op.cpp.
 #include <algorithm>
+#include <cmath>
 
 #include "op_kernels.hpp"
 
@@ -615,6 +616,59 @@ class PadOp : public Operator {
   std::shared_ptr<PadKernel> kernel_;
 };
 
+// Pooling (shadow/operators/pooling_op.cpp:7-100): `pool` 0 = max, 1 = average; `global_pooling`
+// makes the kernel the whole spatial extent (stride 1, pad 0); otherwise `kernel_size`, `stride`
+// (default 1), `pad` (default 0) hold one value or one per spatial axis; `full_pooling` (default
+// true) rounds the output size up instead of down.  2 or 3 spatial axes.
+class PoolingOp : public Operator {
+ public:
+  PoolingOp(const shadow::OpParam& op_param, Workspace* ws) : Operator(op_param, ws) {
+    pool_type_ = get_single_argument<int>("pool", 0);
+    CHECK_GE(pool_type_, 0);
+    CHECK_LE(pool_type_, 1);
+    global_pooling_ = get_single_argument<bool>("global_pooling", false);
+    if (global_pooling_) {
+      stride_ = VecInt(1, 1), pad_ = VecInt(1, 0);
+    } else {
+      kernel_size_ = get_repeated_argument<int>("kernel_size", 0);
+      stride_ = get_repeated_argument<int>("stride", 1);
+      pad_ = get_repeated_argument<int>("pad", 0);
+    }
+    full_pooling_ = get_single_argument<bool>("full_pooling", true);
+    kernel_ = kernel_for<PoolingKernel>(op_param, ws_);
+  }
+  void Run(const std::vector<BlobPtr>& inputs, std::vector<BlobPtr>& outputs) override {
+    const auto& input = inputs[0];
+    CHECK_NE(input, outputs[0]);
+    const int ns = input->num_axes() - 2;
+    CHECK(ns == 2 || ns == 3) << "Only support 2D or 3D Pooling";
+    if (global_pooling_ && static_cast<int>(kernel_size_.size()) != ns) {
+      for (int n = 0; n < ns; ++n) kernel_size_.push_back(input->shape(n + 2));
+    }
+    const VecInt k = per_axis(kernel_size_, ns), st = per_axis(stride_, ns), pd = per_axis(pad_, ns);
+    auto shape = input->shape();
+    for (int n = 0; n < ns; ++n) {
+      // float arithmetic, as the reference: (dim + 2.f*pad - kernel) / stride, rounded up or down, plus 1
+      const float q = (input->shape(n + 2) + 2.f * pd[n] - k[n]) / st[n];
+      shape[n + 2] = static_cast<int>(full_pooling_ ? std::ceil(q) : std::floor(q)) + 1;
+    }
+    outputs[0]->reshape(shape);
+    if (ns == 2) kernel_->Run(input, outputs[0], ws_, pool_type_, k[0], k[1], st[0], st[1], pd[0], pd[1], full_pooling_);
+    else kernel_->Run(input, outputs[0], ws_, pool_type_, k[0], k[1], k[2], st[0], st[1], st[2], pd[0], pd[1], pd[2], full_pooling_);
+  }
+
+ private:
+  static VecInt per_axis(const VecInt& v, int n) {
+    if (v.size() == 1) return VecInt(n, v[0]);
+    CHECK_EQ(static_cast<int>(v.size()), n);
+    return v;
+  }
+  int pool_type_;
+  bool global_pooling_, full_pooling_;
+  VecInt kernel_size_, stride_, pad_;
+  std::shared_ptr<PoolingKernel> kernel_;
+};
+
 // SSDNormalize (shadow/operators/ssd_normalize_op.cpp:9-45): `across_spatial` default true,
 // `channel_shared` default true, `eps` default 1e-5; one input, or two (x, scale).
 class SSDNormalizeOp : public Operator {
@@ -785,6 +839,7 @@ REGISTER_OPERATOR(Stack, StackOp);
 REGISTER_OPERATOR(Permute, PermuteOp);
 REGISTER_OPERATOR(Gather, GatherOp);
 REGISTER_OPERATOR(Pad, PadOp);
+REGISTER_OPERATOR(Pooling, PoolingOp);
 REGISTER_OPERATOR(SSDNormalize, SSDNormalizeOp);
 REGISTER_OPERATOR(GroupNorm, GroupNormOp);
 REGISTER_OPERATOR(InstanceNorm, InstanceNormOp);

@@ -118,6 +118,8 @@ const std::vector<std::pair<std::string, std::vector<Spec>>>& op_table() {
       {"InstanceNorm", {{"eps", kFloat, 1e-5, false}}},
       {"Pad", {{"paddings", kInts, 0, false}, {"value", kFloat, 0, false}}},
       {"Permute", {{"order", kInts, 0, false}}},
+      {"Pooling", {{"pool", kInt, 0, false}, {"kernel_size", kInts, 0, false}, {"stride", kInts, 0, false},
+                   {"pad", kInts, 0, false}, {"global_pooling", kInt, 0, false}, {"full_pooling", kInt, 1, false}}},
       {"Reduce", {{"operation", kInt, 0, false}, {"axes", kInts, 0, false}, {"keep_dims", kInt, 1, false}}},
       {"Reshape", {{"shape", kInts, 0, false}, {"axis", kInt, 0, false}, {"num_axes", kInt, -1, false}}},
       {"Scale", {{"axis", kInt, 1, false}, {"has_scale", kInt, 1, false}, {"has_bias", kInt, 1, false},

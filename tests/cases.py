@@ -234,6 +234,17 @@ def small_cases():
     cs.append(_case("pad_crop", "Pad", {"paddings": [-1, -2, -1, 0]}, [xm]))
     cs.append(_case("pad_mixed", "Pad", {"paddings": [2, -1, -2, 3], "value": -1.0}, [xm]))
     cs.append(_case("pad_none", "Pad", {"paddings": [0, 0, 0, 0]}, [xm]))
+    xq = normal(1370, (2, 3, 9, 11))
+    cs.append(_case("pool_max_3x3_s2", "Pooling", {"pool": 0, "kernel_size": [3], "stride": [2]}, [xq]))
+    cs.append(_case("pool_avg_3x3_s2_pad1", "Pooling", {"pool": 1, "kernel_size": [3], "stride": [2], "pad": [1]}, [xq]))
+    cs.append(_case("pool_avg_2x3_floor", "Pooling", {"pool": 1, "kernel_size": [2, 3], "stride": [2, 1], "full_pooling": False}, [xq]))
+    cs.append(_case("pool_max_pad_neg_values", "Pooling", {"pool": 0, "kernel_size": [2], "stride": [2], "pad": [1]},
+                    [uniform(1371, (2, 3, 6, 6), -5.0, -1.0)]))
+    cs.append(_case("pool_global_avg_7x7", "Pooling", {"pool": 1, "global_pooling": True}, [normal(1372, (3, 8, 7, 7))]))
+    cs.append(_case("pool_global_max", "Pooling", {"pool": 0, "global_pooling": True}, [normal(1373, (2, 4, 13, 17))]))
+    cs.append(_case("pool_global_avg_large", "Pooling", {"pool": 1, "global_pooling": True}, [normal(1374, (2, 4, 13, 17), 1.0, 1.0)]))
+    cs.append(_case("pool_3d_max", "Pooling", {"pool": 0, "kernel_size": [2, 3, 2], "stride": [1, 2, 2]}, [normal(1375, (2, 2, 4, 7, 6))]))
+    cs.append(_case("pool_3d_avg_pad", "Pooling", {"pool": 1, "kernel_size": [3], "stride": [2], "pad": [1]}, [normal(1376, (1, 3, 5, 6, 7))]))
     xs = normal(1290, (3, 20, 5, 7))
     cs.append(_case("ssd_normalize_defaults", "SSDNormalize", {}, [xs]))
     cs.append(_case("ssd_normalize_across_shared", "SSDNormalize", {"across_spatial": True, "channel_shared": True},
@@ -397,6 +408,9 @@ def run_port(case) -> np.ndarray:
                               a.get("eps", 1e-5))
     if op == "Gather":
         return orc.gather(x[0], a["indexes"], a.get("axis", 0))
+    if op == "Pooling":
+        return orc.pooling(x[0], a.get("pool", 0), a.get("kernel_size", []), a.get("stride", [1]), a.get("pad", [0]),
+                           a.get("global_pooling", False), a.get("full_pooling", True))
     if op == "Normalize":
         return orc.normalize(x[0], a.get("axis", 1), a.get("p", 2.0), a.get("eps", 1e-12))
     if op == "BatchNorm":
@@ -442,6 +456,13 @@ def tolerance_class(case) -> str:
         return "exact"
     if op in ("GroupNorm", "InstanceNorm", "LayerNorm"):
         return "rownorm"
+    if op == "Pooling":
+        # max, and averages over windows of up to 64 elements (summed in the reference's order), are exact;
+        # larger windows are summed by a warp in double
+        x = case["inputs"][0]
+        window = int(np.prod(x.shape[2:])) if a.get("global_pooling", False) else int(np.prod(
+            a["kernel_size"] * (x.ndim - 2) if len(a["kernel_size"]) == 1 else a["kernel_size"]))
+        return "exact" if a.get("pool", 0) == 0 or window <= 64 else "rel"
     if op == "SSDNormalize":   # only the order of the double additions differs from the reference
         return "ulp2"
     if op == "Normalize":   # p = 1, 2: only the order of the double additions differs from the reference
@@ -489,6 +510,9 @@ def run_cuda(case, device="cuda:0"):
     elif op in ("Reshape", "Flatten", "Squeeze", "Unsqueeze", "Concat", "Stack", "Slice", "Permute", "Pad"):
         torch.cuda.synchronize()
         return _movement(dict(case, _args_inputs=x), F, lambda t: t.cpu().numpy())
+    elif op == "Pooling":
+        y = F.pooling(x[0], a.get("pool", 0), a.get("kernel_size", []), a.get("stride", [1]), a.get("pad", [0]),
+                      a.get("global_pooling", False), a.get("full_pooling", True))
     elif op == "Gather":
         y = F.gather(x[0], torch.tensor(a["indexes"], dtype=torch.int32, device=device), a.get("axis", 0))
     elif op == "SSDNormalize":
@@ -520,6 +544,8 @@ def reduced_length(case) -> int:
     x = case["inputs"][0]
     if case["op"] in ("Softmax", "Normalize"):
         return int(x.shape[case["args"].get("axis", 1)])
+    if case["op"] == "Pooling":
+        return int(np.prod(x.shape[2:]))
     axes = case["args"].get("axes", []) or list(range(x.ndim))
     return int(np.prod([x.shape[a] for a in axes]))
 
