@@ -21,7 +21,6 @@
 #include <float.h>
 
 #include <cstdio>
-#include <cstdlib>
 #include <initializer_list>
 #include <mutex>
 #include <type_traits>
@@ -292,83 +291,7 @@ struct GeomB {
   int64_t r_chunk;      // rows per split
   int64_t n_out;        // K0*K1
   Divisor count;
-  int W, G;             // plane kernel: units per column tile, row groups per block
 };
-
-// Plane layout for K1u that no power-of-two lane count divides well (196 floats = 49 float4: 8-lane
-// tiles leave 1 lane in 8 idle).  A block owns a column tile of W <= 256 units and G = 256 / W row
-// groups; thread (g, c) reduces rows g, g+G, ... of its column, so the threads of a block read
-// consecutive addresses (when the tile spans the whole of K1 the block streams its rows as one
-// contiguous range).  The G groups are merged in index order through shared memory.
-// blockIdx.x = k0*nbx + tile, blockIdx.y = split.
-template <int OP, bool VEC, bool TO_PART>
-__global__ void __launch_bounds__(kThreads)
-redB_plane_kernel(const float* __restrict__ x, float* y, double* part, const __grid_constant__ GeomB g) {
-  using R = RedOp<OP>;
-  using Acc = typename R::Acc;
-  constexpr int W = VEC ? 4 : 1;
-  __shared__ Acc smem[W][kThreads];
-  const int t = threadIdx.x;
-  const int grp = t / g.W, c = t - grp * g.W;
-  const int64_t k0 = blockIdx.x / g.nbx, bx = blockIdx.x - k0 * g.nbx;
-  const int64_t s = blockIdx.y;
-  const int64_t col = bx * g.W + c;   // unit index along K1
-  const bool active = (grp < g.G) && (col < g.K1u);
-  const int64_t r_begin = s * g.r_chunk;
-  int64_t r_end = r_begin + g.r_chunk;
-  if (r_end > g.R) r_end = g.R;
-  Acc acc[W];
-#pragma unroll
-  for (int e = 0; e < W; ++e) acc[e] = R::init();
-  if (active) {
-    const float* p = x + (k0 * g.R + r_begin + grp) * g.K1 + col * W;
-    const int64_t step = static_cast<int64_t>(g.G) * g.K1;
-    const int cnt = static_cast<int>((r_end - r_begin - grp + g.G - 1) / g.G);   // rows of this thread
-    int k = 0;
-    for (; k + kUnroll <= cnt; k += kUnroll, p += kUnroll * step) {
-      float4 v4[kUnroll];
-      float v1[kUnroll];
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        if (VEC) v4[u] = ld_stream(reinterpret_cast<const float4*>(p + u * step));
-        else v1[u] = ld_stream(p + u * step);
-      }
-#pragma unroll
-      for (int u = 0; u < kUnroll; ++u) {
-        if (VEC) {
-          acc[0] = R::step(acc[0], v4[u].x);
-          acc[W > 1 ? 1 : 0] = R::step(acc[W > 1 ? 1 : 0], v4[u].y);
-          acc[W > 2 ? 2 : 0] = R::step(acc[W > 2 ? 2 : 0], v4[u].z);
-          acc[W > 3 ? 3 : 0] = R::step(acc[W > 3 ? 3 : 0], v4[u].w);
-        } else {
-          acc[0] = R::step(acc[0], v1[u]);
-        }
-      }
-    }
-    for (; k < cnt; ++k, p += step) {
-      if (VEC) {
-        const float4 q = ld_stream(reinterpret_cast<const float4*>(p));
-        acc[0] = R::step(acc[0], q.x);
-        acc[W > 1 ? 1 : 0] = R::step(acc[W > 1 ? 1 : 0], q.y);
-        acc[W > 2 ? 2 : 0] = R::step(acc[W > 2 ? 2 : 0], q.z);
-        acc[W > 3 ? 3 : 0] = R::step(acc[W > 3 ? 3 : 0], q.w);
-      } else {
-        acc[0] = R::step(acc[0], ld_stream(p));
-      }
-    }
-  }
-#pragma unroll
-  for (int e = 0; e < W; ++e) smem[e][t] = acc[e];
-  __syncthreads();
-  if (grp == 0 && col < g.K1u) {
-#pragma unroll
-    for (int e = 0; e < W; ++e) {
-      Acc a = smem[e][c];
-      for (int k = 1; k < g.G; ++k) a = R::merge(a, smem[e][k * g.W + c]);
-      emit<OP, TO_PART>(a, y, part, k0 * g.K1 + col * W + e, s, g.n_out, g.count);
-    }
-  }
-}
 
 // blockIdx.x = k0*nbx + bx, blockIdx.y = split.  TX lanes along K1, TY = kThreads/TX rows along R.
 template <int OP, int TX, bool VEC, bool TO_PART>
@@ -630,25 +553,10 @@ int make_plan(const int* in_shape, int num_axes, const int* axes, int n_axes, co
     }
     P->tx = best_tx;
     g.nbx = (g.K1u + best_tx - 1) / best_tx;
-    int ty = kThreads / best_tx;
-    g.W = g.G = 0;
-    // lanes left idle by the best power-of-two tile vs by a plane tile of W = ceil(K1u / ntile) units
-    const int64_t ntile = (g.K1u + kThreads - 1) / kThreads;
-    const int64_t pw = (g.K1u + ntile - 1) / ntile;
-    const int64_t pg = kThreads / pw;
-    const double idle_tile = static_cast<double>(best_waste) / static_cast<double>(g.nbx * best_tx);
-    const double idle_plane = 1.0 - static_cast<double>(g.K1u * pg) / static_cast<double>(ntile * kThreads);
-    static const char* knob = getenv("SB200_REDB_PLANE");
-    if ((knob ? knob[0] == '1' : (idle_tile > 0.0625 && idle_plane < idle_tile)) && K0 * ntile < (1ll << 31)) {
-      P->tx = 0;   // plane kernel
-      g.W = static_cast<int>(pw), g.G = static_cast<int>(pg), g.nbx = ntile;
-      ty = g.G;
-    }
+    const int ty = kThreads / best_tx;
     const int64_t blocks = g.nbx * K0;
     int64_t splits = (target_blocks * kTargetWaves + blocks - 1) / blocks;
     if (blocks >= target_blocks * 4) splits = 1;   // already several waves of blocks: no second kernel
-    static const char* sknob = getenv("SB200_REDB_SPLITS");
-    if (sknob) splits = atoi(sknob);
     const int64_t max_by_work = (Rm + ty * kUnroll * kMinTiles - 1) / (ty * kUnroll * kMinTiles);
     if (splits > max_by_work) splits = max_by_work;
     if (splits > 65535) splits = 65535;
@@ -698,10 +606,7 @@ void launch_stage1(const Plan& P, const float* x, float* y, double* part, cudaSt
 #define SB200_LAUNCH_B(TXV)                                                                          \
   if (P.vec) redB_kernel<OP, TXV, true, TO_PART><<<grid, kThreads, 0, s>>>(x, y, part, P.b);         \
   else redB_kernel<OP, TXV, false, TO_PART><<<grid, kThreads, 0, s>>>(x, y, part, P.b);
-    if (P.tx == 0) {
-      if (P.vec) redB_plane_kernel<OP, true, TO_PART><<<grid, kThreads, 0, s>>>(x, y, part, P.b);
-      else redB_plane_kernel<OP, false, TO_PART><<<grid, kThreads, 0, s>>>(x, y, part, P.b);
-    } else if (P.tx == 32) { SB200_LAUNCH_B(32) }
+    if (P.tx == 32) { SB200_LAUNCH_B(32) }
     else if (P.tx == 16) { SB200_LAUNCH_B(16) }
     else { SB200_LAUNCH_B(8) }
 #undef SB200_LAUNCH_B
