@@ -61,10 +61,12 @@ parts_tile_kernel(const __grid_constant__ Parts p, float* wide, int64_t total) {
 // the wide tensor, the part found by a search over the (at most 16) offsets.
 template <bool TO_WIDE>
 __global__ void __launch_bounds__(kThreads)
-parts_elem_kernel(const __grid_constant__ Parts p, float* wide, int64_t total, int64_t count) {
+parts_elem_kernel(const __grid_constant__ Parts p, float* wide, int64_t total, int64_t count, FastDiv32 div_total) {
   const int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
   if (i >= count) return;
-  const int64_t row = i / total, c = i - row * total;
+  // one high multiply instead of a 64-bit division whenever the indices fit 32 bits
+  const int64_t row = count < (1ll << 32) ? static_cast<int64_t>(div_total.div(static_cast<uint32_t>(i))) : i / total;
+  const int64_t c = i - row * total;
   int k = 0;
 #pragma unroll
   for (int j = 1; j < kMaxParts; ++j)
@@ -116,7 +118,8 @@ int run_parts(float* const* parts, const int64_t* widths, int n_parts, float* wi
       const int64_t count = outer * total;
       blocks = (count + kThreads - 1) / kThreads;
       if (blocks >= (1ll << 31)) return SB200_ERR_UNSUPPORTED;
-      parts_elem_kernel<TO_WIDE><<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(p, wide, total, count);
+      const FastDiv32 div_total(static_cast<uint32_t>(total < (1ll << 32) ? total : 1));
+      parts_elem_kernel<TO_WIDE><<<static_cast<unsigned>(blocks), kThreads, 0, s>>>(p, wide, total, count, div_total);
     }
     const int rc = after_launch(what);
     if (rc != SB200_OK) return rc;
@@ -177,29 +180,48 @@ transpose_tile_kernel(const float* __restrict__ x, float* y, int64_t R, int64_t 
 // ---- Gather, Pad --------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kThreads)
 gather_kernel(const float* __restrict__ x, const int* __restrict__ indexes, float* y, int64_t count, int64_t num_indexes,
-              int64_t gather_dim, int64_t inner) {
+              int64_t gather_dim, int64_t inner, FastDiv32 div_inner, FastDiv32 div_num) {
   const int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
   if (i >= count) return;
-  const int64_t r = i / inner, col = i - r * inner;   // r = outer * num_indexes + which index
-  const int64_t o = r / num_indexes, which = r - o * num_indexes;
+  int64_t r, o;   // r = outer * num_indexes + which index
+  if (count < (1ll << 32)) {
+    r = div_inner.div(static_cast<uint32_t>(i));
+    o = div_num.div(static_cast<uint32_t>(r));
+  } else {
+    r = i / inner;
+    o = r / num_indexes;
+  }
+  const int64_t col = i - r * inner, which = r - o * num_indexes;
   const int64_t gi = __ldg(indexes + which);
   // an index outside [0, gather_dim) would read outside the tensor: it yields 0 instead
   y[i] = (gi >= 0 && gi < gather_dim) ? __ldg(x + (o * gather_dim + gi) * inner + col) : 0.f;
 }
 
+// A thread owns up to kPadRun consecutive columns of one output row: one index decode per thread
+// (by high multiplies: rows < 2^32 is checked by the caller), then plain coalesced 4-byte accesses.
+constexpr int kPadRun = 4;
 __global__ void __launch_bounds__(kThreads)
-pad_kernel(const float* __restrict__ x, float* y, int64_t count, int in_h, int in_w, int out_h, int out_w, int top,
-           int left, float value) {
-  const int64_t i = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
-  if (i >= count) return;
-  const int64_t row = i / out_w;
-  const int ow = static_cast<int>(i - row * out_w);
-  const int64_t plane = row / out_h;
-  const int oh = static_cast<int>(row - plane * out_h);
-  const int h = oh - top, w = ow - left;
-  float v = value;
-  if (h >= 0 && h < in_h && w >= 0 && w < in_w) v = ld_stream(x + (plane * in_h + h) * in_w + w);
-  st_stream(y + i, v);
+pad_kernel(const float* __restrict__ x, float* y, int64_t rows, int in_h, int in_w, int out_h, int out_w, int top,
+           int left, float value, int runs_per_row, FastDiv32 div_runs, FastDiv32 div_out_h) {
+  const int64_t t = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  if (t >= rows * runs_per_row) return;
+  uint32_t row, run, plane, oh;
+  div_runs.divmod(static_cast<uint32_t>(t), row, run);
+  div_out_h.divmod(row, plane, oh);
+  const int h = static_cast<int>(oh) - top;
+  const bool row_inside = h >= 0 && h < in_h;
+  const float* xr = x + (static_cast<int64_t>(plane) * in_h + (row_inside ? h : 0)) * in_w;
+  float* yr = y + static_cast<int64_t>(row) * out_w;
+  // lane-interleaved columns: consecutive threads of a row write consecutive addresses
+#pragma unroll
+  for (int k = 0; k < kPadRun; ++k) {
+    const int ow = static_cast<int>(run) + k * runs_per_row;
+    if (ow >= out_w) break;
+    const int w = ow - left;
+    float v = value;
+    if (row_inside && w >= 0 && w < in_w) v = ld_stream(xr + w);
+    st_stream(yr + ow, v);
+  }
 }
 
 }  // namespace
@@ -301,8 +323,10 @@ int sb200_gather(const float* x, const int* indexes, int64_t num_indexes, int64_
   const int64_t count = outer * num_indexes * inner;
   const int64_t blocks = (count + kThreads - 1) / kThreads;
   if (blocks >= (1ll << 31)) return SB200_ERR_UNSUPPORTED;
-  gather_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(x, indexes, y, count, num_indexes,
-                                                                                                  gather_dim, inner);
+  const FastDiv32 div_inner(static_cast<uint32_t>(inner < (1ll << 32) ? inner : 1));
+  const FastDiv32 div_num(static_cast<uint32_t>(num_indexes < (1ll << 32) ? num_indexes : 1));
+  gather_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+      x, indexes, y, count, num_indexes, gather_dim, inner, div_inner, div_num);
   return after_launch("sb200_gather");
 }
 
@@ -316,11 +340,14 @@ int sb200_pad(const float* x, float* y, int64_t planes, int in_h, int in_w, cons
   if (x == nullptr || y == nullptr || x == y) return SB200_ERR_BAD_ARGUMENT;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 3u) return SB200_ERR_BAD_ARGUMENT;
   if (planes > (1ll << 40) / (out_h * out_w)) return SB200_ERR_UNSUPPORTED;
-  const int64_t count = planes * out_h * out_w;
-  const int64_t blocks = (count + kThreads - 1) / kThreads;
-  if (blocks >= (1ll << 31)) return SB200_ERR_UNSUPPORTED;
+  const int64_t rows = planes * out_h;
+  const int runs_per_row = static_cast<int>((out_w + kPadRun - 1) / kPadRun);
+  const int64_t threads = rows * runs_per_row;
+  if (threads >= (1ll << 32)) return SB200_ERR_UNSUPPORTED;   // 32-bit index decode in the kernel
+  const int64_t blocks = (threads + kThreads - 1) / kThreads;
   pad_kernel<<<static_cast<unsigned>(blocks), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
-      x, y, count, in_h, in_w, static_cast<int>(out_h), static_cast<int>(out_w), paddings[0], paddings[2], value);
+      x, y, rows, in_h, in_w, static_cast<int>(out_h), static_cast<int>(out_w), paddings[0], paddings[2], value, runs_per_row,
+      FastDiv32(static_cast<uint32_t>(runs_per_row)), FastDiv32(static_cast<uint32_t>(out_h)));
   return after_launch("sb200_pad");
 }
 

@@ -8,7 +8,7 @@
 // (+ ScaleBias): six launches, about 36 bytes of traffic per element and a scratch of
 // count + inner + 2*rows floats.  Here a row lives in the registers of TPR threads: one 128-bit
 // read, three in-register steps, one 128-bit write, no scratch: 8 algorithmic bytes per element.
-// Rows longer than 32768 floats take a block-per-row kernel that re-reads the row (from L2).
+// Rows longer than 8192 floats take a block-per-row kernel that re-reads the row (from L2).
 // Arithmetic follows the reference CPU term by term: every term alpha*x (and alpha*(v*v)) is
 // rounded to float and accumulated in double (Blas::BlasSgemv on the CPU), mean and variance
 // are rounded to float, the quotient is the correctly rounded float division, scale and bias are
@@ -27,15 +27,21 @@ struct Affine {
   const float* scale;
   const float* bias;
   int mode;
+  int vec_ok;                // scale and bias are 16-byte aligned
   uint32_t groups;           // channel mode: rows cycle through `groups` groups ...
   uint32_t chan_per_group;   // ... of this many channels ...
   FastDiv32 div_spatial;     // ... of this many elements each
 };
 
-// index into scale / bias of element j of row `row`
-__device__ __forceinline__ uint32_t affine_index(const Affine& a, int64_t row, uint32_t j) {
+// first channel of the group that row `row` belongs to (channel mode)
+__device__ __forceinline__ uint32_t channel_base(const Affine& a, int64_t row) {
+  return a.mode == kAffineChannel ? static_cast<uint32_t>(row % a.groups) * a.chan_per_group : 0u;
+}
+
+// index into scale / bias of element j of a row whose group starts at channel `base`
+__device__ __forceinline__ uint32_t affine_index(const Affine& a, uint32_t base, uint32_t j) {
   if (a.mode == kAffinePosition) return j;
-  return static_cast<uint32_t>(row % a.groups) * a.chan_per_group + a.div_spatial.div(j);
+  return base + a.div_spatial.div(j);
 }
 
 __device__ __forceinline__ float affine_apply(const Affine& a, float v, uint32_t k) {
@@ -110,15 +116,25 @@ rownorm_rows_kernel(const float* x, float* y, int64_t rows, int units_per_row, f
   const float d = __fsqrt_rn(__fadd_rn(var, eps));
   const bool d_ok = (d >= 0x1p-60f) && (d <= 0x1p60f);
   const float rcp = __frcp_rn(d);
+  const uint32_t base = channel_base(aff, row);
+  // position mode with float4 units: scale and bias are read as float4 too (vec_affine: both 16-byte aligned)
+  const bool vec_affine = VEC && aff.mode == kAffinePosition && aff.vec_ok;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     const int u = t + i * TPR;
     if (live && u < units_per_row) {
       float o[W];
 #pragma unroll
-      for (int e = 0; e < W; ++e) {
-        o[e] = div_exact(v[i][e], d, rcp, d_ok);
-        if (aff.mode != kAffineNone) o[e] = affine_apply(aff, o[e], affine_index(aff, row, static_cast<uint32_t>(u * W + e)));
+      for (int e = 0; e < W; ++e) o[e] = div_exact(v[i][e], d, rcp, d_ok);
+      if (vec_affine) {
+        const float4 sc = __ldg(reinterpret_cast<const float4*>(aff.scale) + u), bs = __ldg(reinterpret_cast<const float4*>(aff.bias) + u);
+        o[0] = __fadd_rn(__fmul_rn(o[0], sc.x), bs.x);
+        o[W > 1 ? 1 : 0] = __fadd_rn(__fmul_rn(o[W > 1 ? 1 : 0], sc.y), bs.y);
+        o[W > 2 ? 2 : 0] = __fadd_rn(__fmul_rn(o[W > 2 ? 2 : 0], sc.z), bs.z);
+        o[W > 3 ? 3 : 0] = __fadd_rn(__fmul_rn(o[W > 3 ? 3 : 0], sc.w), bs.w);
+      } else if (aff.mode != kAffineNone) {
+#pragma unroll
+        for (int e = 0; e < W; ++e) o[e] = affine_apply(aff, o[e], affine_index(aff, base, static_cast<uint32_t>(u * W + e)));
       }
       if (VEC) st_stream(reinterpret_cast<float4*>(y + row_off) + u, make_float4(o[0], o[W > 1 ? 1 : 0], o[W > 2 ? 2 : 0], o[W > 3 ? 3 : 0]));
       else st_stream(y + row_off + u, o[0]);
@@ -126,30 +142,84 @@ rownorm_rows_kernel(const float* x, float* y, int64_t rows, int units_per_row, f
   }
 }
 
-// Any row length: one block per row (grid-strided), three passes over the row.
+// Long rows: one block per row (grid-strided), three passes over the row; the second and third
+// read come from L2 (the grid is sized so that the rows in flight fit there).  Used for rows that
+// would need a 1024-thread block in the register kernel (one resident block per SM, no overlap
+// of one row's load with another's arithmetic) and for rows too long for registers at all.
+template <bool VEC>
 __global__ void __launch_bounds__(256)
 rownorm_long_rows_kernel(const float* x, float* y, int64_t rows, int64_t inner, float alpha, float eps,
                          const __grid_constant__ Affine aff) {
+  constexpr int W = VEC ? 4 : 1;
   __shared__ double red[32];
+  const int64_t units = inner / W;
+  auto load = [&](const float* xr, int64_t u, float (&v)[W]) {
+    if (VEC) {
+      const float4 q = *(reinterpret_cast<const float4*>(xr) + u);
+      v[0] = q.x; v[W > 1 ? 1 : 0] = q.y; v[W > 2 ? 2 : 0] = q.z; v[W > 3 ? 3 : 0] = q.w;
+    } else {
+      v[0] = xr[u];
+    }
+  };
+  // kB units per thread and step, loaded together so that they are in flight together
+  constexpr int kB = 4;
   for (int64_t row = blockIdx.x; row < rows; row += gridDim.x) {
     const float* xr = x + row * inner;
     float* yr = y + row * inner;
     double acc = 0.0;
-    for (int64_t i = threadIdx.x; i < inner; i += 256) acc += static_cast<double>(__fmul_rn(alpha, xr[i]));
+    for (int64_t u0 = threadIdx.x; u0 < units; u0 += 256 * kB) {
+      float v[kB][W];
+#pragma unroll
+      for (int k = 0; k < kB; ++k)
+        if (u0 + k * 256 < units) load(xr, u0 + k * 256, v[k]);
+#pragma unroll
+      for (int k = 0; k < kB; ++k)
+        if (u0 + k * 256 < units) {
+#pragma unroll
+          for (int e = 0; e < W; ++e) acc += static_cast<double>(__fmul_rn(alpha, v[k][e]));
+        }
+    }
     const float mean = static_cast<float>(block_reduce(acc, OpAddD(), 0.0, red));
     acc = 0.0;
-    for (int64_t i = threadIdx.x; i < inner; i += 256) {
-      const float c = __fsub_rn(xr[i], mean);
-      acc += static_cast<double>(__fmul_rn(alpha, __fmul_rn(c, c)));
+    for (int64_t u0 = threadIdx.x; u0 < units; u0 += 256 * kB) {
+      float v[kB][W];
+#pragma unroll
+      for (int k = 0; k < kB; ++k)
+        if (u0 + k * 256 < units) load(xr, u0 + k * 256, v[k]);
+#pragma unroll
+      for (int k = 0; k < kB; ++k)
+        if (u0 + k * 256 < units) {
+#pragma unroll
+          for (int e = 0; e < W; ++e) {
+            const float c = __fsub_rn(v[k][e], mean);
+            acc += static_cast<double>(__fmul_rn(alpha, __fmul_rn(c, c)));
+          }
+        }
     }
     const float var = static_cast<float>(block_reduce(acc, OpAddD(), 0.0, red));
     const float d = __fsqrt_rn(__fadd_rn(var, eps));
     const bool d_ok = (d >= 0x1p-60f) && (d <= 0x1p60f);
     const float rcp = __frcp_rn(d);
-    for (int64_t i = threadIdx.x; i < inner; i += 256) {
-      float o = div_exact(__fsub_rn(xr[i], mean), d, rcp, d_ok);
-      if (aff.mode != kAffineNone) o = affine_apply(aff, o, affine_index(aff, row, static_cast<uint32_t>(i)));
-      yr[i] = o;
+    const uint32_t base = channel_base(aff, row);
+    for (int64_t u0 = threadIdx.x; u0 < units; u0 += 256 * kB) {
+      float v[kB][W];
+#pragma unroll
+      for (int k = 0; k < kB; ++k)
+        if (u0 + k * 256 < units) load(xr, u0 + k * 256, v[k]);
+#pragma unroll
+      for (int k = 0; k < kB; ++k) {
+        const int64_t u = u0 + k * 256;
+        if (u < units) {
+          float o[W];
+#pragma unroll
+          for (int e = 0; e < W; ++e) {
+            o[e] = div_exact(__fsub_rn(v[k][e], mean), d, rcp, d_ok);
+            if (aff.mode != kAffineNone) o[e] = affine_apply(aff, o[e], affine_index(aff, base, static_cast<uint32_t>(u * W + e)));
+          }
+          if (VEC) st_stream(reinterpret_cast<float4*>(yr) + u, make_float4(o[0], o[W > 1 ? 1 : 0], o[W > 2 ? 2 : 0], o[W > 3 ? 3 : 0]));
+          else st_stream(yr + u, o[0]);
+        }
+      }
     }
     __syncthreads();
   }
@@ -170,8 +240,7 @@ bool pick_rows(const float* x, float* y, int64_t rows, int units, float alpha, f
 #define SB200_TRY(TPR, NV) \
   if (units <= TPR * NV) { launch_rows<TPR, NV, VEC>(x, y, rows, units, alpha, eps, aff, s); return true; }
   SB200_TRY(32, 1) SB200_TRY(32, 2) SB200_TRY(32, 4)
-  SB200_TRY(64, 4) SB200_TRY(128, 4) SB200_TRY(256, 4) SB200_TRY(512, 4) SB200_TRY(1024, 4)
-  SB200_TRY(1024, 8)
+  SB200_TRY(64, 4) SB200_TRY(128, 4) SB200_TRY(256, 4) SB200_TRY(512, 4)
 #undef SB200_TRY
   return false;
 }
@@ -191,6 +260,7 @@ extern "C" int sb200_row_norm(const float* x, float* y, int64_t rows, int64_t in
   if (inner >= (1ll << 31) || rows >= (1ll << 31) || rows > (1ll << 40) / inner) return SB200_ERR_UNSUPPORTED;
   Affine aff;
   aff.scale = scale, aff.bias = bias, aff.mode = affine_mode, aff.groups = 1, aff.chan_per_group = 1;
+  aff.vec_ok = (scale != nullptr && bias != nullptr && aligned16(scale) && aligned16(bias)) ? 1 : 0;
   if (affine_mode != kAffineNone) {
     if (scale == nullptr || bias == nullptr) return SB200_ERR_BAD_ARGUMENT;
     if (affine_mode == kAffineChannel) {
@@ -203,11 +273,17 @@ extern "C" int sb200_row_norm(const float* x, float* y, int64_t rows, int64_t in
   }
   const float alpha = 1.f / static_cast<float>(inner);   // the reference's 1.f / inner_num
   cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const bool vec = inner % 4 == 0 && aligned16(x) && aligned16(y);
   bool done = false;
-  if (inner % 4 == 0 && aligned16(x) && aligned16(y) && inner / 4 <= 1024 * 8)
-    done = pick_rows<true>(x, y, rows, static_cast<int>(inner / 4), alpha, eps, aff, s);
-  else if (inner <= 1024 * 8)
-    done = pick_rows<false>(x, y, rows, static_cast<int>(inner), alpha, eps, aff, s);
-  if (!done) rownorm_long_rows_kernel<<<stream_grid(rows, 8), 256, 0, s>>>(x, y, rows, inner, alpha, eps, aff);
+  if (vec) done = pick_rows<true>(x, y, rows, static_cast<int>(inner / 4), alpha, eps, aff, s);
+  else if (inner <= 512 * 4) done = pick_rows<false>(x, y, rows, static_cast<int>(inner), alpha, eps, aff, s);
+  if (!done) {
+    // rows in flight (grid x row bytes) are kept near 48 MB so that the re-reads hit L2
+    int64_t per_sm = (48ll << 20) / (inner * 4) / sm_count();
+    per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
+    const unsigned grid = stream_grid(rows, static_cast<int>(per_sm));
+    if (vec) rownorm_long_rows_kernel<true><<<grid, 256, 0, s>>>(x, y, rows, inner, alpha, eps, aff);
+    else rownorm_long_rows_kernel<false><<<grid, 256, 0, s>>>(x, y, rows, inner, alpha, eps, aff);
+  }
   return after_launch("sb200_row_norm");
 }

@@ -263,6 +263,8 @@ def small_cases():
     cs.append(_case("group_norm_g4_affine", "GroupNorm", {"group": 4, "eps": float(np.float32(1e-3))}, [xg, gs, gb]))
     cs.append(_case("group_norm_g12", "GroupNorm", {"group": 12}, [xg]))
     cs.append(_case("group_norm_vec_rows", "GroupNorm", {"group": 2}, [normal(1273, (2, 8, 4, 4)), normal(1274, (8,)), normal(1275, (8,))]))
+    cs.append(_case("group_norm_long_rows_affine", "GroupNorm", {"group": 1},
+                    [normal(1283, (2, 8, 36, 36), 0.2, 1.0), normal(1284, (8,), 1.0, 0.3), normal(1285, (8,))]))
     cs.append(_case("instance_norm", "InstanceNorm", {}, [xg]))
     cs.append(_case("instance_norm_affine", "InstanceNorm", {}, [xg, gs, gb]))
     xl = normal(1276, (4, 9, 130), -1.0, 3.0)
