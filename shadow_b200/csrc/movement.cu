@@ -5,8 +5,9 @@
 // Concat, Stack and Slice are one geometry: a "wide" tensor [outer, total] whose rows are the
 // concatenation of the rows of N "parts" [outer, width_k].  The reference launches one strided
 // copy per part; here one launch moves all parts (up to 16 per launch, longer lists chained).
-// Permute collapses dimensions that stay adjacent, then uses a shared-memory tile transpose when
-// what is left is a (batched) 2-D transpose and an index-arithmetic gather otherwise; no index
+// Permute collapses dimensions that stay adjacent, then transposes 32x32 tiles through shared
+// memory whenever the innermost dim changes (batched over the other dims) and uses an
+// index-arithmetic gather when the innermost dim stays (reads and writes both contiguous); no index
 // tables are uploaded (the reference copies three int arrays to the device per call).
 #include "common.cuh"
 
@@ -154,27 +155,49 @@ permute_gather_kernel(const float* __restrict__ x, float* y, int64_t count, cons
   y[i] = __ldg(x + src);
 }
 
-// Batched transpose [B, R, C] -> [B, C, R] through a 32x33 shared tile: both the reads and the
-// writes are 128-byte row segments.
+// Tile transpose for every permutation whose innermost output dim (a) is not the innermost input
+// dim (b): a block moves kTilesB tiles of 32 (along a) x 32 (along b) through shared memory, reading
+// 128-byte segments along b (contiguous in x) and writing 128-byte segments along a (contiguous in
+// y); all 4 * kTilesB loads of a thread are issued before the barrier.  The remaining dims are the
+// batch, decoded once per block.  NCHW <-> NHWC is the case with one batch dim.
+constexpr int kTilesB = 4;
+struct TileGeom {
+  int64_t A, Bn;               // extents of a and b
+  int64_t a_in_step, b_out_step;   // step of a in x, of b in y (a has step 1 in y, b step 1 in x)
+  int64_t tiles_a, tiles_b;    // tiles along a, groups of kTilesB tiles along b
+  int nbatch;
+  int64_t batch_ext[kMaxDims], batch_in_step[kMaxDims], batch_out_step[kMaxDims];
+};
+
 __global__ void __launch_bounds__(256)
-transpose_tile_kernel(const float* __restrict__ x, float* y, int64_t R, int64_t C, int64_t tiles_c, int64_t tiles_rc) {
-  __shared__ float tile[32][33];
-  const int64_t b = blockIdx.x / tiles_rc, t = blockIdx.x - b * tiles_rc;
-  const int64_t tr = t / tiles_c, tc = t - tr * tiles_c;
-  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-  const float* xb = x + b * R * C;
-  float* yb = y + b * R * C;
-#pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    const int64_t r = tr * 32 + ty + k * 8, c = tc * 32 + tx;
-    if (r < R && c < C) tile[ty + k * 8][tx] = ld_stream(xb + r * C + c);
+permute_tile_kernel(const float* __restrict__ x, float* y, const __grid_constant__ TileGeom g) {
+  __shared__ float tile[kTilesB][32][33];
+  int64_t rest = blockIdx.x;
+  const int64_t tb = rest % g.tiles_b; rest /= g.tiles_b;
+  const int64_t ta = rest % g.tiles_a; rest /= g.tiles_a;
+  int64_t in_base = 0, out_base = 0;
+  for (int d = g.nbatch - 1; d >= 0; --d) {
+    const int64_t idx = rest % g.batch_ext[d];
+    rest /= g.batch_ext[d];
+    in_base += idx * g.batch_in_step[d], out_base += idx * g.batch_out_step[d];
   }
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
+  const int64_t a0 = ta * 32, b0 = tb * 32 * kTilesB;
+#pragma unroll
+  for (int t = 0; t < kTilesB; ++t)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int64_t a = a0 + ty + k * 8, b = b0 + t * 32 + tx;
+      if (a < g.A && b < g.Bn) tile[t][ty + k * 8][tx] = ld_stream(x + in_base + a * g.a_in_step + b);
+    }
   __syncthreads();
 #pragma unroll
-  for (int k = 0; k < 4; ++k) {
-    const int64_t c = tc * 32 + ty + k * 8, r = tr * 32 + tx;
-    if (r < R && c < C) st_stream(yb + c * R + r, tile[tx][ty + k * 8]);
-  }
+  for (int t = 0; t < kTilesB; ++t)
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      const int64_t b = b0 + t * 32 + ty + k * 8, a = a0 + tx;
+      if (a < g.A && b < g.Bn) st_stream(y + out_base + b * g.b_out_step + a, tile[t][tx][ty + k * 8]);
+    }
 }
 
 // ---- Gather, Pad --------------------------------------------------------------------------------
@@ -285,26 +308,44 @@ int sb200_permute(const float* x, float* y, const int* in_shape, const int* orde
     if (e != cudaSuccess) return cuda_failure(e, "sb200_permute(copy)");
     return SB200_OK;
   }
-  // batched 2-D transpose: output dims (B,) C, R read with steps (R*C,) 1, C
-  const bool t2 = nd == 2 && src_step[0] == 1 && src_step[1] == ext[0];
-  const bool t3 = nd == 3 && src_step[0] == ext[1] * ext[2] && src_step[1] == 1 && src_step[2] == ext[1];
-  if (t2 || t3) {
-    const int64_t B = t3 ? ext[0] : 1, C = t3 ? ext[1] : ext[0], R = t3 ? ext[2] : ext[1];
-    const int64_t tiles_c = (C + 31) / 32, tiles_r = (R + 31) / 32;
-    const int64_t blocks = B * tiles_c * tiles_r;
-    if (blocks < (1ll << 31)) {
-      transpose_tile_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(x, y, R, C, tiles_c, tiles_c * tiles_r);
-      return after_launch("sb200_permute");
+  // output steps of the collapsed dims
+  int64_t out_step[kMaxDims];
+  {
+    int64_t st = 1;
+    for (int j = nd - 1; j >= 0; --j) { out_step[j] = st; st *= ext[j]; }
+  }
+  // innermost output dim a = nd - 1; if it is not the innermost input dim, transpose tiles of
+  // (a, b) with b the dim that has step 1 in x (one exists: the last input dim of extent > 1)
+  if (src_step[nd - 1] != 1) {
+    int jb = -1;
+    for (int j = 0; j < nd - 1; ++j)
+      if (src_step[j] == 1) jb = j;
+    if (jb >= 0) {
+      TileGeom g;
+      g.A = ext[nd - 1], g.Bn = ext[jb];
+      g.a_in_step = src_step[nd - 1], g.b_out_step = out_step[jb];
+      g.tiles_a = (g.A + 31) / 32, g.tiles_b = (g.Bn + 32 * kTilesB - 1) / (32 * kTilesB);
+      g.nbatch = 0;
+      int64_t blocks = g.tiles_a * g.tiles_b;
+      for (int j = 0; j < nd - 1; ++j) {
+        if (j == jb) continue;
+        g.batch_ext[g.nbatch] = ext[j], g.batch_in_step[g.nbatch] = src_step[j], g.batch_out_step[g.nbatch] = out_step[j];
+        ++g.nbatch;
+        blocks *= ext[j];
+      }
+      for (int d = g.nbatch; d < kMaxDims; ++d) g.batch_ext[d] = 1, g.batch_in_step[d] = 0, g.batch_out_step[d] = 0;
+      if (blocks < (1ll << 31)) {
+        permute_tile_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(x, y, g);
+        return after_launch("sb200_permute");
+      }
     }
   }
   PermGeom g;
   g.nd = nd;
-  int64_t ostep = 1;
   for (int j = nd - 1; j >= 0; --j) {
-    g.out_step[j] = static_cast<uint32_t>(ostep);
-    g.out_div[j] = FastDiv32(static_cast<uint32_t>(ostep));
+    g.out_step[j] = static_cast<uint32_t>(out_step[j]);
+    g.out_div[j] = FastDiv32(static_cast<uint32_t>(out_step[j]));
     g.in_step[j] = src_step[j];
-    ostep *= ext[j];
   }
   for (int j = nd; j < kMaxDims; ++j) { g.out_step[j] = 1; g.out_div[j] = FastDiv32(1); g.in_step[j] = 0; }
   const int64_t blocks = (count + kThreads - 1) / kThreads;

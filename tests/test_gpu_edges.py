@@ -208,3 +208,17 @@ def test_unaligned_data_movement(offset):
     bad = torch.tensor([9, -1, 2], dtype=torch.int32, device="cuda")   # out-of-range indexes give zeros, no fault
     got = F.gather(da, bad, 1).cpu().numpy()
     assert np.all(got[:, 0] == 0) and np.all(got[:, 1] == 0) and orc.bit_equal(got[:, 2], a[:, 2])
+
+
+def test_every_permutation_of_small_tensors():
+    """All 24 + 120 axis orders of a 4-d and a 5-d tensor (tile transposes, gathers and plain copies)."""
+    import itertools
+    from shadow_b200 import functional as F
+    torch = _torch()
+    for shape in ((3, 33, 5, 70), (2, 3, 35, 2, 40), (1, 9, 1, 64)):
+        x = cases.normal(95 + len(shape), shape)
+        dx = torch.from_numpy(x).cuda()
+        for order in itertools.permutations(range(len(shape))):
+            got = F.permute(dx, list(order)).cpu().numpy()
+            assert got.shape == tuple(shape[a] for a in order)
+            assert orc.bit_equal(got, np.ascontiguousarray(x.transpose(order))), (shape, order)
