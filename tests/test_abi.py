@@ -56,7 +56,29 @@ def test_bad_arguments_are_rejected_before_launch(lib):
     assert lib.sb200_reduce(256, shp, 2, capi.ints([1]), 1, 9, 512, None, 0, None) == 1  # unknown op
     assert lib.sb200_unary(258, 512, 16, 0, None) == 1              # not 4-byte aligned
     assert capi.launch_count() == before
+    # the operators added after the first six
+    import ctypes
+    ptrs = (ctypes.c_void_p * 2)(256, 512)
+    widths = (ctypes.c_int64 * 2)(4, 0)
+    assert lib.sb200_eltwise(ptrs, 1, None, 1024, 16, 1, None) == 1                     # needs two inputs
+    assert lib.sb200_axpy(256, 512, 768, 1024, 2, 0, None) == 1                        # inner < 1
+    assert lib.sb200_batch_norm(256, 512, 16, None, 1024, 4, 4, 1.0, 1e-5, None) == 1   # no mean
+    assert lib.sb200_normalize(256, 512, 2, 0, 4, 2.0, 1e-12, None) == 1                # dim < 1
+    assert lib.sb200_ssd_normalize(256, 512, 2, 0, 4, 1, 1e-5, None, 1, None) == 1
+    assert lib.sb200_row_norm(256, 512, 2, 8, 1e-5, None, None, 1, 1, 1, 1, None) == 1  # affine without scale
+    assert lib.sb200_row_norm(256, 512, 2, 8, 1e-5, 1024, 2048, 2, 2, 3, 2, None) == 1  # 3*2 != inner
+    assert lib.sb200_concat(ptrs, widths, 2, 1024, 3, None) == 1                        # a zero width
+    assert lib.sb200_slice(256, ptrs, widths, 2, 3, None) == 1
+    assert lib.sb200_permute(256, 512, shp, capi.ints([0, 0]), 2, None) == 1            # not a permutation
+    assert lib.sb200_permute(256, 256, shp, capi.ints([1, 0]), 2, None) == 1            # in place
+    assert lib.sb200_gather(256, None, 2, 1, 4, 3, 512, None) == 1                      # no indexes
+    assert lib.sb200_pad(256, 512, 2, 4, 4, capi.ints([-3, -3, 0, 0]), 0.0, None) == 1  # nothing left
+    three = capi.ints([1, 4, 4])
+    assert lib.sb200_pooling(256, 512, 2, three, three, capi.ints([1, 0, 2]), three, capi.ints([0, 0, 0]), 0, None) == 1
+    assert lib.sb200_pooling(256, 512, 2, three, three, three, three, capi.ints([0, 0, 0]), 2, None) == 1  # pool type
+    assert capi.launch_count() == before
     # zero-size calls succeed without launching
+    assert lib.sb200_concat(ptrs, widths, 2, None, 0, None) == 0
     assert lib.sb200_unary(None, None, 0, 0, None) == 0
     assert lib.sb200_fill(None, 0, 1.0, None) == 0
     assert capi.launch_count() == before
