@@ -6,7 +6,7 @@ Two artefacts:
 * ``oracle/liboracle_port.so``  - the plain-C restatement of the reference's CPU algorithms
   (``oracle/oracle_port.c``), always buildable (gcc only).
 * ``oracle/_ref/libshadow_ref.so`` - the reference's own CPU ``Default`` kernels, compiled from
-  the sources where they lie (``$SHADOW_REFERENCE_ROOT``, default ``/root/reference``) with no
+  the sources where they lie (the checkout named by ``$SHADOW_REFERENCE_ROOT``, or the default below) with no
   ``USE_*`` define (plain-loop kernels, glibc libm, no Eigen/DNNL/NNPACK, CPUContext only),
   plus the C adapter ``shadow_b200/host/net_capi.cpp`` compiled against the reference's headers
   with the symbol prefix ``sref_``.  Built only when the reference tree is present; a machine
