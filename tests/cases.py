@@ -289,9 +289,9 @@ def small_cases():
     cs.append(_case("softmax_cluster4_wide", "Softmax", {"axis": 1}, [normal(1110, (2, 100, 300))]))
     cs.append(_case("softmax_plane_two_pass", "Softmax", {"axis": 1}, [normal(1111, (2, 300, 300), 0.0, 3.0)]))
     cs.append(_case("softmax_inner2", "Softmax", {"axis": 0}, [normal(1112, (700, 2))]))
-    # shared-memory patch geometries: packed tiny planes (odd and 4-aligned plane sizes), column
-    # tiles with 16-byte and 4-byte copies, a ragged last tile, a patch that needs the 1024-thread
-    # block, and a channel count too large for any patch (plane kernel)
+    # strided-softmax block geometries: several tiny planes packed into one block (odd and 4-aligned
+    # plane sizes), inner extents above one column tile (256) with and without a ragged last tile,
+    # a [900, 52] plane (512-thread blocks), and a long channel axis with a narrow inner extent
     cs.append(_case("softmax_patch_packed_odd", "Softmax", {"axis": 1}, [normal(1113, (11, 7, 3, 3))]))
     cs.append(_case("softmax_patch_packed_vec", "Softmax", {"axis": 1}, [normal(1114, (13, 8, 10))]))
     cs.append(_case("softmax_patch_tiles_vec", "Softmax", {"axis": 1}, [normal(1115, (2, 21, 520), 0.0, 3.0)]))
