@@ -64,6 +64,21 @@ int SHADOW_CAPI(net_add_blob)(void* net, const char* name, int ndim, const int* 
  * (the protobuf-free model text format, shadow/util/io.hpp:47-52, shadow/core/parser.cpp:1844-1917). */
 int SHADOW_CAPI(net_parse_text)(void* net, const char* text);
 
+#ifdef SHADOW_CAPI_PRODUCT_EXTENSIONS
+/* Only in this repository's build of the adapter (the reference's protobuf-free build has no binary
+ * reader to compare with).
+ * net_parse_binary: replace the NetParam under construction by the one decoded from a protobuf
+ * binary model (IO::ReadProtoFromArray); with `network` >= 0 the bytes are a MetaNetParam and that
+ * network of it is taken.
+ * net_dump: write a line-based description of the NetParam under construction into `buf` (at most
+ * `cap` bytes including the terminator) and return the length it needs; floats are written as C99
+ * hexadecimal literals so that they compare exactly.  Lines:
+ *   net <name> / netarg|arg <name> <kind> <values...> / blob <name> <type> <ndim> <dims...> <n data_f> <values...>
+ *   / op <type> <name> <n bottoms> <bottoms...> <n tops> <tops...> <n args>  (its arg lines follow). */
+int SHADOW_CAPI(net_parse_binary)(void* net, const void* data, int size, int network);
+int SHADOW_CAPI(net_dump)(void* net, char* buf, int cap);
+#endif
+
 /* Network::LoadXModel with backend arguments backend_type / device_id and the net
  * argument out_blob (mandatory, shadow/backends/native/native.cpp:186-188). */
 int SHADOW_CAPI(net_load)(void* net, const char* backend_type, int device_id, int n_out,

@@ -84,7 +84,9 @@ def build_host(force: bool = False) -> str | None:
     os.makedirs(LIB_DIR, exist_ok=True)
     os.makedirs(OBJ_DIR, exist_ok=True)
     cuda_home = os.path.dirname(os.path.dirname(_nvcc()))
-    flags = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-I" + os.path.join(HOST, "shadow"),
+    # SHADOW_CAPI_PRODUCT_EXTENSIONS: adapter entry points that exist only on this library's side
+    # (binary model parsing, NetParam dump); the reference-side build of the adapter omits them
+    flags = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-DSHADOW_CAPI_PRODUCT_EXTENSIONS", "-I" + os.path.join(HOST, "shadow"),
              "-I" + os.path.join(REPO, "include"), "-I" + os.path.join(cuda_home, "include")]
 
     def one(src):

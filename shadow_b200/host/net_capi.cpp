@@ -11,6 +11,7 @@
 #include "core/network.hpp"
 #include "util/io.hpp"
 
+#include <cstdio>
 #include <cstring>
 #include <exception>
 #include <map>
@@ -135,6 +136,67 @@ int SHADOW_CAPI(net_parse_text)(void* net, const char* text) {
     handle->param = parsed;
   });
 }
+
+#ifdef SHADOW_CAPI_PRODUCT_EXTENSIONS
+int SHADOW_CAPI(net_parse_binary)(void* net, const void* data, int size, int network) {
+  return guarded([&] {
+    auto* handle = static_cast<NetHandle*>(net);
+    if (handle == nullptr || data == nullptr || size < 0) throw std::runtime_error("net_parse_binary: bad argument");
+    if (network < 0) {
+      shadow::NetParam parsed;
+      Shadow::IO::ReadProtoFromArray(data, size, &parsed);
+      handle->param = parsed;
+    } else {
+      shadow::MetaNetParam meta;
+      Shadow::IO::ReadProtoFromArray(data, size, &meta);
+      if (network >= meta.network_size()) throw std::runtime_error("net_parse_binary: the file holds fewer networks");
+      handle->param = meta.network(network);
+    }
+  });
+}
+
+int SHADOW_CAPI(net_dump)(void* net, char* buf, int cap) {
+  auto* handle = static_cast<NetHandle*>(net);
+  if (handle == nullptr) return -1;
+  std::string out;
+  char num[64];
+  auto hexf = [&](float v) { std::snprintf(num, sizeof(num), " %a", static_cast<double>(v)); out += num; };
+  auto dump_arg = [&](const char* word, const shadow::Argument& a) {
+    out += std::string(word) + " " + a.name();
+    if (a.has_s_f()) { out += " s_f"; hexf(a.s_f()); }
+    else if (a.has_s_i()) out += " s_i " + std::to_string(a.s_i());
+    else if (a.has_s_s()) out += " s_s " + a.s_s();
+    else if (a.v_f_size() > 0) { out += " v_f"; for (float v : a.v_f()) hexf(v); }
+    else if (a.v_s_size() > 0) { out += " v_s"; for (const auto& v : a.v_s()) out += " " + v; }
+    else { out += " v_i"; for (int v : a.v_i()) out += " " + std::to_string(v); }
+    out += "\n";
+  };
+  const auto& p = handle->param;
+  out += "net " + p.name() + "\n";
+  for (const auto& a : p.arg()) dump_arg("netarg", a);
+  for (const auto& b : p.blob()) {
+    out += "blob " + b.name() + " " + (b.has_type() ? b.type() : std::string("float")) + " " + std::to_string(b.shape_size());
+    for (int d : b.shape()) out += " " + std::to_string(d);
+    out += " " + std::to_string(b.data_f_size());
+    for (float v : b.data_f()) hexf(v);
+    out += "\n";
+  }
+  for (const auto& op : p.op()) {
+    out += "op " + op.type() + " " + op.name() + " " + std::to_string(op.bottom_size());
+    for (const auto& s : op.bottom()) out += " " + s;
+    out += " " + std::to_string(op.top_size());
+    for (const auto& s : op.top()) out += " " + s;
+    out += " " + std::to_string(op.arg_size()) + "\n";
+    for (const auto& a : op.arg()) dump_arg("arg", a);
+  }
+  if (buf != nullptr && cap > 0) {
+    const size_t n = out.size() < static_cast<size_t>(cap - 1) ? out.size() : static_cast<size_t>(cap - 1);
+    std::memcpy(buf, out.data(), n);
+    buf[n] = 0;
+  }
+  return static_cast<int>(out.size() + 1);
+}
+#endif
 
 int SHADOW_CAPI(net_load)(void* net, const char* backend_type, int device_id, int n_out,
                           const char* const* out_blobs) {

@@ -95,6 +95,13 @@ class NetParam {
   SB_LIST_FIELD(arg, Argument)
 };
 
+// shadow/proto/shadow.proto:41-47: several networks in one file
+class MetaNetParam {
+  SB_SCALAR_FIELD(name, std::string)
+  SB_LIST_FIELD(network, NetParam)
+  SB_LIST_FIELD(arg, Argument)
+};
+
 #undef SB_SCALAR_FIELD
 #undef SB_LIST_FIELD
 
@@ -516,6 +523,13 @@ class Network {
 namespace IO {
 bool ReadProtoFromText(const std::string& proto_text, shadow::NetParam* proto);
 bool ReadProtoFromTextFile(const std::string& proto_file, shadow::NetParam* proto);
+// Protobuf binary models (shadow/util/io.hpp:20-27; messages of shadow/proto/shadow.proto), decoded
+// without a protobuf runtime.  Throw (CHECK) on malformed input; the file forms return false when the
+// file cannot be opened.
+bool ReadProtoFromArray(const void* proto_data, int proto_size, shadow::NetParam* proto);
+bool ReadProtoFromArray(const void* proto_data, int proto_size, shadow::MetaNetParam* proto);
+bool ReadProtoFromBinaryFile(const std::string& proto_file, shadow::NetParam* proto);
+bool ReadProtoFromBinaryFile(const std::string& proto_file, shadow::MetaNetParam* proto);
 }  // namespace IO
 
 }  // namespace Shadow

@@ -43,6 +43,9 @@ class NetLibrary:
                                   C.POINTER(C.c_double), C.POINTER(C.c_char_p)])
         f("net_add_blob", C.c_int, [C.c_void_p, C.c_char_p, C.c_int, C.POINTER(C.c_int), C.c_void_p])
         f("net_parse_text", C.c_int, [C.c_void_p, C.c_char_p])
+        if prefix == "sb200net_":     # extensions of this repository's build of the adapter
+            f("net_parse_binary", C.c_int, [C.c_void_p, C.c_char_p, C.c_int, C.c_int])
+            f("net_dump", C.c_int, [C.c_void_p, C.c_char_p, C.c_int])
         f("net_load", C.c_int, [C.c_void_p, C.c_char_p, C.c_int, C.c_int, C.POINTER(C.c_char_p)])
         f("net_forward", C.c_int, [C.c_void_p, C.c_int, C.POINTER(C.c_char_p), C.POINTER(C.c_void_p)])
         f("net_blob_shape", C.c_int, [C.c_void_p, C.c_char_p, C.POINTER(C.c_int), C.c_int])
@@ -175,6 +178,19 @@ class Net:
         (IO::ReadProtoFromText, shadow/util/io.hpp:47-52)."""
         self.L.check(self.L.net_parse_text(self.h, text.encode()), "net_parse_text")
         return self
+
+    def parse_binary(self, data: bytes, network: int = -1) -> "Net":
+        """Replace the net under construction by the one decoded from a protobuf binary model
+        (IO::ReadProtoFromArray); `network` >= 0 picks that network of a MetaNetParam."""
+        self.L.check(self.L.net_parse_binary(self.h, data, len(data), network), "net_parse_binary")
+        return self
+
+    def dump(self) -> str:
+        """Line-based description of the net under construction (floats as C99 hex literals)."""
+        need = self.L.net_dump(self.h, None, 0)
+        buf = C.create_string_buffer(need)
+        self.L.net_dump(self.h, buf, need)
+        return buf.value.decode()
 
     def load(self, backend_type: str = "Native", device_id: int = 0, out_blobs: Sequence[str] = ()) -> "Net":
         outs = list(out_blobs)

@@ -1,0 +1,188 @@
+"""Protobuf binary models: the reader in the host library (no protobuf runtime linked) against bytes
+produced by the official Python protobuf runtime for the reference's schema
+(shadow/proto/shadow.proto:5-47, rebuilt here as a descriptor - field numbers, types, labels and the
+packed options are the schema's).  Also checks that the reader and the text-format reader agree on
+the NetParam they produce (dump of one == dump of the other)."""
+import os
+import sys
+
+import numpy as np
+import pytest
+
+sys.path.insert(0, os.path.dirname(__file__))
+import cases  # noqa: E402
+from oracle import oracle as orc  # noqa: E402
+from shadow_b200.netapi import Net, ShadowError, model_text  # noqa: E402
+
+pb = pytest.importorskip("google.protobuf")
+from google.protobuf import descriptor_pb2, descriptor_pool, message_factory  # noqa: E402
+
+F = descriptor_pb2.FieldDescriptorProto
+
+
+def _schema():
+    fd = descriptor_pb2.FileDescriptorProto(name="shadow_test.proto", package="shadow", syntax="proto2")
+
+    def message(name, fields):
+        m = fd.message_type.add(name=name)
+        for fname, number, ftype, label, extra in fields:
+            f = m.field.add(name=fname, number=number, type=ftype, label=label)
+            if extra.get("packed"):
+                f.options.packed = True
+            if "msg" in extra:
+                f.type_name = ".shadow." + extra["msg"]
+    O, R = F.LABEL_OPTIONAL, F.LABEL_REPEATED
+    message("Blob", [("name", 1, F.TYPE_STRING, O, {}), ("type", 2, F.TYPE_STRING, O, {}), ("shape", 3, F.TYPE_INT32, R, {}),
+                     ("data_f", 4, F.TYPE_FLOAT, R, {"packed": True}), ("data_i", 5, F.TYPE_INT32, R, {"packed": True}),
+                     ("data_b", 6, F.TYPE_BYTES, R, {})])
+    message("Argument", [("name", 1, F.TYPE_STRING, O, {}), ("s_f", 2, F.TYPE_FLOAT, O, {}), ("s_i", 3, F.TYPE_INT32, O, {}),
+                         ("s_s", 4, F.TYPE_STRING, O, {}), ("v_f", 5, F.TYPE_FLOAT, R, {}), ("v_i", 6, F.TYPE_INT32, R, {}),
+                         ("v_s", 7, F.TYPE_STRING, R, {})])
+    message("OpParam", [("name", 1, F.TYPE_STRING, O, {}), ("type", 2, F.TYPE_STRING, O, {}), ("bottom", 3, F.TYPE_STRING, R, {}),
+                        ("top", 4, F.TYPE_STRING, R, {}), ("arg", 11, F.TYPE_MESSAGE, R, {"msg": "Argument"})])
+    message("NetParam", [("name", 1, F.TYPE_STRING, O, {}), ("blob", 5, F.TYPE_MESSAGE, R, {"msg": "Blob"}),
+                         ("op", 11, F.TYPE_MESSAGE, R, {"msg": "OpParam"}), ("arg", 12, F.TYPE_MESSAGE, R, {"msg": "Argument"})])
+    message("MetaNetParam", [("name", 1, F.TYPE_STRING, O, {}), ("network", 11, F.TYPE_MESSAGE, R, {"msg": "NetParam"}),
+                             ("arg", 12, F.TYPE_MESSAGE, R, {"msg": "Argument"})])
+    pool = descriptor_pool.DescriptorPool()
+    pool.Add(fd)
+    get = lambda n: message_factory.GetMessageClass(pool.FindMessageTypeByName("shadow." + n))   # noqa: E731
+    return get("NetParam"), get("MetaNetParam")
+
+
+NetParam, MetaNetParam = _schema()
+
+
+def _set_arg(arg, name, val):
+    arg.name = name
+    if isinstance(val, (bool, np.bool_, int, np.integer)):
+        arg.s_i = int(val)
+    elif isinstance(val, (float, np.floating)):
+        arg.s_f = float(np.float32(val))
+    elif isinstance(val, str):
+        arg.s_s = val
+    else:
+        seq = list(val)
+        if seq and all(isinstance(v, str) for v in seq):
+            arg.v_s.extend(seq)
+        elif seq and any(isinstance(v, (float, np.floating)) for v in seq):
+            arg.v_f.extend(float(np.float32(v)) for v in seq)
+        else:
+            arg.v_i.extend(int(v) for v in seq)
+
+
+def _message(name, ops, net_args=None, blobs=()):
+    net = NetParam(name=name)
+    for k, v in (net_args or {}).items():
+        _set_arg(net.arg.add(), k, v)
+    for bname, btype, shape, data in blobs:
+        b = net.blob.add(name=bname, type=btype)
+        b.shape.extend(shape)
+        if data is not None:
+            b.data_f.extend(float(v) for v in np.asarray(data, np.float32).ravel())
+    for op_type, op_name, bottoms, tops, args in ops:
+        op = net.op.add(name=op_name, type=op_type)
+        op.bottom.extend(bottoms)
+        op.top.extend(tops)
+        for k, v in args.items():
+            _set_arg(op.arg.add(), k, v)
+    return net
+
+
+def _lib():
+    import shadow_b200
+    return shadow_b200.host_library()
+
+
+GRAPH = [("Input", "input", [], ["x", "g"], {"x": [2, 3, 4], "g": [3]}),
+         ("Scale", "s", ["x", "g"], ["y"], {"axis": 1, "has_scale": True, "has_bias": False}),
+         ("Activate", "a", ["y"], ["z"], {"type": 2, "slope": 0.125}),
+         ("Reduce", "r", ["z"], ["out"], {"operation": 2, "axes": [0, 2], "keep_dims": False}),
+         ("Eltwise", "e", ["z", "z"], ["w"], {"operation": 1, "coeff": [0.5, -1.5]})]
+WEIGHT = ("w0", "float", [2, 2], np.array([[1.5, -2.25], [3e-7, 1e9]], np.float32))
+
+
+def test_reader_reproduces_every_field():
+    graph = list(GRAPH)
+    graph[3] = ("Reduce", "r", ["z"], ["out"], {"operation": 2, "axes": [0, -1], "keep_dims": False})   # parsed, never run
+    msg = _message("net-a", graph, {"out_blob": ["out", "w"], "note": "hello world", "version": 3, "ratio": 0.1},
+                   [WEIGHT, ("empty", "float", [4, 0], None)])
+    dump = Net(_lib(), "x").parse_binary(msg.SerializeToString()).dump().splitlines()
+    assert dump[0] == "net net-a"
+    assert "netarg out_blob v_s out w" in dump and "netarg note s_s hello world" in dump and "netarg version s_i 3" in dump
+    assert "netarg ratio s_f " + float(np.float32(0.1)).hex() in [" ".join(line.split()[:3] + [float.fromhex(line.split()[3]).hex()])
+                                                                   for line in dump if line.startswith("netarg ratio")]
+    blob = [line.split() for line in dump if line.startswith("blob w0")][0]
+    assert blob[2:6] == ["float", "2", "2", "2"] and blob[6] == "4"
+    assert [np.float32(float.fromhex(v)) for v in blob[7:]] == list(WEIGHT[3].ravel())
+    assert "blob empty float 2 4 0 0" in dump
+    ops = [line for line in dump if line.startswith("op ")]
+    assert ops == ["op Input input 0 2 x g 2", "op Scale s 2 x g 1 y 3", "op Activate a 1 y 1 z 2",
+                   "op Reduce r 1 z 1 out 3", "op Eltwise e 2 z z 1 w 2"]
+    assert "arg axes v_i 0 -1" in dump and "arg keep_dims s_i 0" in dump           # negative int32: 10-byte varint
+    slope = [line.split() for line in dump if line.startswith("arg slope")][0]
+    assert float.fromhex(slope[3]) == 0.125
+
+
+def test_packed_and_unpacked_repeated_scalars_are_both_accepted():
+    """A parser must take either encoding whatever the schema says: hand-encoded v_i (declared
+    unpacked) as a packed payload and data_f (declared packed) as single values."""
+    def varint(v):
+        v &= (1 << 64) - 1
+        out = b""
+        while True:
+            b = v & 0x7f
+            v >>= 7
+            out += bytes([b | (0x80 if v else 0)])
+            if not v:
+                return out
+    def ld(field, payload):
+        return varint(field << 3 | 2) + varint(len(payload)) + payload
+    arg = ld(1, b"axes") + ld(6, varint(5) + varint(-2) + varint(300))
+    op = ld(1, b"r") + ld(2, b"Reduce") + ld(3, b"x") + ld(4, b"y") + ld(11, arg)
+    blob = ld(1, b"w") + varint(3 << 3 | 0) + varint(2) + b"".join(varint(4 << 3 | 5) + np.float32(v).tobytes() for v in (1.5, -3.0))
+    unknown = varint(99 << 3 | 0) + varint(7) + ld(98, b"ignored")
+    net = ld(1, b"n") + unknown + ld(5, blob) + ld(11, op)
+    dump = Net(_lib(), "x").parse_binary(net).dump()
+    assert "arg axes v_i 5 -2 300" in dump
+    blob_line = [line.split() for line in dump.splitlines() if line.startswith("blob w ")][0]
+    assert blob_line[2:6] == ["float", "1", "2", "2"] and [float.fromhex(v) for v in blob_line[6:]] == [1.5, -3.0]
+
+
+def test_meta_net_and_errors():
+    meta = MetaNetParam(name="pack")
+    meta.network.add().CopyFrom(_message("first", GRAPH[:2]))
+    meta.network.add().CopyFrom(_message("second", GRAPH[:3]))
+    data = meta.SerializeToString()
+    assert Net(_lib(), "x").parse_binary(data, network=1).dump().startswith("net second\n")
+    with pytest.raises(ShadowError, match="fewer networks"):
+        Net(_lib(), "x").parse_binary(data, network=2)
+    good = _message("n", GRAPH).SerializeToString()
+    for cut in (1, len(good) // 2, len(good) - 1):
+        with pytest.raises(ShadowError):
+            Net(_lib(), "x").parse_binary(good[:cut])            # truncated payloads are refused, not read past
+
+
+def test_binary_and_text_readers_agree():
+    """The same graph through both readers (all arguments given, so the text format's own defaults
+    add nothing): identical NetParam apart from the text format's argument order."""
+    ops = [GRAPH[0], ("Reduce", "r", ["x"], ["out"], {"operation": 1, "axes": [2], "keep_dims": True}),
+           ("Softmax", "s", ["out"], ["p"], {"axis": 1})]
+    fill = {"net_args": {"from_text": 1}, "blobs": [("unused_blob", "float", [1])]}
+    a = Net(_lib(), "x").parse_text(model_text("n", ops, **fill)).dump()
+    b = Net(_lib(), "x").parse_binary(_message("n", ops, fill["net_args"], [("unused_blob", "float", [1], None)]).SerializeToString()).dump()
+    assert sorted(a.splitlines()) == sorted(b.splitlines())
+
+
+@pytest.mark.gpu
+def test_binary_model_runs_like_the_programmatic_net():
+    lib = _lib()
+    x, g = cases.normal(11, (2, 3, 4)), cases.normal(12, (3,))
+    msg = _message("n", GRAPH, blobs=[WEIGHT])
+    net = Net(lib, "n").parse_binary(msg.SerializeToString())
+    net.load("Native", out_blobs=["out", "w", "w0"])
+    net.forward({"x": x, "g": g})
+    z = orc.activate(orc.scale(x, 1, g, None), 2, np.float32(0.125))
+    assert orc.bit_equal(net.blob("out"), orc.reduce(z, 2, [0, 2], False))
+    assert orc.bit_equal(net.blob("w"), orc.eltwise([z, z], 1, [0.5, -1.5]))
+    assert orc.bit_equal(net.blob("w0"), WEIGHT[3])
