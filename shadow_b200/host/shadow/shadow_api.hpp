@@ -521,8 +521,13 @@ class Network {
 // this library does not have; ReadProtoFromTextFile returns false when the file cannot be opened.
 // ---------------------------------------------------------------------------------------------
 namespace IO {
+// ReadProtoFromText takes either text form: the line-based one (it starts with '[') or protobuf text
+// format (`.shadowtxt`, what TextFormat prints for shadow/proto/shadow.proto; shadow/util/io.hpp:20-22).
 bool ReadProtoFromText(const std::string& proto_text, shadow::NetParam* proto);
 bool ReadProtoFromTextFile(const std::string& proto_file, shadow::NetParam* proto);
+// protobuf text format only, for either top-level message
+bool ReadProtoFromProtoText(const std::string& proto_text, shadow::NetParam* proto);
+bool ReadProtoFromProtoText(const std::string& proto_text, shadow::MetaNetParam* proto);
 // Protobuf binary models (shadow/util/io.hpp:20-27; messages of shadow/proto/shadow.proto), decoded
 // without a protobuf runtime.  Throw (CHECK) on malformed input; the file forms return false when the
 // file cannot be opened.

@@ -211,6 +211,10 @@ namespace IO {
 
 bool ReadProtoFromText(const std::string& proto_text, shadow::NetParam* proto) {
   CHECK_NOTNULL(proto);
+  // the line-based format opens with "[net name]"; protobuf text format opens with a field name
+  const auto first = proto_text.find_first_not_of(" \t\r\n");
+  if (first != std::string::npos && proto_text[first] != '[') return ReadProtoFromProtoText(proto_text, proto);
+  *proto = shadow::NetParam();
   parse_net(proto_text, proto);
   return true;
 }

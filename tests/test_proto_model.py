@@ -174,6 +174,37 @@ def test_binary_and_text_readers_agree():
     assert sorted(a.splitlines()) == sorted(b.splitlines())
 
 
+def test_protobuf_text_format_reader_agrees_with_the_binary_reader():
+    """`.shadowtxt`: every way the official runtime prints the message (multi-line, one line, short
+    repeated form, floats at full precision) parses to the NetParam the binary reader gives."""
+    from google.protobuf import text_format
+    graph = list(GRAPH)
+    graph[3] = ("Reduce", "r", ["z"], ["out"], {"operation": 2, "axes": [0, -1], "keep_dims": False})
+    msg = _message("net \"quoted\" \\ name\n2nd line", graph, {"out_blob": ["out", "w"], "note": "tab\there 'single' \x01", "ratio": 0.1},
+                   [WEIGHT, ("empty", "float", [4, 0], None)])
+    want = Net(_lib(), "x").parse_binary(msg.SerializeToString()).dump()
+    variants = [text_format.MessageToString(msg), text_format.MessageToString(msg, as_one_line=True),
+                text_format.MessageToString(msg, use_short_repeated_primitives=True),
+                text_format.MessageToString(msg, pointy_brackets=True), text_format.MessageToString(msg, as_utf8=True)]
+    for text in variants:
+        assert Net(_lib(), "x").parse_text(text).dump() == want, text[:200]
+    hand = """
+      # hand-written, with the looser forms the grammar allows
+      name: "n"   op: { type: 'Unary' name: "u" bottom: "a", top: "b"; arg < name: "operation" s_i: 0x4 > }
+      op { name: "s" type: "Scale" bottom: ["b"] top: "c"
+           arg { name: "scale_value" v_f: [1.5f, -2e-3, inf] } arg { name: "axis" s_i: -1 } }
+      blob { name: "w" "0" shape: [2, 1] data_f: 1 data_f: 2.5 }
+    """
+    dump = Net(_lib(), "x").parse_text(hand).dump().splitlines()
+    assert "op Unary u 1 a 1 b 1" in dump and "arg operation s_i 4" in dump and "arg axis s_i -1" in dump
+    sv = [line.split() for line in dump if line.startswith("arg scale_value")][0]
+    assert [float.fromhex(v) for v in sv[3:]] == [1.5, float(np.float32(-2e-3)), float("inf")]
+    assert [line for line in dump if line.startswith("blob w0 float 2 2 1 2")]
+    for bad in ('name: "n" bogus: 1', 'op { name: "x" ', 'op { name: x }', 'arg { s_i: 99999999999 }'):
+        with pytest.raises(ShadowError):
+            Net(_lib(), "x").parse_text(bad)
+
+
 @pytest.mark.gpu
 def test_binary_model_runs_like_the_programmatic_net():
     lib = _lib()
