@@ -217,3 +217,88 @@ def test_binary_model_runs_like_the_programmatic_net():
     assert orc.bit_equal(net.blob("out"), orc.reduce(z, 2, [0, 2], False))
     assert orc.bit_equal(net.blob("w"), orc.eltwise([z, z], 1, [0.5, -1.5]))
     assert orc.bit_equal(net.blob("w0"), WEIGHT[3])
+
+
+def _expected_dump(msg):
+    """What Net.dump() must print for `msg`, computed from the message itself."""
+    def arg(word, a):
+        if a.HasField("s_f"):
+            return [word, a.name, "s_f", float(a.s_f).hex()]
+        if a.HasField("s_i"):
+            return [word, a.name, "s_i", str(a.s_i)]
+        if a.HasField("s_s"):
+            return [word, a.name, "s_s", a.s_s]
+        if len(a.v_f):
+            return [word, a.name, "v_f"] + [float(v).hex() for v in a.v_f]
+        if len(a.v_s):
+            return [word, a.name, "v_s"] + list(a.v_s)
+        return [word, a.name, "v_i"] + [str(v) for v in a.v_i]
+    lines = [["net", msg.name]]
+    lines += [arg("netarg", a) for a in msg.arg]
+    for b in msg.blob:
+        lines.append(["blob", b.name, b.type if b.HasField("type") else "float", str(len(b.shape))] + [str(d) for d in b.shape] +
+                     [str(len(b.data_f))] + [float(v).hex() for v in b.data_f])
+    for op in msg.op:
+        lines.append(["op", op.type, op.name, str(len(op.bottom))] + list(op.bottom) + [str(len(op.top))] + list(op.top) +
+                     [str(len(op.arg))])
+        lines += [arg("arg", a) for a in op.arg]
+    return lines
+
+
+def _normalise(dump):
+    out = []
+    for line in dump.splitlines():
+        tok = line.split(" ")
+        if tok[0] in ("arg", "netarg") and tok[2] in ("s_f", "v_f"):
+            tok = tok[:3] + [float.fromhex(t).hex() for t in tok[3:]]
+        if tok[0] == "blob":
+            nd = int(tok[3])
+            tok = tok[:5 + nd] + [float.fromhex(t).hex() for t in tok[5 + nd:]]
+        out.append(tok)
+    return out
+
+
+def test_random_messages_through_both_protobuf_readers():
+    """Seeded random NetParams (names without spaces, so that the dump tokenises): the official
+    encoder's bytes and the official text printer's output both decode to exactly the message."""
+    from google.protobuf import text_format
+    rng = np.random.Generator(np.random.PCG64(2024))
+    word = lambda: "".join(rng.choice(list("abcXYZ_019/.-"), size=int(rng.integers(1, 9))))   # noqa: E731
+    f32 = lambda: float(np.float32(rng.choice([0.0, -0.0, 1.0, 1e-38, 3.4e38, -2.5, 1 / 3, 1e-45, 123456.789])))   # noqa: E731
+    i32 = lambda: int(rng.choice([0, 1, -1, 127, 128, -129, 2 ** 31 - 1, -2 ** 31, 300, 65536]))   # noqa: E731
+
+    def fill(a):
+        a.name = word()
+        kind = int(rng.integers(0, 6))
+        if kind == 0:
+            a.s_f = f32()
+        elif kind == 1:
+            a.s_i = i32()
+        elif kind == 2:
+            a.s_s = word()
+        elif kind == 3:
+            a.v_f.extend(f32() for _ in range(int(rng.integers(1, 5))))
+        elif kind == 4:
+            a.v_i.extend(i32() for _ in range(int(rng.integers(1, 5))))
+        else:
+            a.v_s.extend(word() for _ in range(int(rng.integers(1, 4))))
+    for _ in range(40):
+        msg = NetParam(name=word())
+        for _ in range(int(rng.integers(0, 4))):
+            fill(msg.arg.add())
+        for _ in range(int(rng.integers(0, 3))):
+            b = msg.blob.add(name=word())
+            if rng.integers(0, 2):
+                b.type = word()
+            b.shape.extend(int(rng.integers(0, 5)) for _ in range(int(rng.integers(0, 4))))
+            b.data_f.extend(f32() for _ in range(int(rng.integers(0, 6))))
+        for _ in range(int(rng.integers(0, 5))):
+            op = msg.op.add(name=word(), type=word())
+            op.bottom.extend(word() for _ in range(int(rng.integers(0, 3))))
+            op.top.extend(word() for _ in range(int(rng.integers(0, 3))))
+            for _ in range(int(rng.integers(0, 4))):
+                fill(op.arg.add())
+        want = _expected_dump(msg)
+        assert _normalise(Net(_lib(), "x").parse_binary(msg.SerializeToString()).dump()) == want
+        if len(msg.arg) or len(msg.blob) or len(msg.op):   # an otherwise empty message prints as one name line, also fine
+            assert _normalise(Net(_lib(), "x").parse_text(text_format.MessageToString(msg)).dump()) == want
