@@ -25,6 +25,7 @@
 #include <mutex>
 #include <type_traits>
 
+#include "colwalk.cuh"
 #include "common.cuh"
 #include "math.cuh"
 
@@ -374,6 +375,67 @@ redB_kernel(const float* __restrict__ x, float* y, double* part, const __grid_co
   }
 }
 
+// Inner-kept family on the fixed-column 128-bit walk (colwalk.cuh): x viewed as [K0, R, K1] is a
+// stack of K0 planes; every access is a float4 whatever K1 is (K1 = 196: no idle lanes, where the
+// TX-lane tiles of redB_kernel leave 7 of 56 idle), a thread's four lanes are four fixed columns,
+// and the block combines the partial rows of a column through shared memory in row order.  Used
+// when the planes alone give enough blocks (no split of R over blocks).
+template <int OP, int U, bool TO_PART>
+__global__ void __launch_bounds__(640, 2)
+redC_kernel(const float* __restrict__ x, float* y, double* part, const __grid_constant__ ColWalk q, int64_t n_out,
+            Divisor count) {
+  using R = RedOp<OP>;
+  using Acc = typename R::Acc;
+  extern __shared__ double sm_raw[];
+  Acc* sm = reinterpret_cast<Acc*>(sm_raw);   // [blockDim * 4]
+  const ColLane L = colwalk_thread(q, threadIdx.x, blockIdx.x);
+  const float4* ptr = reinterpret_cast<const float4*>(x) + L.first4;
+  const int64_t step = L.step4;
+  const int cnt = L.cnt;
+  Acc acc[4] = {R::init(), R::init(), R::init(), R::init()};
+  auto take = [&](const float4& v) {
+    acc[0] = R::step(acc[0], v.x), acc[1] = R::step(acc[1], v.y);
+    acc[2] = R::step(acc[2], v.z), acc[3] = R::step(acc[3], v.w);
+  };
+  int k = 0;
+  for (; k + U <= cnt; k += U, ptr += U * step) {
+    float4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) v[u] = ld_stream(ptr + u * step);
+#pragma unroll
+    for (int u = 0; u < U; ++u) take(v[u]);
+  }
+  if (k < cnt) {
+    float4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (k + u < cnt) v[u] = ld_stream(ptr + u * step);
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (k + u < cnt) take(v[u]);
+  }
+  if (L.slot >= 0) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) sm[L.slot + e] = acc[e];
+  }
+  __syncthreads();
+  const int planes = q.tiled ? 1 : q.P;
+  const int plane_slots = 4 * q.tact;
+  const int64_t tile_n = blockIdx.x / q.ntile, tile = blockIdx.x - tile_n * q.ntile;
+  const int64_t K1 = q.tiled ? q.row4 * 4 : q.ncols;
+  for (int c = threadIdx.x; c < planes * q.ncols; c += blockDim.x) {
+    const int pl = static_cast<int>(q.div_ncols.div(static_cast<uint32_t>(c)));
+    const int cc = c - pl * q.ncols;
+    const int64_t n = q.tiled ? tile_n : static_cast<int64_t>(blockIdx.x) * q.P + pl;
+    const int64_t col = q.tiled ? tile * q.ncols + cc : cc;
+    if (n >= q.outer || col >= K1) continue;
+    const Acc* p = sm + pl * plane_slots + cc;
+    Acc a = p[0];
+    for (int r = 1; r < q.R; ++r) a = R::merge(a, p[r * q.ncols]);
+    emit<OP, TO_PART>(a, y, part, n * K1 + col, 0, n_out, count);
+  }
+}
+
 // ---- generic: any alternation of kept / reduced dims ----------------------------------------------
 struct GeomG {
   int nk, nr;                                  // kept / reduced dim counts (outermost first)
@@ -441,6 +503,8 @@ struct Plan {
   bool a_rows;        // family A: staged short-rows kernel
   int rows_per_block;
   int tx;             // family B
+  bool b_colwalk;     // family B on the fixed-column walk
+  ColWalk cw;
   int64_t splits;
   int64_t n_out, n_red;
   GeomA a;
@@ -473,7 +537,7 @@ int make_plan(const int* in_shape, int num_axes, const int* axes, int n_axes, co
   }
   if (nd > kMaxDims) return SB200_ERR_UNSUPPORTED;
   P->n_out = n_out, P->n_red = n_red, P->splits = 1, P->scratch_bytes = 0, P->vec = false;
-  P->a_warp = false, P->a_rows = false, P->rows_per_block = 1, P->tx = 32;
+  P->a_warp = false, P->a_rows = false, P->rows_per_block = 1, P->tx = 32, P->b_colwalk = false;
   const Divisor count(static_cast<double>(n_red));
   const int64_t target_blocks = static_cast<int64_t>(sm_count()) * 8;
 
@@ -565,6 +629,11 @@ int make_plan(const int* in_shape, int num_axes, const int* axes, int n_axes, co
     splits = (Rm + chunk - 1) / chunk;
     g.r_chunk = chunk;
     P->splits = splits;
+    // the 128-bit walk when the planes alone fill the machine twice over (no split of R)
+    ColWalk cw;
+    if (K1 >= 2 && plan_colwalk(x, x, K0, Rm, K1, &cw, false) && cw.grid >= 2u * static_cast<unsigned>(sm_count())) {
+      P->b_colwalk = true, P->cw = cw, P->vec = true, P->splits = 1;
+    }
   } else {
     GeomG& g = P->gen;
     g.nk = g.nr = 0;
@@ -601,6 +670,9 @@ void launch_stage1(const Plan& P, const float* x, float* y, double* part, cudaSt
       if (P.vec) redA_block_kernel<OP, true, TO_PART><<<grid, kThreads, 0, s>>>(x, y, part, P.a);
       else redA_block_kernel<OP, false, TO_PART><<<grid, kThreads, 0, s>>>(x, y, part, P.a);
     }
+  } else if (P.family == kFamB && P.b_colwalk) {
+    const size_t smem = colwalk_smem(P.cw, sizeof(typename RedOp<OP>::Acc));
+    redC_kernel<OP, 4, TO_PART><<<P.cw.grid, P.cw.threads, smem, s>>>(x, y, part, P.cw, P.n_out, P.b.count);
   } else if (P.family == kFamB) {
     dim3 grid(static_cast<unsigned>(P.b.nbx * P.b.K0), static_cast<unsigned>(P.splits));
 #define SB200_LAUNCH_B(TXV)                                                                          \

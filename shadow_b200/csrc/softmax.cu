@@ -22,6 +22,7 @@
 // tolerance of 1e-5*log2(n) relative).  Algorithmic bytes: 8 per element.
 #include <float.h>
 
+#include "colwalk.cuh"
 #include "common.cuh"
 #include "math.cuh"
 
@@ -237,6 +238,130 @@ softmax_plane_kernel(const float* x, float* y, int64_t outer, int dim, int64_t i
   }
 }
 
+// Strided softmax on the fixed-column 128-bit walk (colwalk.cuh): every load and store is a float4,
+// a thread's four lanes stay on four fixed columns, and per element the instruction stream is
+//   pass 1: max within a batch of U float4, one re-reference of the running sum per lane and batch,
+//           then subtract, multiply, 2^x (hardware unit: the sum only feeds the denominator), add;
+//   merge:  column maxima through shared memory, every thread re-references its own four sums with
+//           expf (in parallel), column sums in partial-row order, one correctly rounded reciprocal;
+//   pass 2: the float4 again (from L2: the block read its patch a moment ago), subtract, the
+//           compensated 2^x of exp_nonpos, multiply, one float4 store.
+// About 16 instructions per element against 32-36 for the 4-byte walk of softmax_plane_kernel.
+template <int U>
+__global__ void __launch_bounds__(1024, 1)
+softmax_colvec_kernel(const float* x, float* y, const __grid_constant__ ColWalk q) {
+  extern __shared__ float sm_dyn[];
+  float* sm_m = sm_dyn;                       // [blockDim * 4]
+  float* sm_l = sm_dyn + blockDim.x * 4;      // [blockDim * 4]
+  const ColLane L = colwalk_thread(q, threadIdx.x, blockIdx.x);
+  const float4* xp = reinterpret_cast<const float4*>(x) + L.first4;
+  float4* yp = reinterpret_cast<float4*>(y) + L.first4;
+  const int64_t step = L.step4;
+  const int cnt = L.cnt;
+  constexpr float kLog2e = 1.4426950408889634f;
+  auto exp2_fast = [](float d) {
+    float r;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d));
+    return r;
+  };
+  float m[4] = {-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX}, l[4] = {0.f, 0.f, 0.f, 0.f};
+  auto batch = [&](const float4 (&v)[U]) {
+    float a[4][U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) a[0][u] = v[u].x, a[1][u] = v[u].y, a[2][u] = v[u].z, a[3][u] = v[u].w;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float bm = a[e][0];
+#pragma unroll
+      for (int u = 1; u < U; ++u) bm = fmaxf(bm, a[e][u]);
+      const float nm = fmaxf(m[e], bm);
+      l[e] = l[e] * exp2_fast((m[e] - nm) * kLog2e);   // 1 when the maximum stays
+      m[e] = nm;
+#pragma unroll
+      for (int u = 0; u < U; ++u) l[e] = l[e] + exp2_fast((a[e][u] - nm) * kLog2e);
+    }
+  };
+  {
+    const float4* p = xp;
+    int k = 0;
+    for (; k + U <= cnt; k += U, p += U * step) {
+      float4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u) v[u] = p[u * step];   // default caching: stays in L2 for pass 2
+      batch(v);
+    }
+    if (k < cnt) {   // last, partial batch: absent float4 read as -inf (their 2^x is 0)
+      float4 v[U];
+#pragma unroll
+      for (int u = 0; u < U; ++u)
+        v[u] = (k + u < cnt) ? p[u * step] : make_float4(-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F);
+      batch(v);
+    }
+  }
+  if (L.slot >= 0) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) sm_m[L.slot + e] = m[e];
+  }
+  __syncthreads();
+  // column maxima: one thread per (plane, column), partial rows in order; result left in row 0
+  const int planes = q.tiled ? 1 : q.P;
+  const int plane_slots = 4 * q.tact;
+  for (int c = threadIdx.x; c < planes * q.ncols; c += blockDim.x) {
+    const int pl = static_cast<int>(q.div_ncols.div(static_cast<uint32_t>(c)));
+    float* col = sm_m + pl * plane_slots + (c - pl * q.ncols);
+    float M = col[0];
+    for (int r = 1; r < q.R; ++r) M = std_max(col[r * q.ncols], M);
+    col[0] = M;
+  }
+  // a column's row-0 slot is overwritten only after its own thread read it, and other threads read
+  // rows >= 1 of it never: no race inside the loop above; the barrier publishes row 0
+  __syncthreads();
+  float M[4];
+  if (L.slot >= 0) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      M[e] = sm_m[L.plane_base + colwalk_col(q, L, e)];
+      sm_l[L.slot + e] = __fmul_rn(l[e], expf(__fsub_rn(m[e], M[e])));
+    }
+  }
+  __syncthreads();
+  for (int c = threadIdx.x; c < planes * q.ncols; c += blockDim.x) {
+    const int pl = static_cast<int>(q.div_ncols.div(static_cast<uint32_t>(c)));
+    float* col = sm_l + pl * plane_slots + (c - pl * q.ncols);
+    float S = col[0];
+    for (int r = 1; r < q.R; ++r) S = __fadd_rn(S, col[r * q.ncols]);
+    col[0] = __frcp_rn(S);
+  }
+  __syncthreads();
+  if (cnt == 0) return;
+  float inv[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) inv[e] = sm_l[L.plane_base + colwalk_col(q, L, e)];
+  auto out4 = [&](const float4& v) {
+    return make_float4(__fmul_rn(exp_nonpos(__fsub_rn(v.x, M[0])), inv[0]), __fmul_rn(exp_nonpos(__fsub_rn(v.y, M[1])), inv[1]),
+                       __fmul_rn(exp_nonpos(__fsub_rn(v.z, M[2])), inv[2]), __fmul_rn(exp_nonpos(__fsub_rn(v.w, M[3])), inv[3]));
+  };
+  const float4* p = xp;
+  float4* o = yp;
+  int k = 0;
+  for (; k + U <= cnt; k += U, p += U * step, o += U * step) {
+    float4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u) v[u] = ld_stream(p + u * step);
+#pragma unroll
+    for (int u = 0; u < U; ++u) st_stream(o + u * step, out4(v[u]));
+  }
+  if (k < cnt) {
+    float4 v[U];
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (k + u < cnt) v[u] = ld_stream(p + u * step);
+#pragma unroll
+    for (int u = 0; u < U; ++u)
+      if (k + u < cnt) st_stream(o + u * step, out4(v[u]));
+  }
+}
+
 template <int TPR, int NV, bool VEC>
 void launch_rows(const float* x, float* y, int64_t rows, int units, cudaStream_t s) {
   constexpr int BLOCK = TPR < 256 ? 256 : TPR;
@@ -285,6 +410,12 @@ extern "C" int sb200_softmax(const float* x, float* y, int64_t outer, int64_t di
     return after_launch("sb200_softmax");
   }
   if (dim >= (1ll << 31)) return SB200_ERR_UNSUPPORTED;
+  ColWalk cw;
+  if (plan_colwalk(x, y, outer, dim, inner, &cw)) {
+    const size_t smem = 2 * colwalk_smem(cw, sizeof(float));
+    softmax_colvec_kernel<4><<<cw.grid, cw.threads, smem, s>>>(x, y, cw);
+    return after_launch("sb200_softmax");
+  }
   const int W = static_cast<int>(inner < 256 ? inner : 256);
   const int64_t ntile = (inner + W - 1) / W;
   // block size: 512 threads when every thread still gets full batches of rows, else 256
