@@ -124,10 +124,12 @@ __device__ __forceinline__ float norm_divisor(double sum, float p, float eps) {
 // The same operator on the fixed-column 128-bit walk (colwalk.cuh; inner > 1): float4 loads and
 // stores, four double accumulators per thread (one per lane = column), column sums through shared
 // memory in partial-row order, then the patch again from L2 and one float4 store per float4.
-template <int MODE, int SCALE, int U>
+template <int MODE, int SCALE, int U, int NB>
 __global__ void __launch_bounds__(1024, 1)
 normalize_colvec_kernel(const float* x, float* y, const __grid_constant__ ColWalk q, float p, float eps,
                         const __grid_constant__ SsdScale ssd) {
+  // during pass 1 the memory is the threads' copy rings (colwalk_stream); afterwards it holds the
+  // per-lane partial sums
   extern __shared__ double sm_sum[];   // [blockDim * 4]
   const ColLane L = colwalk_thread(q, threadIdx.x, blockIdx.x);
   const float4* xp = reinterpret_cast<const float4*>(x) + L.first4;
@@ -135,32 +137,17 @@ normalize_colvec_kernel(const float* x, float* y, const __grid_constant__ ColWal
   const int64_t step = L.step4;
   const int cnt = L.cnt;
   double acc[4] = {0.0, 0.0, 0.0, 0.0};
-  {
-    const float4* ptr = xp;
-    int k = 0;
-    for (; k + U <= cnt; k += U, ptr += U * step) {
-      float4 v[U];
+  colwalk_stream<U, NB>(xp, step, cnt, reinterpret_cast<float4*>(sm_sum) + threadIdx.x,
+                        [&](const float4 (&v)[U], int, int valid) {
 #pragma unroll
-      for (int u = 0; u < U; ++u) v[u] = ptr[u * step];   // default caching: stays in L2 for pass 2
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        acc[0] += norm_term<MODE>(v[u].x, p), acc[1] += norm_term<MODE>(v[u].y, p);
-        acc[2] += norm_term<MODE>(v[u].z, p), acc[3] += norm_term<MODE>(v[u].w, p);
-      }
-    }
-    if (k < cnt) {
-      float4 v[U];
-#pragma unroll
-      for (int u = 0; u < U; ++u) v[u] = (k + u < cnt) ? ptr[u * step] : make_float4(0.f, 0.f, 0.f, 0.f);
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        if (k + u < cnt) {
-          acc[0] += norm_term<MODE>(v[u].x, p), acc[1] += norm_term<MODE>(v[u].y, p);
-          acc[2] += norm_term<MODE>(v[u].z, p), acc[3] += norm_term<MODE>(v[u].w, p);
-        }
-      }
-    }
-  }
+                          for (int u = 0; u < U; ++u) {
+                            if (u < valid) {
+                              acc[0] += norm_term<MODE>(v[u].x, p), acc[1] += norm_term<MODE>(v[u].y, p);
+                              acc[2] += norm_term<MODE>(v[u].z, p), acc[3] += norm_term<MODE>(v[u].w, p);
+                            }
+                          }
+                        });
+  __syncthreads();   // all rings drained: the memory now takes the partials
   if (L.slot >= 0) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) sm_sum[L.slot + e] = acc[e];
@@ -321,7 +308,15 @@ bool try_norm_rows(const float* x, float* y, int64_t rows, int64_t dim, float p,
 
 template <int MODE, int SCALE>
 void launch_colvec(const float* x, float* y, const ColWalk& cw, float p, float eps, const SsdScale& ssd, cudaStream_t s) {
-  normalize_colvec_kernel<MODE, SCALE, 4><<<cw.grid, cw.threads, colwalk_smem(cw, sizeof(double)), s>>>(x, y, cw, p, eps, ssd);
+  constexpr int U = 4, NB = 2;
+  size_t smem = colwalk_smem(cw, sizeof(double));
+  if (smem < colwalk_ring_bytes(cw, U, NB)) smem = colwalk_ring_bytes(cw, U, NB);
+  static bool attr_set = false;   // per instantiation; racing first calls set the same value
+  if (!attr_set) {
+    cudaFuncSetAttribute(normalize_colvec_kernel<MODE, SCALE, U, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 1024 * U * NB * 16);
+    attr_set = true;
+  }
+  normalize_colvec_kernel<MODE, SCALE, U, NB><<<cw.grid, cw.threads, smem, s>>>(x, y, cw, p, eps, ssd);
 }
 
 struct PlaneGeo {

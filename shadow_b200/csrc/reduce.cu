@@ -380,40 +380,27 @@ redB_kernel(const float* __restrict__ x, float* y, double* part, const __grid_co
 // TX-lane tiles of redB_kernel leave 7 of 56 idle), a thread's four lanes are four fixed columns,
 // and the block combines the partial rows of a column through shared memory in row order.  Used
 // when the planes alone give enough blocks (no split of R over blocks).
-template <int OP, int U, bool TO_PART>
-__global__ void __launch_bounds__(640, 2)
+template <int OP, int U, int NB, bool TO_PART>
+__global__ void __launch_bounds__(512, 3)
 redC_kernel(const float* __restrict__ x, float* y, double* part, const __grid_constant__ ColWalk q, int64_t n_out,
             Divisor count) {
   using R = RedOp<OP>;
   using Acc = typename R::Acc;
   extern __shared__ double sm_raw[];
-  Acc* sm = reinterpret_cast<Acc*>(sm_raw);   // [blockDim * 4]
+  Acc* sm = reinterpret_cast<Acc*>(sm_raw);   // [blockDim * 4], after the walk (the ring lives here during it)
   const ColLane L = colwalk_thread(q, threadIdx.x, blockIdx.x);
-  const float4* ptr = reinterpret_cast<const float4*>(x) + L.first4;
-  const int64_t step = L.step4;
-  const int cnt = L.cnt;
   Acc acc[4] = {R::init(), R::init(), R::init(), R::init()};
-  auto take = [&](const float4& v) {
-    acc[0] = R::step(acc[0], v.x), acc[1] = R::step(acc[1], v.y);
-    acc[2] = R::step(acc[2], v.z), acc[3] = R::step(acc[3], v.w);
-  };
-  int k = 0;
-  for (; k + U <= cnt; k += U, ptr += U * step) {
-    float4 v[U];
+  colwalk_stream<U, NB>(reinterpret_cast<const float4*>(x) + L.first4, L.step4, L.cnt,
+                        reinterpret_cast<float4*>(sm_raw) + threadIdx.x, [&](const float4 (&v)[U], int, int valid) {
 #pragma unroll
-    for (int u = 0; u < U; ++u) v[u] = ld_stream(ptr + u * step);
-#pragma unroll
-    for (int u = 0; u < U; ++u) take(v[u]);
-  }
-  if (k < cnt) {
-    float4 v[U];
-#pragma unroll
-    for (int u = 0; u < U; ++u)
-      if (k + u < cnt) v[u] = ld_stream(ptr + u * step);
-#pragma unroll
-    for (int u = 0; u < U; ++u)
-      if (k + u < cnt) take(v[u]);
-  }
+                          for (int u = 0; u < U; ++u) {
+                            if (u < valid) {
+                              acc[0] = R::step(acc[0], v[u].x), acc[1] = R::step(acc[1], v[u].y);
+                              acc[2] = R::step(acc[2], v[u].z), acc[3] = R::step(acc[3], v[u].w);
+                            }
+                          }
+                        });
+  __syncthreads();   // every thread is done with its ring slots: the memory now holds the partials
   if (L.slot >= 0) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) sm[L.slot + e] = acc[e];
@@ -631,7 +618,7 @@ int make_plan(const int* in_shape, int num_axes, const int* axes, int n_axes, co
     P->splits = splits;
     // the 128-bit walk when the planes alone fill the machine twice over (no split of R)
     ColWalk cw;
-    if (K1 >= 2 && plan_colwalk(x, x, K0, Rm, K1, &cw, false) && cw.grid >= 2u * static_cast<unsigned>(sm_count())) {
+    if (K1 >= 2 && plan_colwalk(x, x, K0, Rm, K1, &cw, kWalkOnePass) && cw.grid >= 2u * static_cast<unsigned>(sm_count())) {
       P->b_colwalk = true, P->cw = cw, P->vec = true, P->splits = 1;
     }
   } else {
@@ -671,8 +658,15 @@ void launch_stage1(const Plan& P, const float* x, float* y, double* part, cudaSt
       else redA_block_kernel<OP, false, TO_PART><<<grid, kThreads, 0, s>>>(x, y, part, P.a);
     }
   } else if (P.family == kFamB && P.b_colwalk) {
-    const size_t smem = colwalk_smem(P.cw, sizeof(typename RedOp<OP>::Acc));
-    redC_kernel<OP, 4, TO_PART><<<P.cw.grid, P.cw.threads, smem, s>>>(x, y, part, P.cw, P.n_out, P.b.count);
+    constexpr int U = 2, NB = 3;
+    size_t smem = colwalk_smem(P.cw, sizeof(typename RedOp<OP>::Acc));
+    if (smem < colwalk_ring_bytes(P.cw, U, NB)) smem = colwalk_ring_bytes(P.cw, U, NB);
+    static bool attr_set = false;   // per instantiation; racing first calls set the same value
+    if (!attr_set) {
+      cudaFuncSetAttribute(redC_kernel<OP, U, NB, TO_PART>, cudaFuncAttributeMaxDynamicSharedMemorySize, 512 * U * NB * 16);
+      attr_set = true;
+    }
+    redC_kernel<OP, U, NB, TO_PART><<<P.cw.grid, P.cw.threads, smem, s>>>(x, y, part, P.cw, P.n_out, P.b.count);
   } else if (P.family == kFamB) {
     dim3 grid(static_cast<unsigned>(P.b.nbx * P.b.K0), static_cast<unsigned>(P.splits));
 #define SB200_LAUNCH_B(TXV)                                                                          \

@@ -238,128 +238,233 @@ softmax_plane_kernel(const float* x, float* y, int64_t outer, int dim, int64_t i
   }
 }
 
-// Strided softmax on the fixed-column 128-bit walk (colwalk.cuh): every load and store is a float4,
-// a thread's four lanes stay on four fixed columns, and per element the instruction stream is
-//   pass 1: max within a batch of U float4, one re-reference of the running sum per lane and batch,
-//           then subtract, multiply, 2^x (hardware unit: the sum only feeds the denominator), add;
-//   merge:  column maxima through shared memory, every thread re-references its own four sums with
-//           expf (in parallel), column sums in partial-row order, one correctly rounded reciprocal;
-//   pass 2: the float4 again (from L2: the block read its patch a moment ago), subtract, the
-//           compensated 2^x of exp_nonpos, multiply, one float4 store.
-// About 16 instructions per element against 32-36 for the 4-byte walk of softmax_plane_kernel.
+// ---- exponentials against an integer reference ---------------------------------------------------
+// softmax is invariant under a common shift of a column, and in the base-2 domain any shift works
+// as long as sum and numerators use it alike.  The kernels below therefore never subtract a float
+// maximum: a column's reference is an INTEGER c (about log2(e) * max), a term is
+// 2^(x*log2(e) - c) - one fused multiply-add and one pass through the hardware 2^x unit - and
+// partial sums taken against different references are brought together by exact powers of two.
+// Error of a term: the fused multiply-add rounds once at magnitude |x*log2(e) - c| (below 2^-19
+// absolute for the terms that matter, 6.6e-7 relative in the result) plus the unit's 2^-22: under
+// 1e-6 relative, a tenth of the softmax bar at its tightest (1e-5 for n = 2).  NaN stays NaN, -inf
+// gives 0.  The numerators carry a bias of 2^24 that the reciprocal of the sum takes back, so that
+// the unit (which flushes results below 2^-126) is exact down to 2^-150 and outputs in the
+// denormal range come out right.
+constexpr float kLog2eF = 1.4426950408889634f;
+constexpr float kNumeratorBias = 24.f;
+__device__ __forceinline__ float ex2_ftz(float t) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t));
+  return r;
+}
+// 2^d for an integer-valued float d <= 0, exact (0 below 2^-126).
+__device__ __forceinline__ float pow2_int(float d) {
+  const int k = static_cast<int>(fmaxf(d, -127.f));
+  return __int_as_float((127 + k) << 23);   // k = -127 gives +0
+}
+
+// Running (reference, sum) of one lane.  `take` adds a batch of U values: the reference moves up
+// (to the batch maximum, rounded to an integer) only when the batch would otherwise produce terms
+// above 2^8, which after the first batch is rare; a move rescales the sum by an exact power of two.
+struct LaneSum {
+  float c, l;
+  __device__ __forceinline__ void init() { c = -3.0e38f, l = 0.f; }
+};
+
+template <int U>
+__device__ __forceinline__ void lanes_take(LaneSum (&s)[4], const float4 (&v)[U]) {
+  float bm[4] = {v[0].x, v[0].y, v[0].z, v[0].w};
+#pragma unroll
+  for (int u = 1; u < U; ++u) bm[0] = fmaxf(bm[0], v[u].x), bm[1] = fmaxf(bm[1], v[u].y), bm[2] = fmaxf(bm[2], v[u].z), bm[3] = fmaxf(bm[3], v[u].w);
+  const float over = fmaxf(fmaxf(__fmaf_rn(bm[0], kLog2eF, -s[0].c), __fmaf_rn(bm[1], kLog2eF, -s[1].c)),
+                           fmaxf(__fmaf_rn(bm[2], kLog2eF, -s[2].c), __fmaf_rn(bm[3], kLog2eF, -s[3].c)));
+  if (over > 8.f) {   // one branch per batch; rarely taken after a thread's first batch
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      // never move down: a batch of small values must not blow the sum up
+      const float cn = fmaxf(s[e].c, rintf(fminf(__fmul_rn(bm[e], kLog2eF), 3.0e38f)));
+      s[e].l = __fmul_rn(s[e].l, pow2_int(__fsub_rn(s[e].c, cn)));
+      s[e].c = cn;
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < U; ++u) {
+    s[0].l = __fadd_rn(s[0].l, ex2_ftz(__fmaf_rn(v[u].x, kLog2eF, -s[0].c)));
+    s[1].l = __fadd_rn(s[1].l, ex2_ftz(__fmaf_rn(v[u].y, kLog2eF, -s[1].c)));
+    s[2].l = __fadd_rn(s[2].l, ex2_ftz(__fmaf_rn(v[u].z, kLog2eF, -s[2].c)));
+    s[3].l = __fadd_rn(s[3].l, ex2_ftz(__fmaf_rn(v[u].w, kLog2eF, -s[3].c)));
+  }
+}
+
+// Strided softmax on the fixed-column 128-bit walk (colwalk.cuh), two passes: every load and store
+// is a float4, a thread's four lanes stay on four fixed columns, offsets are 32-bit.
+//   pass 1: U float4 in flight per thread; per element one fused multiply-add, one 2^x, one add
+//           (lanes_take);
+//   merge:  column references (maximum of the lanes' integers), every thread brings its four sums to
+//           its columns' references by an exact power of two, column sums in a fixed order;
+//   pass 2: the float4 again (from L2: the block read its patch a moment ago), one fused
+//           multiply-add, one 2^x, one multiplication by the reciprocal of the sum, one float4 store.
 template <int U>
 __global__ void __launch_bounds__(1024, 1)
 softmax_colvec_kernel(const float* x, float* y, const __grid_constant__ ColWalk q) {
-  extern __shared__ float sm_dyn[];
-  float* sm_m = sm_dyn;                       // [blockDim * 4]
-  float* sm_l = sm_dyn + blockDim.x * 4;      // [blockDim * 4]
+  extern __shared__ float4 sm_dyn[];
+  float* sm_c = reinterpret_cast<float*>(sm_dyn);   // [blockDim * 4]
+  float* sm_l = sm_c + blockDim.x * 4;              // [blockDim * 4]
   const ColLane L = colwalk_thread(q, threadIdx.x, blockIdx.x);
   const float4* xp = reinterpret_cast<const float4*>(x) + L.first4;
   float4* yp = reinterpret_cast<float4*>(y) + L.first4;
-  const int64_t step = L.step4;
+  const uint32_t step = static_cast<uint32_t>(L.step4);   // a patch spans fewer than 2^31 float4
   const int cnt = L.cnt;
-  constexpr float kLog2e = 1.4426950408889634f;
-  auto exp2_fast = [](float d) {
-    float r;
-    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d));
-    return r;
-  };
-  float m[4] = {-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX}, l[4] = {0.f, 0.f, 0.f, 0.f};
-  auto batch = [&](const float4 (&v)[U]) {
-    float a[4][U];
+  const int full = cnt / U, rem = cnt - full * U;
+  LaneSum s[4];
 #pragma unroll
-    for (int u = 0; u < U; ++u) a[0][u] = v[u].x, a[1][u] = v[u].y, a[2][u] = v[u].z, a[3][u] = v[u].w;
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      float bm = a[e][0];
-#pragma unroll
-      for (int u = 1; u < U; ++u) bm = fmaxf(bm, a[e][u]);
-      const float nm = fmaxf(m[e], bm);
-      l[e] = l[e] * exp2_fast((m[e] - nm) * kLog2e);   // 1 when the maximum stays
-      m[e] = nm;
-#pragma unroll
-      for (int u = 0; u < U; ++u) l[e] = l[e] + exp2_fast((a[e][u] - nm) * kLog2e);
-    }
-  };
+  for (int e = 0; e < 4; ++e) s[e].init();
   {
-    const float4* p = xp;
-    int k = 0;
-    for (; k + U <= cnt; k += U, p += U * step) {
+    uint32_t off = 0;
+    for (int b = 0; b < full; ++b, off += U * step) {
       float4 v[U];
 #pragma unroll
-      for (int u = 0; u < U; ++u) v[u] = p[u * step];   // default caching: stays in L2 for pass 2
-      batch(v);
+      for (int u = 0; u < U; ++u) v[u] = xp[off + u * step];   // default caching: stays in L2 for pass 2
+      lanes_take<U>(s, v);
     }
-    if (k < cnt) {   // last, partial batch: absent float4 read as -inf (their 2^x is 0)
+    if (rem > 0) {   // last, partial batch: absent float4 read as -inf (their 2^x is 0)
       float4 v[U];
 #pragma unroll
       for (int u = 0; u < U; ++u)
-        v[u] = (k + u < cnt) ? p[u * step] : make_float4(-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F);
-      batch(v);
+        v[u] = (u < rem) ? xp[off + u * step] : make_float4(-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F);
+      lanes_take<U>(s, v);
     }
   }
-  if (L.slot >= 0) {
-#pragma unroll
-    for (int e = 0; e < 4; ++e) sm_m[L.slot + e] = m[e];
-  }
+  if (L.slot >= 0) *reinterpret_cast<float4*>(sm_c + L.slot) = make_float4(s[0].c, s[1].c, s[2].c, s[3].c);
   __syncthreads();
-  // column maxima: one thread per (plane, column), partial rows in order; result left in row 0
-  const int planes = q.tiled ? 1 : q.P;
-  const int plane_slots = 4 * q.tact;
-  for (int c = threadIdx.x; c < planes * q.ncols; c += blockDim.x) {
-    const int pl = static_cast<int>(q.div_ncols.div(static_cast<uint32_t>(c)));
-    float* col = sm_m + pl * plane_slots + (c - pl * q.ncols);
-    float M = col[0];
-    for (int r = 1; r < q.R; ++r) M = std_max(col[r * q.ncols], M);
-    col[0] = M;
-  }
-  // a column's row-0 slot is overwritten only after its own thread read it, and other threads read
-  // rows >= 1 of it never: no race inside the loop above; the barrier publishes row 0
+  colwalk_merge(q, sm_c, OpMaxF(), -3.0e38f);   // column references, left in row 0
   __syncthreads();
-  float M[4];
+  float c[4];
   if (L.slot >= 0) {
 #pragma unroll
     for (int e = 0; e < 4; ++e) {
-      M[e] = sm_m[L.plane_base + colwalk_col(q, L, e)];
-      sm_l[L.slot + e] = __fmul_rn(l[e], expf(__fsub_rn(m[e], M[e])));
+      c[e] = sm_c[L.plane_base + colwalk_col(q, L, e)];
+      sm_l[L.slot + e] = __fmul_rn(s[e].l, pow2_int(__fsub_rn(s[e].c, c[e])));
     }
   }
   __syncthreads();
-  for (int c = threadIdx.x; c < planes * q.ncols; c += blockDim.x) {
-    const int pl = static_cast<int>(q.div_ncols.div(static_cast<uint32_t>(c)));
-    float* col = sm_l + pl * plane_slots + (c - pl * q.ncols);
-    float S = col[0];
-    for (int r = 1; r < q.R; ++r) S = __fadd_rn(S, col[r * q.ncols]);
-    col[0] = __frcp_rn(S);
-  }
+  colwalk_merge(q, sm_l, OpAddF(), 0.f);   // column sums, left in row 0
   __syncthreads();
   if (cnt == 0) return;
-  float inv[4];
+  float inv[4], k[4];
 #pragma unroll
-  for (int e = 0; e < 4; ++e) inv[e] = sm_l[L.plane_base + colwalk_col(q, L, e)];
+  for (int e = 0; e < 4; ++e) {
+    inv[e] = __fmul_rn(__frcp_rn(sm_l[L.plane_base + colwalk_col(q, L, e)]), 0x1p-24f);   // takes the bias back
+    k[e] = __fsub_rn(kNumeratorBias, c[e]);
+  }
   auto out4 = [&](const float4& v) {
-    return make_float4(__fmul_rn(exp_nonpos(__fsub_rn(v.x, M[0])), inv[0]), __fmul_rn(exp_nonpos(__fsub_rn(v.y, M[1])), inv[1]),
-                       __fmul_rn(exp_nonpos(__fsub_rn(v.z, M[2])), inv[2]), __fmul_rn(exp_nonpos(__fsub_rn(v.w, M[3])), inv[3]));
+    return make_float4(__fmul_rn(ex2_ftz(__fmaf_rn(v.x, kLog2eF, k[0])), inv[0]), __fmul_rn(ex2_ftz(__fmaf_rn(v.y, kLog2eF, k[1])), inv[1]),
+                       __fmul_rn(ex2_ftz(__fmaf_rn(v.z, kLog2eF, k[2])), inv[2]), __fmul_rn(ex2_ftz(__fmaf_rn(v.w, kLog2eF, k[3])), inv[3]));
   };
-  const float4* p = xp;
-  float4* o = yp;
-  int k = 0;
-  for (; k + U <= cnt; k += U, p += U * step, o += U * step) {
+  uint32_t off = 0;
+  for (int b = 0; b < full; ++b, off += U * step) {
     float4 v[U];
 #pragma unroll
-    for (int u = 0; u < U; ++u) v[u] = ld_stream(p + u * step);
+    for (int u = 0; u < U; ++u) v[u] = ld_stream(xp + (off + u * step));
 #pragma unroll
-    for (int u = 0; u < U; ++u) st_stream(o + u * step, out4(v[u]));
+    for (int u = 0; u < U; ++u) st_stream(yp + (off + u * step), out4(v[u]));
   }
-  if (k < cnt) {
+  if (rem > 0) {
     float4 v[U];
 #pragma unroll
     for (int u = 0; u < U; ++u)
-      if (k + u < cnt) v[u] = ld_stream(p + u * step);
+      if (u < rem) v[u] = ld_stream(xp + (off + u * step));
 #pragma unroll
     for (int u = 0; u < U; ++u)
-      if (k + u < cnt) st_stream(o + u * step, out4(v[u]));
+      if (u < rem) st_stream(yp + (off + u * step), out4(v[u]));
   }
+}
+
+// Strided softmax with the block's patch held in registers (fixed-column walk, at most NV float4 per
+// thread, blocks of 512 threads or fewer so that two or more share an SM): the tensor is read ONCE -
+// no second pass over L2 - and each exponential is computed once, for the sum and for the output
+// alike.  All of a thread's loads are issued before the first is used: NV*16 bytes per thread in flight.
+//   1. load; per-lane maximum; column maxima through shared memory;
+//   2. e = 2^24 * 2^(x*log2(e) - c), c the column's integer reference, kept in the registers; per-lane
+//      sums; column sums -> reciprocal (which takes the 2^24 back);
+//   3. e * (1/sum), one float4 store per float4.
+// Combining a column's partials: tiled layouts with 8 row groups or fewer read the other groups'
+// partials of their own four columns directly (one 128-bit shared-memory load per group, no second
+// barrier); the others go through colwalk_merge.
+template <typename Op>
+__device__ __forceinline__ float4 colreg_combine(const ColWalk& q, const ColLane& L, float* sm, const float4& mine, Op op,
+                                                 float identity) {
+  if (L.slot >= 0) *reinterpret_cast<float4*>(sm + L.slot) = mine;
+  __syncthreads();
+  float4 r = make_float4(identity, identity, identity, identity);
+  if (q.tiled && q.R <= 8) {
+    if (L.slot >= 0) {
+      const float* col = sm + L.col0;   // [R][4*W4]: this thread's four columns, row group g at g*ncols
+      r = *reinterpret_cast<const float4*>(col);
+      for (int g = 1; g < q.R; ++g) {
+        const float4 o = *reinterpret_cast<const float4*>(col + g * q.ncols);
+        r.x = op(r.x, o.x), r.y = op(r.y, o.y), r.z = op(r.z, o.z), r.w = op(r.w, o.w);
+      }
+    }
+    return r;
+  }
+  colwalk_merge(q, sm, op, identity);
+  __syncthreads();
+  if (L.slot >= 0) {
+    const float* p = sm + L.plane_base;
+    r = make_float4(p[colwalk_col(q, L, 0)], p[colwalk_col(q, L, 1)], p[colwalk_col(q, L, 2)], p[colwalk_col(q, L, 3)]);
+  }
+  return r;
+}
+
+template <int NV>
+__global__ void __launch_bounds__(512, 2)
+softmax_colreg_kernel(const float* x, float* y, const __grid_constant__ ColWalk q) {
+  extern __shared__ float4 sm_dyn[];
+  float* sm_m = reinterpret_cast<float*>(sm_dyn);   // [blockDim * 4]
+  float* sm_l = sm_m + blockDim.x * 4;              // [blockDim * 4]
+  const ColLane L = colwalk_thread(q, threadIdx.x, blockIdx.x);
+  const float4* xp = reinterpret_cast<const float4*>(x) + L.first4;
+  const uint32_t step = static_cast<uint32_t>(L.step4);   // a patch spans fewer than 2^31 float4
+  const int cnt = L.cnt;   // <= NV; the guards below are uniform across a warp except at a patch's edge
+  float4 v[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i)
+    if (i < cnt) v[i] = ld_stream(xp + i * step);
+  float4 m = make_float4(-FLT_MAX, -FLT_MAX, -FLT_MAX, -FLT_MAX);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    if (i < cnt) m.x = fmaxf(m.x, v[i].x), m.y = fmaxf(m.y, v[i].y), m.z = fmaxf(m.z, v[i].z), m.w = fmaxf(m.w, v[i].w);
+  }
+  m = colreg_combine(q, L, sm_m, m, OpMaxF(), -FLT_MAX);
+  // integer reference of each column, with the numerators' bias folded in
+  const float4 k = make_float4(__fsub_rn(kNumeratorBias, rintf(__fmul_rn(m.x, kLog2eF))), __fsub_rn(kNumeratorBias, rintf(__fmul_rn(m.y, kLog2eF))),
+                               __fsub_rn(kNumeratorBias, rintf(__fmul_rn(m.z, kLog2eF))), __fsub_rn(kNumeratorBias, rintf(__fmul_rn(m.w, kLog2eF))));
+  float4 l = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    if (i < cnt) {
+      v[i].x = ex2_ftz(__fmaf_rn(v[i].x, kLog2eF, k.x)), v[i].y = ex2_ftz(__fmaf_rn(v[i].y, kLog2eF, k.y));
+      v[i].z = ex2_ftz(__fmaf_rn(v[i].z, kLog2eF, k.z)), v[i].w = ex2_ftz(__fmaf_rn(v[i].w, kLog2eF, k.w));
+      l.x = __fadd_rn(l.x, v[i].x), l.y = __fadd_rn(l.y, v[i].y), l.z = __fadd_rn(l.z, v[i].z), l.w = __fadd_rn(l.w, v[i].w);
+    }
+  }
+  l = colreg_combine(q, L, sm_l, l, OpAddF(), 0.f);
+  if (cnt == 0) return;
+  // the sums carry the numerators' bias, so their reciprocals take it back
+  const float4 inv = make_float4(__frcp_rn(l.x), __frcp_rn(l.y), __frcp_rn(l.z), __frcp_rn(l.w));
+  float4* yp = reinterpret_cast<float4*>(y) + L.first4;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    if (i < cnt)
+      st_stream(yp + i * step, make_float4(__fmul_rn(v[i].x, inv.x), __fmul_rn(v[i].y, inv.y), __fmul_rn(v[i].z, inv.z),
+                                           __fmul_rn(v[i].w, inv.w)));
+  }
+}
+
+template <int NV>
+void launch_colreg(const float* x, float* y, const ColWalk& cw, size_t smem, cudaStream_t s) {
+  softmax_colreg_kernel<NV><<<cw.grid, cw.threads, smem, s>>>(x, y, cw);
 }
 
 template <int TPR, int NV, bool VEC>
@@ -411,9 +516,19 @@ extern "C" int sb200_softmax(const float* x, float* y, int64_t outer, int64_t di
   }
   if (dim >= (1ll << 31)) return SB200_ERR_UNSUPPORTED;
   ColWalk cw;
-  if (plan_colwalk(x, y, outer, dim, inner, &cw)) {
+  if (plan_colwalk(x, y, outer, dim, inner, &cw, kWalkResident, 12)) {
+    // the patch fits the registers of a block: one read, one write
     const size_t smem = 2 * colwalk_smem(cw, sizeof(float));
-    softmax_colvec_kernel<4><<<cw.grid, cw.threads, smem, s>>>(x, y, cw);
+    const int64_t share = cw.tiled ? cw.dim : cw.plane4 / cw.period4;   // rows or periods per block
+    const int64_t per_step = cw.tiled ? cw.G : cw.tact / cw.period4;
+    const int64_t most = (share + per_step - 1) / per_step;
+    if (most <= 4) launch_colreg<4>(x, y, cw, smem, s);
+    else if (most <= 8) launch_colreg<8>(x, y, cw, smem, s);
+    else launch_colreg<12>(x, y, cw, smem, s);
+    return after_launch("sb200_softmax");
+  }
+  if (plan_colwalk(x, y, outer, dim, inner, &cw)) {
+    softmax_colvec_kernel<6><<<cw.grid, cw.threads, 2 * colwalk_smem(cw, sizeof(float)), s>>>(x, y, cw);
     return after_launch("sb200_softmax");
   }
   const int W = static_cast<int>(inner < 256 ? inner : 256);

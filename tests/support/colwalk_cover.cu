@@ -1,5 +1,5 @@
 // Host replay of the fixed-column float4 walk (shadow_b200/csrc/colwalk.cuh): for each geometry on
-// the command line (the number of passes, 1 or 2, then "outer dim inner" triples) every thread of every block is replayed and the
+// the command line (the kind of kernel that uses the layout, 0 = two passes, 1 = one pass, 2 = patch in registers, then "outer dim inner" triples) every thread of every block is replayed and the
 // program checks that each float4 of the tensor is visited exactly once, that each of a thread's
 // four lanes stays on one column and one (plane, column) partial, that the row arithmetic the
 // kernels use for per-row scales holds, and that the shared-memory slots of a block are distinct
@@ -20,9 +20,9 @@ void count_launch(int) {}
 
 using namespace sb200;
 
-static int check(int64_t outer, int64_t dim, int64_t inner, bool two_pass) {
+static int check(int64_t outer, int64_t dim, int64_t inner, int use) {
   ColWalk q;
-  if (!plan_colwalk(reinterpret_cast<void*>(256), reinterpret_cast<void*>(512), outer, dim, inner, &q, two_pass)) {
+  if (!plan_colwalk(reinterpret_cast<void*>(256), reinterpret_cast<void*>(512), outer, dim, inner, &q, static_cast<ColWalkUse>(use), 13)) {
     std::printf("skip %lld %lld %lld (walk does not apply)\n", (long long)outer, (long long)dim, (long long)inner);
     return 0;
   }
@@ -54,6 +54,7 @@ static int check(int64_t outer, int64_t dim, int64_t inner, bool two_pass) {
           }
         }
       } else if (L.cnt != 0) { std::printf("FAIL: working thread without slot\n"); return 1; }
+      if (use == 2 && L.cnt > 13) { std::printf("FAIL: thread owns %d float4, limit 13\n", L.cnt); return 1; }
       for (int j = 0; j < L.cnt; ++j) {
         const int64_t i4 = L.first4 + j * L.step4;
         if (i4 < 0 || i4 >= total4 || seen[i4]) { std::printf("FAIL cover: float4 %lld (block %lld thread %d step %d)\n", (long long)i4, (long long)b, t, j); return 1; }
@@ -85,7 +86,7 @@ static int check(int64_t outer, int64_t dim, int64_t inner, bool two_pass) {
 int main(int argc, char** argv) {
   int bad = 0;
   if (argc < 2) return 2;
-  const bool two_pass = std::atoi(argv[1]) == 2;   // first argument: passes of the kernel that uses the layout (1 or 2)
-  for (int i = 2; i + 2 < argc; i += 3) bad |= check(std::atoll(argv[i]), std::atoll(argv[i + 1]), std::atoll(argv[i + 2]), two_pass);
+  const int use = std::atoi(argv[1]);   // first argument: how the kernel uses the layout (ColWalkUse: 0, 1 or 2)
+  for (int i = 2; i + 2 < argc; i += 3) bad |= check(std::atoll(argv[i]), std::atoll(argv[i + 1]), std::atoll(argv[i + 2]), use);
   return bad;
 }
