@@ -13,12 +13,56 @@
 namespace sb200 {
 
 // ---- transcendental functions -------------------------------------------------------------------
-// The parity bar is 2 ulp against glibc's float functions.  Measured over ALL 2^32 float inputs
-// on B200 against glibc 2.39: CUDA's logf is within 1 ulp of glibc's everywhere (used as is);
-// CUDA's expf reaches 2 ulp and tanhf 3 ulp, and the reference's Sigmoid composition
-// 1/(1+expf(-x)) magnifies a 1-ulp difference in expf up to 4 ulp.  So e^x is computed here in
-// double precision and rounded ONCE to float (correctly rounded except for rare double-rounding
-// ties; at most 1 ulp from glibc on every input), and Sigmoid / Tanh / SoftPlus build on it.
+// The parity bar is 2 ulp against glibc's float functions, checked over ALL 2^32 float inputs
+// (tests/test_gpu_ulp_exhaustive.py).  CUDA's logf is within 1 ulp of glibc's everywhere (used as
+// is); CUDA's expf reaches 2 ulp and tanhf 3 ulp, and the reference's Sigmoid composition
+// 1/(1+expf(-x)) magnifies a 1-ulp difference in expf up to 4 ulp where 1+e^-x crosses 2^24.  So
+// e^x follows glibc's own algorithm step by step (expf_like_glibc: the same bits as glibc 2.39 on
+// every input), Sigmoid builds on it with IEEE operations and is therefore bit-exact too, and
+// Tanh uses a double-precision e^x (exp_core) and rounds once at the end.
+
+// 2^(i/32) as a double's bit pattern minus i << 47, i = 0..31: the table of the expf algorithm below
+// (each entry the correctly rounded double of 2^(i/32)); two 128-byte lines.
+__device__ __align__(128) const unsigned long long kExp2fTable[32] = {
+    0x3ff0000000000000ull, 0x3fefd9b0d3158574ull, 0x3fefb5586cf9890full, 0x3fef9301d0125b51ull,
+    0x3fef72b83c7d517bull, 0x3fef54873168b9aaull, 0x3fef387a6e756238ull, 0x3fef1e9df51fdee1ull,
+    0x3fef06fe0a31b715ull, 0x3feef1a7373aa9cbull, 0x3feedea64c123422ull, 0x3feece086061892dull,
+    0x3feebfdad5362a27ull, 0x3feeb42b569d4f82ull, 0x3feeab07dd485429ull, 0x3feea47eb03a5585ull,
+    0x3feea09e667f3bcdull, 0x3fee9f75e8ec5f74ull, 0x3feea11473eb0187ull, 0x3feea589994cce13ull,
+    0x3feeace5422aa0dbull, 0x3feeb737b0cdc5e5ull, 0x3feec49182a3f090ull, 0x3feed503b23e255dull,
+    0x3feee89f995ad3adull, 0x3feeff76f2fb5e47ull, 0x3fef199bdd85529cull, 0x3fef3720dcef9069ull,
+    0x3fef5818dcfba487ull, 0x3fef7c97337b9b5full, 0x3fefa4afa2a490daull, 0x3fefd0765b6e4540ull};
+
+// expf as glibc computes it (sysdeps/ieee754/flt-32/e_expf.c, the algorithm of Arm's optimized
+// routines): in double, x*32/ln2 = k + r with k an integer (found by adding 1.5*2^52), e^x =
+// 2^(k/32) * 2^(r/32) with 2^(k/32) from a 32-entry table and its exponent field, 2^(r/32) by a cubic;
+// the double result is rounded once to float.  The fused steps are the ones glibc's build for
+// processors with FMA contracts; with them the result equals glibc 2.39's expf on all 2^32 inputs
+// (checked on the host), and a build without FMA differs on two inputs by one ulp.
+__device__ __forceinline__ float expf_like_glibc(float x) {
+  constexpr double kInvLn2N = 0x1.71547652b82fep+0 * 32.0;
+  constexpr double kShift = 0x1.8p+52;
+  constexpr double kC0 = 0x1.c6af84b912394p-5 / 32.0 / 32.0 / 32.0, kC1 = 0x1.ebfce50fac4f3p-3 / 32.0 / 32.0,
+                   kC2 = 0x1.62e42ff0c52d6p-1 / 32.0;
+  // beyond these the float result is inf / 0 (also for the infinities); a NaN fails both tests
+  // and comes out of the arithmetic as a NaN
+  const float xc = fminf(fmaxf(x, -104.5f), 89.f);
+  const double xd = static_cast<double>(xc);
+  const double z = __dmul_rn(kInvLn2N, xd);
+  double kd = __dadd_rn(z, kShift);
+  const unsigned long long ki = static_cast<unsigned long long>(__double_as_longlong(kd));
+  kd = __dsub_rn(kd, kShift);
+  const double r = fma(kInvLn2N, xd, -kd);
+  const unsigned long long t = __ldg(&kExp2fTable[ki & 31]) + (ki << 47);
+  const double s = __longlong_as_double(static_cast<long long>(t));
+  const double q = fma(kC0, r, kC1);
+  const double r2 = __dmul_rn(r, r);
+  double y = fma(kC2, r, 1.0);
+  y = fma(q, r2, y);
+  y = __dmul_rn(y, s);
+  const float f = static_cast<float>(y);
+  return (x == x) ? f : x;
+}
 
 // 2^(j/16), j = 0..15: one 128-byte line, so a warp's 32 lookups are a single L1 transaction.
 __device__ __align__(128) const double kExp2Sixteenths[16] = {
@@ -48,16 +92,6 @@ __device__ __forceinline__ double exp_core(float x) {
   const double v = p * __ldg(&kExp2Sixteenths[ki & 15]);  // in [1, 2.05)
   // scale by 2^(k>>4) through the exponent field; k>>4 stays within [-152, 130]
   return __hiloint2double(__double2hiint(v) + ((ki >> 4) << 20), __double2loint(v));
-}
-
-__device__ __forceinline__ float exp_accurate(float x) {
-  // Branch-free: clamp into the range where exp_core is valid.  e^-105 converts to 0 and e^90 to
-  // +inf, which are the float results for everything beyond the clamp; denormal results come out
-  // right because the scaling is done in double and the single conversion to float rounds into
-  // the denormal range.  fminf/fmaxf drop a NaN, so it is put back at the end.
-  const float xc = fminf(fmaxf(x, -105.f), 90.f);
-  const float y = static_cast<float>(exp_core(xc));
-  return (x == x) ? y : x;
 }
 
 // 1/d for a double d in [2, 1e9], relative error ~1e-14: hardware float reciprocal as the seed,
@@ -141,7 +175,7 @@ struct UnaryFn {
     if (OP == SB200_SQUARE) return __fmul_rn(x, x);
     if (OP == SB200_SQRT) return __fsqrt_rn(x);
     if (OP == SB200_LOG) return logf(x);   // within 1 ulp of glibc's logf on every input
-    if (OP == SB200_EXP) return exp_accurate(x);
+    if (OP == SB200_EXP) return expf_like_glibc(x);
     if (OP == SB200_SIN) return static_cast<float>(sin(static_cast<double>(x)));
     if (OP == SB200_COS) return static_cast<float>(cos(static_cast<double>(x)));
     if (OP == SB200_TAN) return static_cast<float>(tan(static_cast<double>(x)));
@@ -163,11 +197,12 @@ struct ActivateFn {
   __device__ __forceinline__ float operator()(float x) const {
     if (TYPE == SB200_RELU) return x > 0.f ? x : 0.f;
     if (TYPE == SB200_LEAKY) return x > 0.f ? x : __fmul_rn(slope, x);
-    // 1 / (1 + exp(-x)): float add, then the correctly rounded reciprocal (== IEEE 1.0f / y)
-    if (TYPE == SB200_SIGMOID) return rcp_correct(__fadd_rn(1.f, exp_accurate(-x)));
+    // 1 / (1 + exp(-x)): glibc's expf bit for bit, a float add, then the correctly rounded
+    // reciprocal (== IEEE 1.0f / y)
+    if (TYPE == SB200_SIGMOID) return rcp_correct(__fadd_rn(1.f, expf_like_glibc(-x)));
     if (TYPE == SB200_SOFTPLUS) {
-      // log1p(exp(x)) with both steps in double; exp(x) first rounded to float like the reference.
-      float e = exp_accurate(x);
+      // log1pf(expf(x)): expf as glibc computes it, then log1p in double rounded once
+      float e = expf_like_glibc(x);
       return static_cast<float>(log1p(static_cast<double>(e)));
     }
     if (TYPE == SB200_TANH) return tanh_accurate(x);

@@ -123,6 +123,12 @@ class Native : public Backend {
         dst->set_data<float>(blob.data_f().data(), blob.data_f_size());
         // the source vector lives in the caller's NetParam: finish the upload before returning
         ws_->Ctx()->synchronize();
+      } else if (dst->data_type() != DataType::kF32 && blob.data_b_size() > 0 && !blob.data_b(0).empty()) {
+        // non-float blobs (an int32 index list for Gather, ...) travel as raw bytes in data_b(0)
+        // (shadow/backends/native/native.cpp:158-167)
+        CHECK_EQ(blob.data_b(0).size(), dst->raw_size());
+        ws_->Ctx()->allocator()->write(dst->raw_size(), blob.data_b(0).data(), dst->mutable_data<unsigned char>());
+        ws_->Ctx()->synchronize();
       }
     }
     ops_.clear(), in_blob_.clear();

@@ -78,8 +78,10 @@ def _message(name, ops, net_args=None, blobs=()):
     for bname, btype, shape, data in blobs:
         b = net.blob.add(name=bname, type=btype)
         b.shape.extend(shape)
-        if data is not None:
+        if data is not None and btype == "float":
             b.data_f.extend(float(v) for v in np.asarray(data, np.float32).ravel())
+        elif data is not None:   # every other type travels as raw bytes
+            b.data_b.append(np.ascontiguousarray(data).tobytes())
     for op_type, op_name, bottoms, tops, args in ops:
         op = net.op.add(name=op_name, type=op_type)
         op.bottom.extend(bottoms)
@@ -217,6 +219,26 @@ def test_binary_model_runs_like_the_programmatic_net():
     assert orc.bit_equal(net.blob("out"), orc.reduce(z, 2, [0, 2], False))
     assert orc.bit_equal(net.blob("w"), orc.eltwise([z, z], 1, [0.5, -1.5]))
     assert orc.bit_equal(net.blob("w0"), WEIGHT[3])
+
+
+@pytest.mark.gpu
+def test_int32_weight_blob_reaches_the_device():
+    """A non-float weight blob (data_b, shadow/backends/native/native.cpp:158-167): the int32 index
+    list of a Gather stored in the model, not passed as an argument."""
+    lib = _lib()
+    x = cases.normal(21, (5, 7))
+    idx = np.array([3, 0, 0, 2, 4], np.int32)
+    graph = [("Input", "input", [], ["x"], {"x": [5, 7]}),
+             ("Gather", "g", ["x", "idx"], ["out"], {"axis": 0})]
+    msg = _message("n", graph, blobs=[("idx", "int32", [5], idx)])
+    net = Net(lib, "n").parse_binary(msg.SerializeToString())
+    net.load("Native", out_blobs=["out"])
+    net.forward({"x": x})
+    assert orc.bit_equal(net.blob("out"), x[idx])
+    # a byte count that does not match the blob's shape is refused at load time
+    bad = _message("n", graph, blobs=[("idx", "int32", [5], idx[:3])])
+    with pytest.raises(ShadowError):
+        Net(lib, "n").parse_binary(bad.SerializeToString()).load("Native", out_blobs=["out"])
 
 
 def _expected_dump(msg):
