@@ -6,7 +6,8 @@ Two artefacts:
 * ``oracle/liboracle_port.so``  - the plain-C restatement of the reference's CPU algorithms
   (``oracle/oracle_port.c``), always buildable (gcc only).
 * ``oracle/_ref/libshadow_ref.so`` - the reference's own CPU ``Default`` kernels, compiled from
-  the sources where they lie (the checkout named by ``$SHADOW_REFERENCE_ROOT``, or the default below) with no
+  the sources where they lie (the checkout named by ``$SHADOW_REFERENCE_ROOT``, by default the directory
+  ``reference`` beside this repository) with no
   ``USE_*`` define (plain-loop kernels, glibc libm, no Eigen/DNNL/NNPACK, CPUContext only),
   plus the C adapter ``shadow_b200/host/net_capi.cpp`` compiled against the reference's headers
   with the symbol prefix ``sref_``.  Built only when the reference tree is present; a machine
@@ -23,15 +24,17 @@ from __future__ import annotations
 import concurrent.futures as cf
 import glob
 import os
+import shutil
 import subprocess
 import sys
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 REPO = os.path.dirname(HERE)
-REF_ROOT = os.environ.get("SHADOW_REFERENCE_ROOT", "/root/reference")
+REF_ROOT = os.environ.get("SHADOW_REFERENCE_ROOT", os.path.join(os.path.dirname(REPO), "reference"))
 REF_DIR = os.path.join(HERE, "_ref")
 GEN_DIR = os.path.join(HERE, "_gen")
 REF_LIB = os.path.join(REF_DIR, "libshadow_ref.so")
+REF_GPU_LIB = os.path.join(REF_DIR, "libshadow_ref_b200.so")
 PORT_LIB = os.path.join(HERE, "liboracle_port.so")
 
 CONFIG_HPP = """#ifndef SHADOW_CORE_CONFIG_HPP_
@@ -116,11 +119,76 @@ def build_ref(force: bool = False) -> str | None:
     return REF_LIB
 
 
+def build_ref_gpu(force: bool = False) -> str | None:
+    """The reference's own host stack - Network, NetworkImpl, the Native backend, the operator
+    front-ends, Workspace, Blob, the GPU Context and allocator (``core/context.cu``,
+    ``core/allocator.cu``) - compiled from the reference tree with ``-DUSE_CUDA`` (no cuDNN), WITHOUT
+    any of its ``operators/kernels/*.cu``: the GPU kernel registry keys are taken by this
+    repository's binding translation units (``shadow_b200/host/src/gpu_kernels*.cpp``, compiled here
+    against the reference's headers) and resolve to ``libsb200.so``.  The result,
+    ``oracle/_ref/libshadow_ref_b200.so`` with the adapter prefix ``srefgpu_``, is the drop-in proof:
+    the reference's Network runs an operator graph unchanged on this library's kernels.  Needs the
+    reference tree, nvcc and the built ``libsb200.so``; returns the prebuilt file (or None) otherwise."""
+    kernel_lib = os.path.join(REPO, "shadow_b200", "lib", "libsb200.so")
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    if not reference_available() or not os.path.exists(nvcc) or not os.path.exists(kernel_lib):
+        return REF_GPU_LIB if os.path.exists(REF_GPU_LIB) else None
+    shadow = os.path.join(REF_ROOT, "shadow")
+    host_src = os.path.join(REPO, "shadow_b200", "host", "src")
+    shim = os.path.join(REPO, "shadow_b200", "host", "net_capi.cpp")
+    binding = sorted(glob.glob(os.path.join(host_src, "gpu_kernels*.cpp")))
+    sources = []
+    for pat in ("core/*.cpp", "operators/*.cpp", "operators/kernels/*.cpp"):
+        sources += sorted(glob.glob(os.path.join(shadow, pat)))
+    sources += [os.path.join(shadow, p) for p in
+                ("backends/native/native.cpp", "util/io.cpp", "util/json.cpp", "util/boxes.cpp")]
+    cuda_sources = [os.path.join(shadow, "core", "context.cu"), os.path.join(shadow, "core", "allocator.cu")]
+    deps = sources + cuda_sources + binding + [shim, kernel_lib, os.path.abspath(__file__),
+                                               os.path.join(host_src, "gpu_kernels_common.hpp")]
+    if not force and _newer(REF_GPU_LIB, deps):
+        return REF_GPU_LIB
+    os.makedirs(REF_DIR, exist_ok=True)
+    os.makedirs(GEN_DIR, exist_ok=True)
+    with open(os.path.join(GEN_DIR, "config.hpp"), "w") as f:
+        f.write(CONFIG_HPP)
+    obj_dir = os.path.join(GEN_DIR, "obj_gpu")
+    os.makedirs(obj_dir, exist_ok=True)
+    cuda_inc = os.path.join(os.path.dirname(os.path.dirname(nvcc)), "include")
+    cuda_lib = os.path.join(os.path.dirname(os.path.dirname(nvcc)), "lib64")
+    flags = ["-O2", "-DNDEBUG", "-DUSE_CUDA", "-std=c++11", "-fPIC", "-include", "cstdint", "-w",
+             "-I" + shadow, "-I" + GEN_DIR, "-I" + cuda_inc, "-I" + os.path.join(REPO, "include"), "-I" + host_src]
+
+    def compile_one(item):
+        idx, src = item
+        obj = os.path.join(obj_dir, "%03d_%s.o" % (idx, os.path.splitext(os.path.basename(src))[0]))
+        if src.endswith(".cu"):
+            _run([nvcc, "-gencode", "arch=compute_100a,code=sm_100a", "-O2", "-DNDEBUG", "-DUSE_CUDA", "-std=c++11",
+                  "-Xcompiler", "-fPIC,-w", "-include", "cstdint", "-I" + shadow, "-I" + GEN_DIR, "-c", src, "-o", obj])
+        else:
+            _run(["g++"] + flags + ["-c", src, "-o", obj])
+        return obj
+
+    with cf.ThreadPoolExecutor(max_workers=os.cpu_count() or 4) as pool:
+        objs = list(pool.map(compile_one, enumerate(sources + cuda_sources + binding)))
+    shim_obj = os.path.join(obj_dir, "net_capi_srefgpu.o")
+    _run(["g++"] + flags + ["-DSHADOW_CAPI_PREFIX=srefgpu_", "-c", shim, "-o", shim_obj])
+    vers = os.path.join(GEN_DIR, "srefgpu.map")
+    with open(vers, "w") as f:
+        f.write("{ global: srefgpu_*; local: *; };\n")
+    # $ORIGIN-relative path to libsb200.so: the library is found wherever the repository is copied
+    _run(["g++", "-shared", "-o", REF_GPU_LIB] + objs + [shim_obj,
+         "-Wl,-Bsymbolic", "-Wl,--version-script=" + vers,
+         "-L" + os.path.dirname(kernel_lib), "-lsb200", "-Wl,-rpath,$ORIGIN/../../shadow_b200/lib",
+         "-L" + cuda_lib, "-lcudart", "-lcublas", "-ldl"])
+    return REF_GPU_LIB
+
+
 def build_all(force: bool = False) -> dict:
-    out = {"port": None, "ref": None}
+    out = {"port": None, "ref": None, "ref_gpu": None}
     if os.path.exists(os.path.join(HERE, "oracle_port.c")):
         out["port"] = build_port(force)
     out["ref"] = build_ref(force)
+    out["ref_gpu"] = build_ref_gpu(force)
     return out
 
 

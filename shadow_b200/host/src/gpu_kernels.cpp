@@ -1,28 +1,44 @@
-// The GPU kernel classes (six tensor operators + Eltwise and Axpy), registered as "<Op>GPU(Default)".  Each Run translates blobs into
+// The GPU kernel classes (every operator except Reduce and Eltwise, which sit in gpu_kernels_reduce.cpp and
+// gpu_kernels_eltwise.cpp), registered as "<Op>GPU(Default)".  Each Run translates blobs into
 // the raw pointers / sizes of the sb200 C ABI and enqueues on the workspace's stream.  A non-zero
 // status becomes a LOG(FATAL) (print + std::runtime_error), the reference's error convention.
 // There is no other implementation behind these classes: without libsb200 this file does not link.
-#include "op_kernels.hpp"
-#include "sb200.h"
+//
+// The file uses only what the reference's own headers offer (shadow/core/{blob,workspace,kernel}.hpp
+// and shadow/operators/kernels/<op>.hpp: the abstract XxxKernel classes, Blob::count/shape/data,
+// Workspace::Ctx/GrowTempBuffer/CreateTempBlob, Context::stream, REGISTER_OP_KERNEL_DEFAULT), so the
+// same translation unit compiles inside the reference's tree (-I<reference>/shadow) and registers
+// there under the same keys; tests/test_reference_binding.py compiles it both ways.
+#include "operators/kernels/activate.hpp"
+#include "operators/kernels/axpy.hpp"
+#include "operators/kernels/batch_norm.hpp"
+#include "operators/kernels/binary.hpp"
+#include "operators/kernels/concat.hpp"
+#include "operators/kernels/gather.hpp"
+#include "operators/kernels/group_norm.hpp"
+#include "operators/kernels/layer_norm.hpp"
+#include "operators/kernels/normalize.hpp"
+#include "operators/kernels/pad.hpp"
+#include "operators/kernels/permute.hpp"
+#include "operators/kernels/pooling.hpp"
+#include "operators/kernels/scale.hpp"
+#include "operators/kernels/slice.hpp"
+#include "operators/kernels/softmax.hpp"
+#include "operators/kernels/ssd_normalize.hpp"
+#include "operators/kernels/stack.hpp"
+#include "operators/kernels/unary.hpp"
+
+#include "gpu_kernels_common.hpp"
 
 namespace Shadow {
 
 namespace {
 
-void expect_ok(int status, const char* what) {
-  if (status != SB200_OK) {
-    LOG(FATAL) << what << " failed: " << sb200_status_string(status)
-               << (status == SB200_ERR_CUDA ? std::string(" - ") + sb200_last_cuda_error() : std::string());
-  }
-}
-
-void* stream_of(Workspace* ws) { return ws->Ctx()->stream(); }
-
 class BinaryKernelB200 : public BinaryKernel {
  public:
   void Run(const BlobPtr& input, BlobPtr& output, Workspace* ws, int operation, float scalar_value) override {
     expect_ok(sb200_binary_scalar(input->data<float>(), scalar_value, output->mutable_data<float>(),
-                                  static_cast<int64_t>(input->count64()), operation, stream_of(ws)),
+                                  count64(input), operation, stream_of(ws)),
               "sb200_binary_scalar");
   }
   void Run(const BlobPtr& input, const BlobPtr& scalar, BlobPtr& output, Workspace* ws, int operation,
@@ -35,7 +51,7 @@ class BinaryKernelB200 : public BinaryKernel {
                 "sb200_binary_broadcast");
     } else {
       expect_ok(sb200_binary(input->data<float>(), scalar->data<float>(), output->mutable_data<float>(),
-                             static_cast<int64_t>(input->count64()), operation, stream_of(ws)),
+                             count64(input), operation, stream_of(ws)),
                 "sb200_binary");
     }
   }
@@ -47,7 +63,7 @@ class UnaryKernelB200 : public UnaryKernel {
  public:
   void Run(const BlobPtr& input, BlobPtr& output, Workspace* ws, int operation) override {
     expect_ok(sb200_unary(input->data<float>(), output->mutable_data<float>(),
-                          static_cast<int64_t>(input->count64()), operation, stream_of(ws)),
+                          count64(input), operation, stream_of(ws)),
               "sb200_unary");
   }
   DeviceType device_type() const override { return DeviceType::kGPU; }
@@ -58,10 +74,10 @@ class ActivateKernelB200 : public ActivateKernel {
  public:
   void Run(const BlobPtr& input, const BlobPtr& slope, BlobPtr& output, Workspace* ws, int activate_type,
            float slope_val) override {
-    if (activate_type == ActivateCode::kPRelu) {
+    if (activate_type == 0 /* kPRelu, shadow/operators/kernels/activate.hpp:25 */) {
       CHECK_GE(input->num_axes(), 2);
       CHECK_NOTNULL(slope);
-      const bool channel_shared = slope->count64() == 1;
+      const bool channel_shared = slope->count() == 1;
       if (!channel_shared) CHECK_EQ(slope->count(), input->shape(1));
       int64_t dim = 1;
       for (int n = 2; n < input->num_axes(); ++n) dim *= input->shape(n);
@@ -70,7 +86,7 @@ class ActivateKernelB200 : public ActivateKernel {
                 "sb200_prelu");
     } else {
       expect_ok(sb200_activate(input->data<float>(), output->mutable_data<float>(),
-                               static_cast<int64_t>(output->count64()), activate_type, slope_val, stream_of(ws)),
+                               count64(output), activate_type, slope_val, stream_of(ws)),
                 "sb200_activate");
     }
   }
@@ -87,7 +103,7 @@ class ScaleKernelB200 : public ScaleKernel {
     const BlobPtr& ref = scale != nullptr ? scale : bias;
     const int inner = input->count(axis + ref->num_axes());
     expect_ok(sb200_scale_bias(input->data<float>(), output->mutable_data<float>(),
-                               static_cast<int64_t>(input->count64()), scale ? scale->data<float>() : nullptr,
+                               count64(input), scale ? scale->data<float>() : nullptr,
                                bias ? bias->data<float>() : nullptr, ref->count(), inner, stream_of(ws)),
               "sb200_scale_bias");
   }
@@ -111,33 +127,9 @@ class ScaleKernelB200 : public ScaleKernel {
       bias->set_data<float>(bias_value.data(), dim);
     }
     expect_ok(sb200_scale_bias(input->data<float>(), output->mutable_data<float>(),
-                               static_cast<int64_t>(input->count64()), scale ? scale->data<float>() : nullptr,
+                               count64(input), scale ? scale->data<float>() : nullptr,
                                bias ? bias->data<float>() : nullptr, dim, inner, stream_of(ws)),
               "sb200_scale_bias");
-  }
-  DeviceType device_type() const override { return DeviceType::kGPU; }
-  std::string kernel_type() const override { return "Default"; }
-};
-
-class ReduceKernelB200 : public ReduceKernel {
- public:
-  void Run(const BlobPtr& input, BlobPtr& output, Workspace* ws, int operation, const VecInt& axes) override {
-    CHECK(!axes.empty());
-    const int rank = input->num_axes();
-    const int64_t need = sb200_reduce_scratch_bytes(input->shape().data(), rank, axes.data(),
-                                                    static_cast<int>(axes.size()), operation);
-    CHECK_GE(need, 0) << "Reduce: bad axes";
-    void* scratch = nullptr;
-    if (need > 0) {
-      ws->GrowTempBuffer(static_cast<size_t>(need) + 256);
-      const int64_t ints = (need + 3) / 4;
-      CHECK_LE(ints, 0x7fffffff);
-      scratch = ws->CreateTempBlob({static_cast<int>(ints)}, DataType::kI32)->mutable_data<int>();
-    }
-    expect_ok(sb200_reduce(input->data<float>(), input->shape().data(), rank, axes.data(),
-                           static_cast<int>(axes.size()), operation, output->mutable_data<float>(), scratch, need,
-                           stream_of(ws)),
-              "sb200_reduce");
   }
   DeviceType device_type() const override { return DeviceType::kGPU; }
   std::string kernel_type() const override { return "Default"; }
@@ -154,27 +146,11 @@ class SoftmaxKernelB200 : public SoftmaxKernel {
   std::string kernel_type() const override { return "Default"; }
 };
 
-class EltwiseKernelB200 : public EltwiseKernel {
- public:
-  void Run(const std::vector<BlobPtr>& inputs, BlobPtr& output, Workspace* ws, int operation,
-           const VecFloat& coeff) override {
-    std::vector<const float*> ptrs;
-    for (const auto& in : inputs) ptrs.push_back(in->data<float>());
-    // the front-end always passes one coefficient per input (1 by default); only Sum uses them
-    const float* cf = (operation == 1 && coeff.size() == inputs.size()) ? coeff.data() : nullptr;
-    expect_ok(sb200_eltwise(ptrs.data(), static_cast<int>(ptrs.size()), cf, output->mutable_data<float>(),
-                            static_cast<int64_t>(inputs[0]->count64()), operation, stream_of(ws)),
-              "sb200_eltwise");
-  }
-  DeviceType device_type() const override { return DeviceType::kGPU; }
-  std::string kernel_type() const override { return "Default"; }
-};
-
 class AxpyKernelB200 : public AxpyKernel {
  public:
   void Run(const BlobPtr& alpha, const BlobPtr& x, const BlobPtr& y, BlobPtr& output, Workspace* ws) override {
     expect_ok(sb200_axpy(alpha->data<float>(), x->data<float>(), y->data<float>(), output->mutable_data<float>(),
-                         static_cast<int64_t>(alpha->count64()), x->count(2), stream_of(ws)),
+                         count64(alpha), x->count(2), stream_of(ws)),
               "sb200_axpy");
   }
   DeviceType device_type() const override { return DeviceType::kGPU; }
@@ -316,7 +292,7 @@ class GroupNormKernelB200 : public GroupNormKernel {
  public:
   void Run(const BlobPtr& input, const BlobPtr& scale, const BlobPtr& bias, BlobPtr& output, Workspace* ws, int group,
            float eps) override {
-    const int64_t count = static_cast<int64_t>(input->count64());
+    const int64_t count = count64(input);
     const int64_t rows = static_cast<int64_t>(input->shape(0)) * group, inner = count / rows;
     const bool affine = scale != nullptr && bias != nullptr;
     const int channel = input->shape(1);
@@ -338,7 +314,7 @@ class LayerNormKernelB200 : public LayerNormKernel {
   void Run(const BlobPtr& input, const BlobPtr& scale, const BlobPtr& bias, BlobPtr& output, Workspace* ws,
            const VecInt& normalized_shape, float eps) override {
     const int64_t inner = input->count(input->num_axes() - static_cast<int>(normalized_shape.size()));
-    const int64_t rows = static_cast<int64_t>(input->count64()) / inner;
+    const int64_t rows = count64(input) / inner;
     const bool affine = scale != nullptr && bias != nullptr;
     if (affine) {
       CHECK(scale->shape() == normalized_shape);
@@ -374,7 +350,7 @@ class BatchNormKernelB200 : public BatchNormKernel {
     CHECK_EQ(channel, mean->count());
     CHECK_EQ(channel, variance->count());
     expect_ok(sb200_batch_norm(input->data<float>(), output->mutable_data<float>(),
-                               static_cast<int64_t>(input->count64()), mean->data<float>(), variance->data<float>(),
+                               count64(input), mean->data<float>(), variance->data<float>(),
                                channel, input->count(2), scale_factor, eps, stream_of(ws)),
               "sb200_batch_norm");
   }
@@ -396,13 +372,11 @@ REGISTER_OP_KERNEL_DEFAULT(PoolingGPU, PoolingKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(SSDNormalizeGPU, SSDNormalizeKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(GroupNormGPU, GroupNormKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(LayerNormGPU, LayerNormKernelB200);
-REGISTER_OP_KERNEL_DEFAULT(EltwiseGPU, EltwiseKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(AxpyGPU, AxpyKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(BinaryGPU, BinaryKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(UnaryGPU, UnaryKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(ActivateGPU, ActivateKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(ScaleGPU, ScaleKernelB200);
-REGISTER_OP_KERNEL_DEFAULT(ReduceGPU, ReduceKernelB200);
 REGISTER_OP_KERNEL_DEFAULT(SoftmaxGPU, SoftmaxKernelB200);
 
 }  // namespace Shadow
