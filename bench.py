@@ -7,8 +7,8 @@ One STEP is one pass of the sharded large-tensor chain of the baseline configura
 broadcast Mul  A[8,1,2048,2048] x B[1,16,1,2048] -> O[8,16,2048,2048] (2 GiB), then a full-tensor
 ReduceSum and a full-tensor ReduceMax of O.  With N ranks (one process per GPU, torchrun) the
 tensor is split on dim 0 (STRONG scaling: the total work is the fixed 2 GiB tensor), B is
-replicated, and the per-rank double partials of each reduction are combined by one NCCL
-all-reduce.  Inputs are seeded synthetic tensors (U(-1,1) and N(0,1)) resident in HBM before the
+replicated, and the per-rank double partials of both reductions travel in one NCCL all-gather of
+16 bytes per rank (the C entry points of libsb200_nccl.so) and are folded in rank order on every rank.  Inputs are seeded synthetic tensors (U(-1,1) and N(0,1)) resident in HBM before the
 timed region; every step touches > 2 GiB per GPU at N=1 (> 256 MiB at N=8), larger than the
 126 MB L2, so no L2 flush is interposed.
 
@@ -171,61 +171,71 @@ class CpuChain:
                 float(self.orc.reduce(o, RED_MAX, [], False).ravel()[0]))
 
 
-def time_cpu(threads: int, steps: int, warmup: int):
-    """`threads` replicas of the sample chain run concurrently, one per host thread (the reference
-    path itself is single-threaded).  Returns (GB/s, ms per step, kind, results of replica 0)."""
+N_SLICES = (A_SHAPE[0]) * (A_SHAPE[2] // SAMPLE_A[2])   # 32 slices of 1/32 make up the whole step
+
+
+def time_cpu(threads: int, steps: int, warmup: int, slices: int = N_SLICES):
+    """The chain on `slices` of the 32 dim-0 x row slices of the workload (32 = the whole step), spread
+    over `threads` host threads (the reference path itself is single-threaded): thread t runs slices
+    t, t + threads, ... one after the other, each through its own reference Network.  Returns
+    (GB/s, ms per step, kind, (sum, max) over the slices, slice 0 of A)."""
     a_full, b = make_inputs(A_SHAPE, B_SHAPE)
+    rows = SAMPLE_A[2]
     chains = []
-    for t in range(threads):
-        n = t % A_SHAPE[0]
-        r0 = (t // A_SHAPE[0]) * SAMPLE_A[2] % A_SHAPE[2]
-        a = np.ascontiguousarray(a_full[n:n + 1, :, r0:r0 + SAMPLE_A[2], :])
-        c = CpuChain()
-        chains.append((c, a))
+    for t in range(slices):
+        n, r0 = t % A_SHAPE[0], (t // A_SHAPE[0]) * rows
+        a = np.ascontiguousarray(a_full[n:n + 1, :, r0:r0 + rows, :])
+        chains.append((CpuChain(), a))
     del a_full
+    threads = max(1, min(threads, slices))
 
-    def prep(item):
-        item[0].prepare(item[1], b)
-
-    workers = [threading.Thread(target=prep, args=(it,)) for it in chains]
-    [w.start() for w in workers]
-    [w.join() for w in workers]
-    results = [None] * threads
-
-    def one_step():
-        def work(i):
-            results[i] = chains[i][0].run()
-        ws = [threading.Thread(target=work, args=(i,)) for i in range(threads)]
+    def on_threads(fn):
+        def work(t):
+            for i in range(t, slices, threads):
+                fn(i)
+        ws = [threading.Thread(target=work, args=(t,)) for t in range(threads)]
         [w.start() for w in ws]
         [w.join() for w in ws]
 
+    on_threads(lambda i: chains[i][0].prepare(chains[i][1], b))
+    results = [None] * slices
+
+    def run_one(i):
+        results[i] = chains[i][0].run()
+
     for _ in range(warmup):
-        one_step()
+        on_threads(run_one)
     t0 = time.perf_counter()
     for _ in range(steps):
-        one_step()
+        on_threads(run_one)
     dt = time.perf_counter() - t0
-    nbytes = sum(step_bytes(SAMPLE_A, SAMPLE_B, SAMPLE_O).values()) * threads
-    return nbytes * steps / dt / 1e9, dt / steps * 1e3, chains[0][0].kind, results[0], chains[0][1]
+    nbytes = sum(step_bytes(SAMPLE_A, SAMPLE_B, SAMPLE_O).values()) * slices
+    # the slices' float sums added in double in slice order; the maximum is exact
+    total = (float(np.sum(np.array([r[0] for r in results], dtype=np.float64))), max(r[1] for r in results))
+    return nbytes * steps / dt / 1e9, dt / steps * 1e3, chains[0][0].kind, total, chains[0][1], results[0]
 
 
 def run_reference_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return 0
-    threads = max(1, min(os.cpu_count() or 1, 32))
+    threads = max(1, min(os.cpu_count() or 1, N_SLICES))
     steps, warmup = max(1, min(args.steps, 5)), max(1, min(args.warmup, 1))
-    gbs, ms, kind, _, _ = time_cpu(threads, steps, warmup)
+    gbs, ms, kind, total, _, _ = time_cpu(threads, steps, warmup)
     line = {
         "impl": "reference", "metric": METRIC, "value": round(gbs, 4), "unit": UNIT, "n_gpus": args.gpus,
         "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 3), "higher_is_better": True,
         "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": "C5 chain (broadcast Mul -> ReduceSum all -> ReduceMax all) on the CPU",
-                   "sample": SAMPLE_TEXT, "replicas": threads},
+        "config": {"workload": "C5 chain: broadcast Mul A[8,1,2048,2048]xB[1,16,1,2048] -> [8,16,2048,2048] (2 GiB), "
+                               "ReduceSum all axes, ReduceMax all axes, on the host cores",
+                   "how": "the whole step, cut into %d slices (%s) that %d host threads work through, each slice "
+                          "through the reference's own Network API" % (N_SLICES, SAMPLE_TEXT, threads),
+                   "bytes_per_step": sum(step_bytes(A_SHAPE, B_SHAPE, O_SHAPE).values())},
         "cpu_baseline": {"value": round(gbs, 4), "unit": UNIT, "cores": threads, "kind": kind,
-                         "sample": "%d concurrent replicas, each: %s" % (threads, SAMPLE_TEXT)},
+                         "sample": "the full step: %d slices, each %s" % (N_SLICES, SAMPLE_TEXT)},
         "e2e": {"value": round(gbs, 4), "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
+        "results": {"sum": total[0], "max": total[1]},
     }
     print(json.dumps(line))
     return 0
@@ -347,43 +357,86 @@ def per_op_sweep(torch, F, device, peak):
     return rows
 
 
-def run_e2e(n_local, local_rank, a_host, b_host, steps, warmup, dist, torch):
-    """The chain through the Shadow Network API (C++ host library) with HOST buffers: Forward copies
-    the pinned inputs to the device, runs Binary/Reduce/Reduce, and the results are read back."""
+class _DevScalar:
+    """A float32 scalar that lives in a Network blob, exposed to torch without a copy."""
+
+    def __init__(self, ptr: int):
+        self.__cuda_array_interface__ = {"shape": (1,), "typestr": "<f4", "data": (ptr, False), "version": 2}
+
+
+def run_e2e(n_local, local_rank, a_host, b_host, steps, warmup, comm, torch):
+    """The chain through the Shadow Network API (C++ host library) with HOST buffers: every step's
+    Forward copies the pinned inputs to the device and runs Binary/Reduce/Reduce, and the step's two
+    results are read back to the host.  Two Networks (each with its own stream, as in the reference:
+    one Workspace + Context + stream per Network) are driven by two host threads and take the steps
+    alternately, so the input copy of step i+1 runs beside the kernels of step i.  With several
+    ranks the step also holds the exchange: each rank's two scalars go through ONE all-gather of
+    the C entry points (issued by the main thread in step order) and one 16*N-byte read."""
+    import concurrent.futures as cf
     import shadow_b200
     from shadow_b200.netapi import Net
     lib = shadow_b200.host_library()
     a_shape = (n_local,) + A_SHAPE[1:]
-    net = Net(lib, "c5").input({"a": a_shape, "b": B_SHAPE})
-    net.op("Binary", ["a", "b"], ["o"], operation=MUL)
-    net.op("Reduce", ["o"], ["s"], operation=RED_SUM, axes=[], keep_dims=False)
-    net.op("Reduce", ["o"], ["m"], operation=RED_MAX, axes=[], keep_dims=False)
-    net.load("Native", device_id=local_rank, out_blobs=["s", "m"])
     ins = {"a": a_host.data_ptr(), "b": b_host.data_ptr()}
-    world = dist.get_world_size() if dist is not None else 1
-    res = None
-    for i in range(warmup + steps):
-        if i == warmup:
-            if dist is not None:
-                dist.barrier()
-            t0 = time.perf_counter()
+    world = comm.n_ranks if comm is not None else 1
+    device = torch.device("cuda", local_rank)
+
+    def make():
+        net = Net(lib, "c5").input({"a": a_shape, "b": B_SHAPE})
+        net.op("Binary", ["a", "b"], ["o"], operation=MUL)
+        net.op("Reduce", ["o"], ["s"], operation=RED_SUM, axes=[], keep_dims=False)
+        net.op("Reduce", ["o"], ["m"], operation=RED_MAX, axes=[], keep_dims=False)
+        net.load("Native", device_id=local_rank, out_blobs=["s", "m"])
         net.forward(ins)
-        s, m = float(net.blob("s").ravel()[0]), float(net.blob("m").ravel()[0])
-        if world > 1:
-            # the Network API is single-device, as in the reference: ranks combine their two scalars
-            pair = torch.tensor([s, m], dtype=torch.float64, device="cuda:%d" % local_rank)
-            gathered = [torch.empty_like(pair) for _ in range(world)]
-            dist.all_gather(gathered, pair)
-            s = float(sum(g[0].item() for g in gathered))
-            m = float(max(g[1].item() for g in gathered))
-        res = (s, m)
-    dt = time.perf_counter() - t0
-    if dist is not None:
-        tmax = torch.tensor([dt], dtype=torch.float64, device="cuda:%d" % local_rank)
-        dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
+        return net
+
+    nets = [make(), make()]
+    views = None
+    if world > 1:
+        views = [(torch.as_tensor(_DevScalar(n.device_ptr("s")), device=device),
+                  torch.as_tensor(_DevScalar(n.device_ptr("m")), device=device)) for n in nets]
+        record = torch.empty(2, dtype=torch.float64, device=device)
+        gathered = torch.empty(2 * world, dtype=torch.float64, device=device)
+        landing = torch.empty(2 * world, dtype=torch.float64).pin_memory()
+
+    def forward(k):
+        torch.cuda.set_device(local_rank)
+        nets[k].forward(ins)        # H2D of both inputs, three operators, synchronise
+
+    def results(k):
+        if world == 1:
+            return float(nets[k].blob("s").ravel()[0]), float(nets[k].blob("m").ravel()[0])
+        sv, mv = views[k]
+        record[0:1].copy_(sv)       # float -> double on the device
+        record[1:2].copy_(mv)
+        comm.allgather_records(record, gathered, torch.cuda.current_stream().cuda_stream)
+        landing.copy_(gathered, non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        g = landing.numpy()
+        return float(np.sum(g[0::2])), float(np.max(g[1::2]))   # rank order
+
+    res = None
+    with cf.ThreadPoolExecutor(max_workers=2) as pool:
+        total = warmup + steps
+        pending = {}
+        for i in range(min(2, total)):
+            pending[i] = pool.submit(forward, i % 2)
+        t0 = None
+        for i in range(total):
+            if i == warmup:
+                t0 = time.perf_counter()
+            pending.pop(i).result()
+            res = results(i % 2)
+            if i + 2 < total:
+                pending[i + 2] = pool.submit(forward, i % 2)
+        dt = time.perf_counter() - t0
+    if comm is not None:
+        tmax = torch.tensor([dt], dtype=torch.float64, device=device)
+        comm.allreduce_partials(tmax, RED_MAX, torch.cuda.current_stream().cuda_stream)
         dt = float(tmax.item())
     h2d = a_host.numel() * 4 + b_host.numel() * 4
-    return dt / steps, h2d, 8, res
+    d2h = 8 if world == 1 else 16 * world
+    return dt / steps, h2d, d2h, res
 
 
 def run_b200_arm(args):
@@ -397,19 +450,25 @@ def run_b200_arm(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    dist = None
+    dist, comm = None, None
     if world > 1:
         import torch.distributed as dist
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        os.environ["NCCL_DEBUG"] = "WARN"      # keep stdout to the one JSON line
+        # communicator set-up lines (rank count, transport) go to stderr; stdout stays the one JSON line
+        os.environ.setdefault("NCCL_DEBUG", "INFO")
+        os.environ.setdefault("NCCL_DEBUG_SUBSYS", "INIT")
+        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
         # a rank that stalls in a collective must not keep 8 GPUs busy: the whole run takes well
         # under a minute, so after 3 minutes the process ends itself
         safety = threading.Timer(180.0, os._exit, args=(3,))
         safety.daemon = True
         safety.start()
-        opts = dist.ProcessGroupNCCL.Options()
-        opts.is_high_priority_stream = True    # the 16-byte exchange must not queue behind a full-GPU kernel
-        dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local_rank), pg_options=opts)
+        torch.cuda.set_device(local_rank)
+        # torch.distributed carries the rendezvous (the 128-byte identifier, barriers); the data path's
+        # one exchange goes through the C entry points of libsb200_nccl.so on its own communicator
+        dist.init_process_group(backend="nccl", device_id=torch.device("cuda", local_rank))
+        from shadow_b200.comm import Communicator
+        comm = Communicator.from_process_group()
     assert world == args.gpus or world == 1, "launch with torchrun --nproc-per-node %d" % args.gpus
     torch.cuda.set_device(local_rank)
     device = torch.device("cuda", local_rank)
@@ -427,50 +486,39 @@ def run_b200_arm(args):
     O = torch.empty((n_local,) + O_SHAPE[1:], dtype=torch.float32, device=device)
     torch.cuda.synchronize()
 
-    r_sum = torch.empty(1, dtype=torch.float32, device=device)
-    r_max = torch.empty(1, dtype=torch.float32, device=device)
     # Steps are captured `chunk` at a time (the largest divisor of --steps up to 10), each with its
-    # own 16-byte record, so that the exchange of step i can run beside the Mul of step i+1.
+    # own record slot, so that the exchange of step i can run beside the Mul of step i+1.
     chunk = 1
     if world > 1 and not args.no_graph:
         chunk = max(c for c in range(1, 11) if args.steps % c == 0)
-    records = torch.empty(chunk, 2, dtype=torch.float64, device=device)   # this rank's (sum, max) partials per step
-    gathers = torch.empty(chunk, 2 * world, dtype=torch.float64, device=device)
     total = numel(O_SHAPE)
+    # the package's sharded reduction: both reductions behind ONE all-gather of 16 bytes per rank,
+    # folded in rank order on every rank (sharded.ReduceMany over the C entry points)
+    many = sharded.ReduceMany([RED_SUM, RED_MAX], (n_local,) + O_SHAPE[1:], [], O_SHAPE[0], device, comm=comm, slots=chunk)
+    # the 16-byte exchange must not queue behind a full-GPU kernel: highest priority
     side = torch.cuda.Stream(device=device, priority=-1) if world > 1 else None
 
-    def step(evs=None, slot=0, overlap=False):
-        """One pass of the chain.  With several ranks the two reductions share ONE collective: each
-        rank's double partials (sum, max) are all-gathered and merged locally in rank order.  With
-        `overlap` the collective and the merge go to a side stream that the caller joins later, so
-        the next step's Mul does not wait for them."""
-        record, gathered = records[slot], gathers[slot]
-        def mark(i):
-            if evs is not None:
-                evs[i].record()
-        mark(0)
+    def step(slot=0, overlap=False):
+        """One pass of the chain.  With `overlap` the exchange and the fold go to the side stream that
+        the caller joins later (many.join()), so the next step's Mul does not wait for them."""
         F.binary(A, B, MUL, out=O)
-        mark(1)
-        if world == 1:
-            F.reduce(O, RED_SUM, [], out=r_sum)
-            mark(2)
-            F.reduce(O, RED_MAX, [], out=r_max)
-        else:
-            F.reduce_partial(O, RED_SUM, [], out=record[0:1])
-            mark(2)
-            F.reduce_partial(O, RED_MAX, [], out=record[1:2])
+        many(O, slot=slot, side_stream=side if overlap else None)
 
-            def exchange():
-                dist.all_gather_into_tensor(gathered, record)
-                F.reduce_combine(gathered, world, 2, 1, RED_SUM, total, out=r_sum)
-                F.reduce_combine(gathered[1:], world, 2, 1, RED_MAX, total, out=r_max)
-            if overlap:
-                side.wait_stream(torch.cuda.current_stream())
-                with torch.cuda.stream(side):
-                    exchange()
-            else:
-                exchange()
-        mark(3)
+    def step_with_events(evs):
+        """The three kernels of a rank's step launched directly with events between them (the
+        exchange is left out: per-operator durations)."""
+        evs[0].record()
+        F.binary(A, B, MUL, out=O)
+        evs[1].record()
+        if world == 1:
+            F.reduce(O, RED_SUM, [], out=many.results[0][0])
+            evs[2].record()
+            F.reduce(O, RED_MAX, [], out=many.results[0][1])
+        else:
+            F.reduce_partial(O, RED_SUM, [], out=many.records[0][0:1])
+            evs[2].record()
+            F.reduce_partial(O, RED_MAX, [], out=many.records[0][1:2])
+        evs[3].record()
 
     for _ in range(max(args.warmup, 3)):
         step()
@@ -486,7 +534,7 @@ def run_b200_arm(args):
             for c in range(chunk):
                 step(slot=c, overlap=chunk > 1)
             if chunk > 1:
-                torch.cuda.current_stream().wait_stream(side)   # join: every exchange of the chunk has finished
+                many.join()   # every exchange of the chunk has finished
         launches_per_step = (capi.launch_count() - launches_before) // chunk
         for _ in range(3):
             graph.replay()
@@ -502,40 +550,61 @@ def run_b200_arm(args):
     if dist is not None:
         dist.barrier()
     torch.cuda.synchronize()
-    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     launches_before = capi.launch_count()
-    with ClockSampler(local_rank) as clocks:
+
+    def timed_block():
+        """EXACTLY args.steps steps between two events; max over ranks of the device time."""
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         start.record()
         for k in range(args.steps // chunk):
             run_chunk()
         end.record()
         torch.cuda.synchronize()
-        ms_total = start.elapsed_time(end)
+        ms = start.elapsed_time(end)
         if dist is not None:
-            tmax = torch.tensor([ms_total], dtype=torch.float64, device=device)
+            tmax = torch.tensor([ms], dtype=torch.float64, device=device)
             dist.all_reduce(tmax, op=dist.ReduceOp.MAX)
-            ms_total = float(tmax.item())
-        # A timed region shorter than a few sampling periods yields no clock samples: keep the very
-        # same loop running (untimed) under the sampler until about 0.25 s of load have been seen.
-        # The count derives from the max-over-ranks time, so every rank runs the same number of
-        # steps (each step holds a collective).
-        extra = 0
-        if ms_total < 250.0 and not args.no_clocks:
-            extra = int(min(5000, (250.0 - ms_total) / max(ms_total / args.steps, 1e-3)))
-            for k in range(extra // chunk):
-                run_chunk()
-            torch.cuda.synchronize()
-    launches = (launches_per_step * args.steps) if graph is not None else (capi.launch_count() - launches_before)
+            ms = float(tmax.item())
+        return ms
+
+    with ClockSampler(local_rank) as clocks:
+        ms_total = timed_block()          # the reported number: the first block of exactly --steps steps
+        # The same block again, several times: a timed region of a few milliseconds yields no clock
+        # samples and says nothing about run-to-run spread.  The count derives from the max-over-ranks
+        # time, so every rank runs the same number of blocks (each step holds a collective).
+        repeats = [ms_total]
+        if not args.no_clocks:
+            n_more = int(min(200, max(4, 300.0 / max(ms_total, 1e-3))))
+            for _ in range(n_more):
+                repeats.append(timed_block())
+    extra = (len(repeats) - 1) * args.steps
+    launches = (launches_per_step * args.steps) if graph is not None else (capi.launch_count() - launches_before) // len(repeats)
     if dist is not None:
         dist.barrier()
+    last = (chunk - 1) if graph is not None else 0
+    r_sum, r_max = many.results[last]
     s, m = r_sum.clone(), r_max.clone()
+    # ---- self-check of the sharded result: every rank's double partials of the last step, brought to
+    # the host once and folded there in rank order, must give the bits the device path produced
+    results_check = None
+    if world > 1:
+        mine = many.records[last].clone()
+        parts = [torch.empty_like(mine) for _ in range(world)]
+        dist.all_gather(parts, mine)
+        host = np.stack([p.cpu().numpy() for p in parts])            # [rank, (sum, max)]
+        acc = 0.0
+        for r in range(world):
+            acc += float(host[r, 0])
+        want_sum, want_max = float(np.float32(acc)), float(np.float32(host[:, 1].max()))
+        results_check = {"sum_from_rank_partials": want_sum, "max_from_rank_partials": want_max,
+                         "matches": bool(want_sum == float(s.item()) and want_max == float(m.item()))}
 
     # ---- per-operator durations: the same steps launched directly with CUDA events between the
     # operators (events cannot be read inside a graph replay)
     n_inst = max(3, min(args.steps, 20))
     op_events = [[torch.cuda.Event(enable_timing=True) for _ in range(4)] for _ in range(n_inst)]
     for k in range(n_inst):
-        step(op_events[k])
+        step_with_events(op_events[k])
     torch.cuda.synchronize()
     ms_step = ms_total / args.steps
     bytes_job = step_bytes(A_SHAPE, B_SHAPE, O_SHAPE)          # whole job, all ranks
@@ -544,7 +613,6 @@ def run_b200_arm(args):
     op_ms = {
         "binary_broadcast_mul": statistics.mean(e[0].elapsed_time(e[1]) for e in op_events),
         "reduce_sum_all": statistics.mean(e[1].elapsed_time(e[2]) for e in op_events),
-        # with several ranks this span also holds the all-gather and the two merge kernels
         "reduce_max_all": statistics.mean(e[2].elapsed_time(e[3]) for e in op_events),
     }
     peak, peak_kind = measured_peak()
@@ -560,7 +628,7 @@ def run_b200_arm(args):
     if args.no_e2e:
         e2e_s, h2d, d2h, e2e_res = float("nan"), 0, 0, (None, None)
     else:
-        e2e_s, h2d, d2h, e2e_res = run_e2e(n_local, local_rank, a_host, b_host, max(3, min(args.steps, 10)), 2, dist, torch)
+        e2e_s, h2d, d2h, e2e_res = run_e2e(n_local, local_rank, a_host, b_host, max(4, min(args.steps, 20)), 4, comm, torch)
     e2e_value = sum(bytes_job.values()) / e2e_s / 1e9
 
     line = {
@@ -571,22 +639,32 @@ def run_b200_arm(args):
                                "ReduceSum all axes, ReduceMax all axes; dim 0 split over the ranks",
                    "l2": "inputs larger than L2 (each step streams >= 256 MiB per GPU; no flush interposed)",
                    "bytes_per_step": sum(bytes_job.values()),
-                   "collective": ("one nccl all_gather of 16 B per rank per step (sum and max partials together)"
+                   "collective": ("one NCCL all-gather of 16 B per rank per step (sum and max partials together) through the C entry "
+                                  "sb200_sharded_reduce_finish (sharded.ReduceMany)"
                                   + (", on a side stream beside the next step's Mul" if chunk > 1 else "")) if world > 1 else "none",
                    "launch": ("cuda graph replay, %d steps per graph" % chunk) if graph is not None else "direct launches"},
         "frac_of_8tbs_per_gpu": round(value / world / NOMINAL_PEAK_GBS, 4),
         "roofline": roofline, "per_step_ops": per_step_ops,
         "e2e": None if args.no_e2e else {"value": round(e2e_value, 3), "unit": UNIT, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
-                "ms_per_step": round(e2e_s * 1e3, 3), "api": "Shadow::Network::Forward + GetBlobDataByName (C++ host library)"},
+                "ms_per_step": round(e2e_s * 1e3, 3),
+                "api": "Shadow::Network::Forward + GetBlobDataByName (C++ host library); two Networks on two host threads "
+                       "take the steps alternately" + ("; ranks combine through sb200_allgather_records" if world > 1 else "")},
         "gpu_launches": launches,
-        "clocks": dict(clocks.summary(), window="timed region + %d identical untimed steps" % extra),
+        "clocks": dict(clocks.summary(), window="timed region + %d identical steps (the repeats)" % extra),
+        "repeats": {"blocks": len(repeats), "steps_per_block": args.steps,
+                    "ms_per_step_min": round(min(repeats) / args.steps, 4),
+                    "ms_per_step_median": round(statistics.median(repeats) / args.steps, 4),
+                    "ms_per_step_max": round(max(repeats) / args.steps, 4),
+                    "note": "value and ms_per_step are the FIRST block; the others repeat it under the clock sampler"},
         "results": {"sum": result_sum, "max": result_max, "e2e_sum": e2e_res[0], "e2e_max": e2e_res[1]},
     }
+    if results_check is not None:
+        line["results_check"] = results_check
     if rank == 0 and world == 1:
         if not args.no_sweep:
             line["per_op_256mb"] = per_op_sweep(torch, F, device, peak)
         if not args.no_cpu:
-            gbs, ms, kind, cpu_res, a_sample = time_cpu(1, 3, 1)
+            gbs, ms, kind, _, a_sample, cpu_res = time_cpu(1, 3, 1, slices=1)
             # the same sample on the GPU, against the CPU result: parity of what was timed
             As = torch.from_numpy(a_sample).to(device)
             Os = F.binary(As, B, MUL)
@@ -610,6 +688,8 @@ def run_b200_arm(args):
         graph = None
         torch.cuda.synchronize()
         dist.barrier()
+        if comm is not None:
+            comm.close()
         dist.destroy_process_group()
         watchdog.cancel()
     return 0

@@ -1,5 +1,6 @@
 """Build the CUDA kernel library (``shadow_b200/lib/libsb200.so``) and the C++ host library
-(``shadow_b200/lib/libshadow_b200.so``) in-tree with nvcc / g++ for sm_100a.
+(``shadow_b200/lib/libshadow_b200.so``) in-tree with nvcc / g++ for sm_100a, and the NCCL combine library
+(``shadow_b200/lib/libsb200_nccl.so``).
 
     python -m shadow_b200.build [--force]
 """
@@ -20,6 +21,7 @@ LIB_DIR = os.path.join(PKG, "lib")
 OBJ_DIR = os.path.join(PKG, "build")
 KERNEL_LIB = os.path.join(LIB_DIR, "libsb200.so")
 HOST_LIB = os.path.join(LIB_DIR, "libshadow_b200.so")
+COMM_LIB = os.path.join(LIB_DIR, "libsb200_nccl.so")
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -102,8 +104,38 @@ def build_host(force: bool = False) -> str | None:
     return HOST_LIB
 
 
+def _nccl_paths():
+    """(include dir, library file) of an NCCL to build against: the system one, else the copy that
+    ships inside the Python environment (the soname is libnccl.so.2 either way, so at run time the
+    process's already loaded NCCL - torch's, in a Python job - is the one that is used)."""
+    candidates = [("/usr/include", "/usr/lib/x86_64-linux-gnu/libnccl.so.2")]
+    for base in sys.path:
+        candidates.append((os.path.join(base, "nvidia", "nccl", "include"), os.path.join(base, "nvidia", "nccl", "lib", "libnccl.so.2")))
+    for inc, lib in candidates:
+        if os.path.exists(os.path.join(inc, "nccl.h")) and os.path.exists(lib):
+            return inc, lib
+    return None
+
+
+def build_comm(force: bool = False) -> str | None:
+    """libsb200_nccl.so: the cross-GPU combine entry points (include/sb200_nccl.h).  None when no
+    NCCL header/library is installed."""
+    src = os.path.join(PKG, "comm", "sb200_nccl.cpp")
+    nccl = _nccl_paths()
+    if nccl is None or not os.path.exists(src):
+        return None
+    deps = [src, KERNEL_LIB, os.path.abspath(__file__)] + glob.glob(os.path.join(REPO, "include", "*.h"))
+    if not force and not _stale(COMM_LIB, deps):
+        return COMM_LIB
+    cuda_home = os.path.dirname(os.path.dirname(_nvcc()))
+    _run(["g++", "-O2", "-std=c++17", "-fPIC", "-Wall", "-shared", "-o", COMM_LIB, src,
+          "-I" + os.path.join(REPO, "include"), "-I" + os.path.join(cuda_home, "include"), "-I" + nccl[0],
+          "-L" + LIB_DIR, "-lsb200", "-Wl,-rpath,$ORIGIN", nccl[1], "-L" + os.path.join(cuda_home, "lib64"), "-lcudart"])
+    return COMM_LIB
+
+
 def build_all(force: bool = False, verbose: bool = False):
-    return {"kernels": build_kernels(force, verbose), "host": build_host(force)}
+    return {"kernels": build_kernels(force, verbose), "host": build_host(force), "comm": build_comm(force)}
 
 
 if __name__ == "__main__":

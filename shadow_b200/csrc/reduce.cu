@@ -806,6 +806,10 @@ int sb200_reduce(const float* x, const int* in_shape, int num_axes, const int* a
 
 int sb200_reduce_static(const float* x, const int* in_shape, int num_axes, const int* axes, int n_axes,
                         int operation, float* y, void* stream) {
+  // the plan's own status (bad argument, or a geometry the kernels do not cover) is what the caller sees
+  Plan probe;
+  const int plan_rc = make_plan(in_shape, num_axes, axes, n_axes, x, &probe);
+  if (plan_rc != SB200_OK) return plan_rc;
   const int64_t need = sb200_reduce_scratch_bytes(in_shape, num_axes, axes, n_axes, operation);
   if (need < 0) return SB200_ERR_BAD_ARGUMENT;
   if (need > kStaticScratchBytes) {

@@ -6,9 +6,11 @@ holds and processes its slab ``[start:stop]`` of dim 0; operands whose dim 0 is 
 ``B[1,C,1,W]``, per-channel gamma/beta) are replicated.  Elementwise / broadcast / Scale / Softmax
 (axis != 0) and reductions that keep dim 0 need no communication at all.  A reduction whose axes
 include dim 0 reduces the slab to one DOUBLE partial per output (``sb200_reduce_partial``),
-combines the ranks' partials with ONE all-reduce (sum, product, max or min - 8 bytes per output),
-and finishes on every rank (``sb200_reduce_finalize``: cast, or divide by the global count for
-Avg, or sqrt for L2).  The reference has no multi-device code; this layer is new.
+combines the ranks' partials with ONE collective - an all-reduce (``reduce``) or, where several
+reductions share it and the bits must not depend on the collective's order, an all-gather of the
+ranks' records folded in rank order (``ReduceMany``; through the C entry points of
+``libsb200_nccl.so`` when given a ``comm.Communicator``) - and finishes on every rank (cast, or divide
+by the global count for Avg, or sqrt for L2).  The reference has no multi-device code; this layer is new.
 
 The partial/finalize steps are injectable so the host logic (slab bounds, collective choice,
 global counts) can be exercised with CPU tensors over the ``gloo`` backend.
@@ -110,18 +112,29 @@ def reduce(x_local: torch.Tensor, operation: int, axes: Sequence[int], global_di
 
 class ReduceMany:
     """Several reductions (different operations, same axes) of one dim-0-sharded tensor with ONE
-    collective: every rank writes its double partials into one record, the records are
-    all-gathered, and each rank merges them locally in rank order (deterministic) and finishes.
-    Buffers are allocated once, so a step can be captured in a CUDA graph and replayed."""
+    exchange per call: every rank writes its double partials into one record, the records are
+    all-gathered, and each rank folds them locally in rank order (deterministic) and finishes.
+
+    Buffers are allocated once, so calls can be captured in a CUDA graph and replayed.  There are
+    ``slots`` independent sets of (record, gathered, results): with ``side_stream`` given to a call,
+    the exchange and the fold of that call go to the side stream (which first waits for the
+    partials), so the caller's stream is free to start the next step's kernels at once; the results
+    of slot k are valid after ``join()``.  A graph that holds ``slots`` consecutive steps, each in
+    its own slot, followed by one ``join()``, overlaps every exchange but the last with compute.
+
+    ``comm`` is a ``shadow_b200.comm.Communicator`` (the C entry points over NCCL).  Without one the
+    exchange is ``torch.distributed.all_gather_into_tensor`` on ``group``, which together with the
+    injectable ``partial_fn`` / ``combine_fn`` lets the host logic run on CPU tensors over gloo.
+
+    A rank whose slab is empty (more ranks than entries of dim 0) contributes the neutral record."""
 
     def __init__(self, operations: Sequence[int], local_shape: Sequence[int], axes: Sequence[int], global_dim0: int,
-                 device, group=None):
-        from . import functional as F
-        self.F = F
+                 device, group=None, comm=None, slots: int = 1, partial_fn: Optional[Callable] = None,
+                 combine_fn: Optional[Callable] = None, local_fn: Optional[Callable] = None):
         self.ops = list(operations)
         self.axes = list(axes) if len(axes) else list(range(len(local_shape)))
-        self.group = group
-        self.rank, self.size = world()
+        self.group, self.comm = group, comm
+        self.rank, self.size = (comm.rank, comm.n_ranks) if comm is not None else world()
         self.count = 1
         self.total = 1
         for n, d in enumerate(local_shape):
@@ -129,22 +142,71 @@ class ReduceMany:
                 self.total *= global_dim0 if n == 0 else d
             else:
                 self.count *= d
+        self.empty = len(local_shape) > 0 and local_shape[0] == 0
         self.crosses = 0 in self.axes and self.size > 1
-        self.record = torch.empty(len(self.ops) * self.count, dtype=torch.float64, device=device)
-        self.gathered = torch.empty(self.size * self.record.numel(), dtype=torch.float64, device=device)
-        self.results = [torch.empty(self.count, dtype=torch.float32, device=device) for _ in self.ops]
+        self.slots = max(1, int(slots))
+        width = len(self.ops) * self.count
+        self.records = torch.empty(self.slots, width, dtype=torch.float64, device=device)
+        self.gathers = torch.empty(self.slots, self.size * width, dtype=torch.float64, device=device)
+        self.results = [[torch.empty(self.count, dtype=torch.float32, device=device) for _ in self.ops]
+                        for _ in range(self.slots)]
+        # the record of an empty slab: each reduction's neutral element
+        self.neutral = torch.cat([torch.full((self.count,), identity(op), dtype=torch.float64) for op in self.ops]).to(device)
+        self.partial_fn = partial_fn or self._cuda_partial
+        self.combine_fn = combine_fn or self._cuda_combine
+        self.local_fn = local_fn or self._cuda_local
+        self._side = None
 
-    def __call__(self, x_local: torch.Tensor):
-        F = self.F
+    # -- the CUDA steps (C ABI through `functional`)
+    @staticmethod
+    def _cuda_partial(x, operation, axes, out):
+        from . import functional as F
+        F.reduce_partial(x, operation, axes, out=out)
+
+    @staticmethod
+    def _cuda_combine(gathered, n_parts, stride, count, operation, total, out):
+        from . import functional as F
+        F.reduce_combine(gathered, n_parts, stride, count, operation, total, out=out)
+
+    @staticmethod
+    def _cuda_local(x, operation, axes, out):
+        from . import functional as F
+        F.reduce(x, operation, axes, keep_dims=True, out=out)
+
+    def _exchange(self, slot: int) -> None:
+        record, gathered, results = self.records[slot], self.gathers[slot], self.results[slot]
+        if self.comm is not None:
+            stream = torch.cuda.current_stream().cuda_stream
+            self.comm.sharded_reduce_finish(record, gathered, self.ops, self.count, self.total, results, stream)
+            return
+        dist.all_gather_into_tensor(gathered, record, group=self.group)
+        for i, op in enumerate(self.ops):
+            self.combine_fn(gathered[i * self.count:], self.size, record.numel(), self.count, op, self.total, results[i])
+
+    def __call__(self, x_local: torch.Tensor, slot: int = 0, side_stream=None):
+        if not 0 <= slot < self.slots:
+            raise ValueError("slot %d outside 0..%d" % (slot, self.slots - 1))
+        results = self.results[slot]
         if not self.crosses:
             for i, op in enumerate(self.ops):
-                F.reduce(x_local, op, self.axes, keep_dims=True, out=self.results[i])
-            return self.results
-        for i, op in enumerate(self.ops):
-            F.reduce_partial(x_local, op, self.axes, out=self.record[i * self.count:(i + 1) * self.count])
-        dist.all_gather_into_tensor(self.gathered, self.record, group=self.group)
-        stride = self.record.numel()
-        for i, op in enumerate(self.ops):
-            F.reduce_combine(self.gathered[i * self.count:], self.size, stride, self.count, op, self.total,
-                             out=self.results[i])
-        return self.results
+                self.local_fn(x_local, op, self.axes, results[i])
+            return results
+        record = self.records[slot]
+        if self.empty:
+            record.copy_(self.neutral)
+        else:
+            for i, op in enumerate(self.ops):
+                self.partial_fn(x_local, op, self.axes, record[i * self.count:(i + 1) * self.count])
+        if side_stream is None:
+            self._exchange(slot)
+        else:
+            side_stream.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side_stream):
+                self._exchange(slot)
+            self._side = side_stream
+        return results
+
+    def join(self) -> None:
+        """Make the current stream wait for every exchange issued on a side stream so far."""
+        if self._side is not None:
+            torch.cuda.current_stream().wait_stream(self._side)

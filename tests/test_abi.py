@@ -89,3 +89,33 @@ def test_missing_library_fails_loudly(monkeypatch):
     monkeypatch.setattr(capi, "LIB_PATH", "/nonexistent/libsb200.so")
     with pytest.raises(ImportError):
         capi.lib()
+
+
+def test_comm_library_exports_and_argument_checks():
+    """libsb200_nccl.so (include/sb200_nccl.h): every declared symbol is exported; arguments are
+    checked before NCCL is touched, so this needs neither a GPU nor peers."""
+    import ctypes
+    from shadow_b200 import comm
+    if sbuild.build_comm() is None:
+        pytest.skip("no NCCL header/library on this machine")
+    L = comm.lib()
+    names = declared_functions("sb200_nccl.h")
+    assert sorted(comm.EXPORTED) == names
+    for name in names:
+        assert hasattr(L, name), name
+    assert L.sb200_comm_new_id(None) == 1
+    handle = ctypes.c_void_p()
+    ident = b"\0" * comm.ID_BYTES
+    assert L.sb200_comm_create(ident, 2, 2, ctypes.byref(handle)) == 1      # rank outside the world
+    assert L.sb200_comm_create(ident, 0, 0, ctypes.byref(handle)) == 1
+    assert L.sb200_comm_create(None, 1, 0, ctypes.byref(handle)) == 1
+    assert L.sb200_comm_destroy(None) == 1
+    assert L.sb200_comm_query(None, None, None) == 1
+    assert L.sb200_allreduce_partials(None, 256, 4, 1, None) == 1           # no communicator
+    assert L.sb200_allgather_records(None, 256, 512, 4, None) == 1
+    ops = (ctypes.c_int * 1)(1)
+    outs = (ctypes.c_void_p * 1)(1024)
+    assert L.sb200_sharded_reduce_finish(None, 256, 512, 4, 1, ops, 4, 8, outs, None) == 1
+    assert L.sb200_comm_last_error() == b""
+    with pytest.raises(ValueError):
+        comm.Communicator(b"short", 1, 0)

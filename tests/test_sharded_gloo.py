@@ -117,3 +117,76 @@ def test_collective_choice():
     with pytest.raises(ValueError):
         sharded.collective_op(7)
     assert sharded.identity(0) == 1.0 and sharded.identity(2) < -3e38 and sharded.identity(1) == 0.0
+
+
+def _cpu_partial_into(x, operation, axes, out):
+    out.copy_(_cpu_partial(x, operation, axes).reshape(-1))
+
+
+def _cpu_combine_into(gathered, n_parts, stride, count, operation, total, out):
+    """What sb200_reduce_combine does: part p of output o at gathered[p*stride + o], folded in order."""
+    g = gathered.numpy()
+    acc = g[0:count].copy()
+    for p in range(1, n_parts):
+        nxt = g[p * stride:p * stride + count]
+        if operation == 0:
+            acc = acc * nxt
+        elif operation == 2:
+            acc = np.maximum(acc, nxt)
+        elif operation == 3:
+            acc = np.minimum(acc, nxt)
+        else:
+            acc = acc + nxt
+    out.copy_(_cpu_finalize(torch.from_numpy(acc), operation, total))
+
+
+def _cpu_local_into(x, operation, axes, out):
+    out.copy_(_cpu_local(x, operation, axes).reshape(-1))
+
+
+def _many_worker(rank, world, port, shape, out_dir):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    os.environ["MASTER_ADDR"], os.environ["MASTER_PORT"] = "127.0.0.1", str(port)
+    import torch.distributed as dist
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        full = cases.normal(5151, shape)
+        lo, hi = sharded.shard_bounds(shape[0], rank, world)
+        local = torch.from_numpy(np.ascontiguousarray(full[lo:hi]))
+        failures = []
+        ops = [1, 2, 3, 4, 6]
+        for axes in ([], [0, 2], [1]):
+            many = sharded.ReduceMany(ops, local.shape, axes, shape[0], "cpu", slots=2, partial_fn=_cpu_partial_into,
+                                      combine_fn=_cpu_combine_into, local_fn=_cpu_local_into)
+            for slot in (0, 1):
+                scaled = local * float(slot + 1)       # different data per slot: slots must not alias
+                res = many(scaled, slot=slot)
+                many.join()                            # no side stream was used: a no-op
+                for op, r in zip(ops, res):
+                    want = orc.reduce(full * np.float32(slot + 1), op, axes, keep_dims=True)
+                    if 0 not in (axes or list(range(len(shape)))):
+                        want = want[lo:hi]
+                    n = max(2, int(np.prod([shape[a] for a in (axes or range(len(shape)))])))
+                    if r.numel() != want.size or not np.allclose(r.numpy().ravel(), want.ravel(), rtol=1e-5 * np.log2(n), atol=0):
+                        failures.append((op, axes, slot))
+            try:
+                many(local, slot=2)
+                failures.append("slot range not checked")
+            except ValueError:
+                pass
+        with open(os.path.join(out_dir, "many%d.txt" % rank), "w") as f:
+            f.write(repr(failures))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world,shape", [(2, (6, 5, 7)), (3, (2, 4, 3))])
+def test_reduce_many_over_gloo(tmp_path, world, shape):
+    """Several reductions behind one all-gather, two record slots; world 3 over a batch of 2 leaves a
+    rank with an empty slab, which must contribute the neutral record instead of failing before the
+    collective (the other ranks would wait in it for ever)."""
+    port = 31500 + (os.getpid() % 2000) + world
+    mp.spawn(_many_worker, args=(world, port, shape, str(tmp_path)), nprocs=world, join=True)
+    for r in range(world):
+        assert open(os.path.join(str(tmp_path), "many%d.txt" % r)).read() == "[]"

@@ -48,11 +48,27 @@ def test_static_scratch_matches_caller_scratch_twice(shape, axes, operation):
                                            stream), "sb200_reduce_static")
         assert capi.launch_count() - before == 2        # first-stage kernel + finishing kernel
         torch.cuda.synchronize()
+        # the property the entry point exists for: the call takes no device memory.  Free memory as
+        # the driver reports it (not torch's caching allocator) is the same before and after a call.
+        free_before = torch.cuda.mem_get_info()[0]
+        capi.check(lib.sb200_reduce_static(_ptr(x), shape_c, len(shape), axes_c, len(axes), operation, _ptr(got),
+                                           stream), "sb200_reduce_static")
+        torch.cuda.synchronize()
+        assert torch.cuda.mem_get_info()[0] == free_before
         w, g = want.cpu().numpy(), got.cpu().numpy()
         # same plan, same kernels, same combination order: identical bits (the tests' bar for
         # reductions is 1e-5*log2(n) relative; this is far inside it)
         assert np.array_equal(w.view(np.uint32), g.view(np.uint32))
         assert not np.isnan(g).any()
+        if call == 1:
+            # and against the CPU oracle, at the reductions' bar
+            from oracle import oracle as orc
+            ref = orc.reduce(x.cpu().numpy(), operation, axes, keep_dims=True)
+            n = int(np.prod([shape[a] for a in axes]))
+            if operation == 2:
+                assert np.array_equal(ref, g)
+            else:
+                assert np.allclose(g, ref, rtol=1e-5 * np.log2(n), atol=0)
 
 
 def test_static_scratch_without_split_needs_no_buffer():
@@ -81,6 +97,15 @@ def test_oversized_reduction_is_refused_before_launch():
     before = capi.launch_count()
     rc = lib.sb200_reduce_static(_ptr(dummy), shape_c, 2, axes_c, 1, 1, _ptr(dummy), None)
     assert rc == 4
+    assert capi.launch_count() == before
+    # a geometry that the planner refuses keeps its own status (more than 8 axes after collapsing)
+    many_axes = [2, 3] * 9
+    odd_axes = list(range(0, 18, 2))
+    rc2 = lib.sb200_reduce_static(_ptr(dummy), capi.ints(many_axes), 18, capi.ints(odd_axes), 9, 1, _ptr(dummy), None)
+    assert rc2 == lib.sb200_reduce(_ptr(dummy), capi.ints(many_axes), 18, capi.ints(odd_axes), 9, 1, _ptr(dummy), None, 0, None)
+    assert rc2 in (1, 2)
+    rc3 = lib.sb200_reduce_static(_ptr(dummy), shape_c, 2, capi.ints([5]), 1, 1, _ptr(dummy), None)   # axis out of range
+    assert rc3 == 1
     assert capi.launch_count() == before
     text = lib.sb200_last_cuda_error().decode()
     assert str(need) in text and str(STATIC_BYTES) in text
