@@ -451,8 +451,14 @@ def run_b200_arm(args):
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     dist, comm = None, None
+    json_out = sys.stdout
     if world > 1:
         import torch.distributed as dist
+        # NCCL writes its version banner to the process's stdout whatever NCCL_DEBUG_FILE says: move
+        # file descriptor 1 to stderr for the run and keep the real stdout for the one JSON line
+        sys.stdout.flush()
+        json_out = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         # communicator set-up lines (rank count, transport) go to stderr; stdout stays the one JSON line
         os.environ.setdefault("NCCL_DEBUG", "INFO")
@@ -675,7 +681,7 @@ def run_b200_arm(args):
                                     "sample": SAMPLE_TEXT, "ms_per_sample_step": round(ms, 2),
                                     "sample_parity": bool(abs(gs - cpu_res[0]) <= tol * abs(cpu_res[0]) and gm == cpu_res[1])}
     if rank == 0:
-        print(json.dumps(line), flush=True)
+        print(json.dumps(line), file=json_out, flush=True)
     # ---- teardown.  Everything has been reported; a collective captured in a CUDA graph must be
     # released before the communicator goes away, and a teardown that stalls must not keep the job
     # (and the GPUs) alive: after 20 s the process exits on its own.
