@@ -72,7 +72,10 @@ inline bool plan_colwalk(const void* x, const void* y, int64_t outer, int64_t di
     const double occ = static_cast<double>(per_sm * T) / budget;
     int64_t resident = static_cast<int64_t>(sms) * per_sm;
     const double waves = static_cast<double>(blocks) / static_cast<double>(resident);
-    const double tail = waves >= 8.0 ? 1.0 : waves / static_cast<double>(static_cast<int64_t>(waves + 0.999999));
+    // single-pass walks stream whole planes: a short last wave costs them nothing measurable (its few
+    // blocks get the bandwidth of the idle SMs), while the kernels that hold a patch lose the time of
+    // their barriers and merges in it
+    const double tail = (use == kWalkOnePass || waves >= 8.0) ? 1.0 : waves / static_cast<double>(static_cast<int64_t>(waves + 0.999999));
     if (resident > blocks) resident = blocks;
     const double footprint = static_cast<double>(resident) * static_cast<double>(patch_bytes);
     const double l2 = (use != kWalkTwoPass || footprint <= 64e6) ? 1.0 : (footprint <= 100e6 ? 0.9 : 0.75);
@@ -102,8 +105,12 @@ inline bool plan_colwalk(const void* x, const void* y, int64_t outer, int64_t di
         if (P > outer) P = outer;
         const int64_t blocks = (outer + P - 1) / P;
         if (blocks >= (1ll << 31)) continue;
-        const double score = rate(T, static_cast<double>(P * tact) / T, P * chunk * p * 16, blocks,
-                                               static_cast<double>(chunk) / static_cast<double>(k));
+        // single-pass walks: the longer the contiguous run a block reads per step, the better DRAM
+        // pages are used (measured on [1024,512,14,14] over axis 1: 7840-byte runs 0.77 of 8 TB/s,
+        // 3920-byte runs 0.70)
+        const double run = (use != kWalkOnePass || P * tact * 16 >= 6144) ? 1.0 : (P * tact * 16 >= 3072 ? 0.96 : 0.92);
+        const double score = run * rate(T, static_cast<double>(P * tact) / T, P * chunk * p * 16, blocks,
+                                        static_cast<double>(chunk) / static_cast<double>(k));
         if (score > best + 1e-9) {
           best = score;
           b.tiled = 0, b.threads = T, b.tact = static_cast<int>(tact), b.P = static_cast<int>(P);
@@ -255,13 +262,6 @@ __device__ __forceinline__ void colwalk_merge(const ColWalk& q, T* sm, Op op, T 
 // budget.  A thread only ever reads the slots it filled itself, after cp.async.wait_group: no block
 // barrier, no mbarrier, nothing to spin on.
 // fn(v, k0, valid): v[0..valid) are the float4 of steps k0..k0+valid; v[valid..U) hold stale bytes.
-__device__ __forceinline__ void cp_async16(uint32_t smem_addr, const void* gptr) {
-  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr), "l"(gptr) : "memory");
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
-template <int N>
-__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
-
 template <int U, int NB, typename F>
 __device__ __forceinline__ void colwalk_stream(const float4* ptr, int64_t step, int cnt, float4* ring, F&& fn) {
   // ring: this thread's slot 0; slot i of the thread is ring[i * blockDim.x]

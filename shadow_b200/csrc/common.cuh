@@ -112,4 +112,12 @@ struct OpMulD { __device__ __forceinline__ double operator()(double a, double b)
 struct OpMaxF { __device__ __forceinline__ float operator()(float a, float b) const { return (a < b) ? b : a; } };
 struct OpMinF { __device__ __forceinline__ float operator()(float a, float b) const { return (b < a) ? b : a; } };
 
+// ---- asynchronous 16-byte copies global -> shared (no register staging) ---------------------------
+__device__ __forceinline__ void cp_async16(uint32_t smem_addr, const void* gptr) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr), "l"(gptr) : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
 }  // namespace sb200

@@ -5,8 +5,9 @@
 // Concat, Stack and Slice are one geometry: a "wide" tensor [outer, total] whose rows are the
 // concatenation of the rows of N "parts" [outer, width_k].  The reference launches one strided
 // copy per part; here one launch moves all parts (up to 16 per launch, longer lists chained).
-// Permute collapses dimensions that stay adjacent, then transposes 32x32 tiles through shared
-// memory whenever the innermost dim changes (batched over the other dims) and uses an
+// Permute collapses dimensions that stay adjacent, then transposes tiles through shared memory
+// whenever the innermost dim changes (batched over the other dims; 64x64 tiles moved as float4 on
+// both sides when extents and steps are multiples of 4, else 32x32 tiles of floats) and uses an
 // index-arithmetic gather when the innermost dim stays (reads and writes both contiguous); no index
 // tables are uploaded (the reference copies three int arrays to the device per call).
 #include "common.cuh"
@@ -200,6 +201,61 @@ permute_tile_kernel(const float* __restrict__ x, float* y, const __grid_constant
     }
 }
 
+// The same transposition with 128-bit accesses on both sides, for extents and steps that are
+// multiples of 4 floats (16-byte aligned rows): a block moves a 64 (along a) x 64 (along b) tile.
+// Thread (ag, b4) reads four float4 - rows a = 4*ag .. 4*ag+3 at columns 4*b4 .. 4*b4+3, 256
+// contiguous bytes per 16 threads - transposes its 4x4 block in registers, and leaves four float4
+// (row b = 4*b4+j, columns a = 4*ag .. +3) in shared memory; after the barrier the threads read the
+// tile row by row and write 256 contiguous bytes per 16 threads.  The shared tile is [64][16] float4
+// with the column XOR-ed by (b >> 2) & 7, so the eight lanes that the hardware serves together hit
+// eight different 16-byte bank groups in both phases: no padding, no conflicts.  Batch indices are
+// decoded once per block with multiply-high divisions.
+struct Tile4Geom {
+  int A4, B4;                    // extents of a and b in float4
+  int64_t a_in_step4, b_out_step4;   // step of a in x and of b in y, in float4
+  FastDiv32 div_tiles_b, div_tiles_a;
+  int nbatch;
+  FastDiv32 div_batch[kMaxDims];
+  int64_t batch_in_step4[kMaxDims], batch_out_step4[kMaxDims];
+};
+
+__global__ void __launch_bounds__(256)
+permute_tile4_kernel(const float4* __restrict__ x, float4* y, const __grid_constant__ Tile4Geom g) {
+  __shared__ float4 tile[64][16];
+  uint32_t rest = blockIdx.x, tb, ta;
+  g.div_tiles_b.divmod(rest, rest, tb);
+  g.div_tiles_a.divmod(rest, rest, ta);
+  int64_t in_base = 0, out_base = 0;
+  for (int d = g.nbatch - 1; d >= 0; --d) {
+    uint32_t idx;
+    g.div_batch[d].divmod(rest, rest, idx);
+    in_base += idx * g.batch_in_step4[d], out_base += idx * g.batch_out_step4[d];
+  }
+  {
+    const int b4l = threadIdx.x & 15, agl = threadIdx.x >> 4;   // position inside the tile
+    const int b4 = static_cast<int>(tb) * 16 + b4l, ag = static_cast<int>(ta) * 16 + agl;
+    if (b4 < g.B4 && ag < g.A4) {
+      const float4* src = x + in_base + static_cast<int64_t>(4 * ag) * g.a_in_step4 + b4;
+      const float4 r0 = ld_stream(src), r1 = ld_stream(src + g.a_in_step4), r2 = ld_stream(src + 2 * g.a_in_step4),
+                   r3 = ld_stream(src + 3 * g.a_in_step4);
+      const int col = agl ^ (b4l & 7);
+      tile[4 * b4l + 0][col] = make_float4(r0.x, r1.x, r2.x, r3.x);
+      tile[4 * b4l + 1][col] = make_float4(r0.y, r1.y, r2.y, r3.y);
+      tile[4 * b4l + 2][col] = make_float4(r0.z, r1.z, r2.z, r3.z);
+      tile[4 * b4l + 3][col] = make_float4(r0.w, r1.w, r2.w, r3.w);
+    }
+  }
+  __syncthreads();
+  const int agl = threadIdx.x & 15, ag = static_cast<int>(ta) * 16 + agl;
+  if (ag >= g.A4) return;
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int bl = (threadIdx.x >> 4) + 16 * k;
+    const int b = static_cast<int>(tb) * 64 + bl;
+    if (b < 4 * g.B4) st_stream(y + out_base + static_cast<int64_t>(b) * g.b_out_step4 + ag, tile[bl][agl ^ ((bl >> 2) & 7)]);
+  }
+}
+
 // ---- Gather, Pad --------------------------------------------------------------------------------
 __global__ void __launch_bounds__(kThreads)
 gather_kernel(const float* __restrict__ x, const int* __restrict__ indexes, float* y, int64_t count, int64_t num_indexes,
@@ -244,6 +300,38 @@ pad_kernel(const float* __restrict__ x, float* y, int64_t rows, int in_h, int in
     float v = value;
     if (row_inside && w >= 0 && w < in_w) v = ld_stream(xr + w);
     st_stream(yr + ow, v);
+  }
+}
+
+// The same operator with 128-bit stores: the output is one flat run of floats, a thread writes one
+// aligned float4 of it and finds the (plane, row, column) of its first element with two
+// multiply-high divisions; the following three elements are reached by incrementing.  The sources
+// are read as floats (a padded row starts at an arbitrary 4-byte offset of its source row), through
+// the L1: the four loads of a warp cover the same sectors.
+__global__ void __launch_bounds__(kThreads)
+pad_vec_kernel(const float* __restrict__ x, float* y, int64_t total, int in_h, int in_w, int out_h, int out_w, int top,
+               int left, float value, FastDiv32 div_out_w, FastDiv32 div_out_h) {
+  const int64_t i4 = static_cast<int64_t>(blockIdx.x) * kThreads + threadIdx.x;
+  const int64_t flat = 4 * i4;
+  if (flat >= total) return;
+  uint32_t row, ow, plane, oh;
+  div_out_w.divmod(static_cast<uint32_t>(flat), row, ow);
+  div_out_h.divmod(row, plane, oh);
+  float v[4];
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int h = static_cast<int>(oh) - top, w = static_cast<int>(ow) - left;
+    const bool inside = h >= 0 && h < in_h && w >= 0 && w < in_w && flat + k < total;
+    v[k] = inside ? __ldg(x + (static_cast<int64_t>(plane) * in_h + h) * in_w + w) : value;
+    if (++ow == static_cast<uint32_t>(out_w)) {
+      ow = 0;
+      if (++oh == static_cast<uint32_t>(out_h)) oh = 0, ++plane;
+    }
+  }
+  if (flat + 4 <= total) {
+    st_stream(reinterpret_cast<float4*>(y) + i4, make_float4(v[0], v[1], v[2], v[3]));
+  } else {
+    for (int k = 0; flat + k < total; ++k) y[flat + k] = v[k];
   }
 }
 
@@ -321,6 +409,33 @@ int sb200_permute(const float* x, float* y, const int* in_shape, const int* orde
     for (int j = 0; j < nd - 1; ++j)
       if (src_step[j] == 1) jb = j;
     if (jb >= 0) {
+      // 128-bit variant when every extent and step involved is a multiple of 4 floats
+      bool vec = aligned16(x) && aligned16(y) && ext[nd - 1] % 4 == 0 && ext[jb] % 4 == 0 && src_step[nd - 1] % 4 == 0 &&
+                 out_step[jb] % 4 == 0 && ext[nd - 1] / 4 < (1ll << 30) && ext[jb] / 4 < (1ll << 30);
+      for (int j = 0; j < nd - 1 && vec; ++j)
+        if (j != jb) vec = src_step[j] % 4 == 0 && out_step[j] % 4 == 0 && ext[j] < (1ll << 31);
+      if (vec) {
+        Tile4Geom g;
+        g.A4 = static_cast<int>(ext[nd - 1] / 4), g.B4 = static_cast<int>(ext[jb] / 4);
+        g.a_in_step4 = src_step[nd - 1] / 4, g.b_out_step4 = out_step[jb] / 4;
+        const int64_t tiles_a = (g.A4 + 15) / 16, tiles_b = (g.B4 + 15) / 16;
+        g.div_tiles_a = FastDiv32(static_cast<uint32_t>(tiles_a)), g.div_tiles_b = FastDiv32(static_cast<uint32_t>(tiles_b));
+        g.nbatch = 0;
+        int64_t blocks = tiles_a * tiles_b;
+        for (int j = 0; j < nd - 1; ++j) {
+          if (j == jb) continue;
+          g.div_batch[g.nbatch] = FastDiv32(static_cast<uint32_t>(ext[j]));
+          g.batch_in_step4[g.nbatch] = src_step[j] / 4, g.batch_out_step4[g.nbatch] = out_step[j] / 4;
+          ++g.nbatch;
+          blocks *= ext[j];
+        }
+        for (int d = g.nbatch; d < kMaxDims; ++d) g.div_batch[d] = FastDiv32(1), g.batch_in_step4[d] = 0, g.batch_out_step4[d] = 0;
+        if (blocks < (1ll << 31)) {
+          permute_tile4_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(reinterpret_cast<const float4*>(x),
+                                                                             reinterpret_cast<float4*>(y), g);
+          return after_launch("sb200_permute");
+        }
+      }
       TileGeom g;
       g.A = ext[nd - 1], g.Bn = ext[jb];
       g.a_in_step = src_step[nd - 1], g.b_out_step = out_step[jb];
@@ -381,6 +496,14 @@ int sb200_pad(const float* x, float* y, int64_t planes, int in_h, int in_w, cons
   if (x == nullptr || y == nullptr || x == y) return SB200_ERR_BAD_ARGUMENT;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 3u) return SB200_ERR_BAD_ARGUMENT;
   if (planes > (1ll << 40) / (out_h * out_w)) return SB200_ERR_UNSUPPORTED;
+  const int64_t total = planes * out_h * out_w;
+  if (aligned16(y) && total < (1ll << 32)) {
+    const int64_t blocks4 = ((total + 3) / 4 + kThreads - 1) / kThreads;
+    pad_vec_kernel<<<static_cast<unsigned>(blocks4), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        x, y, total, in_h, in_w, static_cast<int>(out_h), static_cast<int>(out_w), paddings[0], paddings[2], value,
+        FastDiv32(static_cast<uint32_t>(out_w)), FastDiv32(static_cast<uint32_t>(out_h)));
+    return after_launch("sb200_pad");
+  }
   const int64_t rows = planes * out_h;
   const int runs_per_row = static_cast<int>((out_w + kPadRun - 1) / kPadRun);
   const int64_t threads = rows * runs_per_row;

@@ -188,8 +188,14 @@ normalize_colvec_kernel(const float* x, float* y, const __grid_constant__ ColWal
     }
     if (SCALE == kScaleChannel) {
       const int base = k * q.rows_per_step;
+      if (q.tiled) {   // the four lanes of a tiled layout sit in one row: one scale for the float4
+        const float sc = __ldg(ssd.scale + row[0] + base);
 #pragma unroll
-      for (int e = 0; e < 4; ++e) o[e] = __fmul_rn(o[e], __ldg(ssd.scale + row[e] + base));
+        for (int e = 0; e < 4; ++e) o[e] = __fmul_rn(o[e], sc);
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[e] = __fmul_rn(o[e], __ldg(ssd.scale + row[e] + base));
+      }
     }
     return make_float4(o[0], o[1], o[2], o[3]);
   };

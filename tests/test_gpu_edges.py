@@ -222,3 +222,57 @@ def test_every_permutation_of_small_tensors():
             got = F.permute(dx, list(order)).cpu().numpy()
             assert got.shape == tuple(shape[a] for a in order)
             assert orc.bit_equal(got, np.ascontiguousarray(x.transpose(order))), (shape, order)
+
+
+@pytest.mark.parametrize("rows,inner,group_affine", [
+    (400, 8448, True),      # 33 KB rows, more rows than blocks: the double-buffered loop runs several rounds
+    (300, 8196, False),     # the same kernel just above the row-in-registers limit
+    (5, 30000, True),       # 120 KB rows: one buffer
+    (3, 57344, False),      # the longest row that fits shared memory
+    (2, 60000, True),       # longer: block-per-row kernel re-reading from L2
+    (150, 8450, False),     # not a multiple of 4 floats: scalar long-row kernel
+])
+def test_long_row_normalisation(rows, inner, group_affine):
+    """GroupNorm / LayerNorm on rows that do not fit the registers of a block."""
+    from shadow_b200 import functional as F
+    torch = _torch()
+    spatial = inner // 2 if inner % 2 == 0 else inner
+    channels = inner // spatial
+    x = cases.normal(7000 + rows, (rows, channels, spatial), 0.5, 2.0)
+    if group_affine:
+        sc, bs = cases.normal(7001, (channels,), 1.0, 0.3), cases.normal(7002, (channels,))
+        got = F.group_norm(torch.from_numpy(x).cuda(), 1, torch.from_numpy(sc).cuda(), torch.from_numpy(bs).cuda(), 1e-5)
+        case = {"name": "long_rows", "op": "GroupNorm", "args": {"group": 1, "eps": 1e-5}, "inputs": [x, sc, bs]}
+    else:
+        flat = x.reshape(rows, inner)
+        got = F.layer_norm(torch.from_numpy(flat).cuda(), [inner], None, None, 1e-5)
+        case = {"name": "long_rows", "op": "LayerNorm", "args": {"normalized_shape": [inner], "eps": 1e-5}, "inputs": [flat]}
+    torch.cuda.synchronize()
+    want = cases.run_port(case)
+    cases.assert_parity(case, got.cpu().numpy().reshape(want.shape), want)
+
+
+def test_permute_vector_tiles_with_ragged_edges():
+    """The 128-bit tile transpose on extents that are multiples of 4 but not of the 64-wide tile, and
+    the scalar tile kernel right beside it (extents not multiples of 4)."""
+    from shadow_b200 import functional as F
+    torch = _torch()
+    for shape, order in (((3, 68, 100), (0, 2, 1)), ((2, 4, 260), (2, 0, 1)), ((5, 132, 12, 8), (0, 2, 3, 1)),
+                         ((3, 66, 100), (0, 2, 1)), ((2, 8, 6, 36), (1, 3, 0, 2)), ((7, 64, 64), (0, 2, 1))):
+        x = cases.normal(7100 + len(shape) + shape[1], shape)
+        got = F.permute(torch.from_numpy(x).cuda(), list(order))
+        torch.cuda.synchronize()
+        assert orc.bit_equal(got.cpu().numpy(), np.ascontiguousarray(np.transpose(x, order))), (shape, order)
+
+
+def test_pad_vector_stores_cross_row_boundaries():
+    """Output rows of 58, 7 and 3 floats: most float4 of the flat output straddle two rows (or three)."""
+    from shadow_b200 import functional as F
+    torch = _torch()
+    for shape, pads, value in (((3, 5, 56, 56), (1, 1, 1, 1), 0.0), ((2, 3, 4, 5), (2, 0, 1, 1), -7.5),
+                               ((4, 1, 6, 1), (0, 3, 1, 1), 2.0), ((2, 2, 9, 9), (-2, -1, -3, 0), 0.0), ((1, 1, 1, 1), (0, 0, 0, 0), 1.0)):
+        x = cases.normal(7200 + shape[2], shape)
+        got = F.pad(torch.from_numpy(x).cuda(), list(pads), value)
+        torch.cuda.synchronize()
+        want = orc.pad(x, list(pads), value)
+        assert orc.bit_equal(got.cpu().numpy(), want), (shape, pads)
