@@ -36,32 +36,35 @@ __device__ __align__(128) const unsigned long long kExp2fTable[32] = {
 // expf as glibc computes it (sysdeps/ieee754/flt-32/e_expf.c, the algorithm of Arm's optimized
 // routines): in double, x*32/ln2 = k + r with k an integer (found by adding 1.5*2^52), e^x =
 // 2^(k/32) * 2^(r/32) with 2^(k/32) from a 32-entry table and its exponent field, 2^(r/32) by a cubic;
-// the double result is rounded once to float.  The fused steps are the ones glibc's build for
-// processors with FMA contracts; with them the result equals glibc 2.39's expf on all 2^32 inputs
-// (checked on the host), and a build without FMA differs on two inputs by one ulp.
+// the double result is rounded once to float.  The fused steps (the rounding step k, the residual r and
+// the polynomial) are the ones glibc's build for processors with FMA contracts; with them the result
+// equals glibc 2.39's expf on all 2^32 inputs (checked on the host), and a build without FMA differs
+// on two inputs by one ulp.
 __device__ __forceinline__ float expf_like_glibc(float x) {
   constexpr double kInvLn2N = 0x1.71547652b82fep+0 * 32.0;
   constexpr double kShift = 0x1.8p+52;
   constexpr double kC0 = 0x1.c6af84b912394p-5 / 32.0 / 32.0 / 32.0, kC1 = 0x1.ebfce50fac4f3p-3 / 32.0 / 32.0,
                    kC2 = 0x1.62e42ff0c52d6p-1 / 32.0;
-  // beyond these the float result is inf / 0 (also for the infinities); a NaN fails both tests
-  // and comes out of the arithmetic as a NaN
-  const float xc = fminf(fmaxf(x, -104.5f), 89.f);
+  // Beyond these bounds the float result is inf / 0 (also for the infinities).  The clamps are the
+  // NaN-propagating forms, so a NaN runs through the arithmetic and comes out as a NaN by itself.
+  float xc;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(xc) : "f"(x), "f"(-104.5f));
+  asm("min.NaN.f32 %0, %1, %2;" : "=f"(xc) : "f"(xc), "f"(89.f));
   const double xd = static_cast<double>(xc);
-  const double z = __dmul_rn(kInvLn2N, xd);
-  double kd = __dadd_rn(z, kShift);
-  const unsigned long long ki = static_cast<unsigned long long>(__double_as_longlong(kd));
+  double kd = fma(kInvLn2N, xd, kShift);              // k = round(x*32/ln2) sits in the low word
+  const int ki = __double2loint(kd);
   kd = __dsub_rn(kd, kShift);
   const double r = fma(kInvLn2N, xd, -kd);
-  const unsigned long long t = __ldg(&kExp2fTable[ki & 31]) + (ki << 47);
-  const double s = __longlong_as_double(static_cast<long long>(t));
+  // 2^(k/32): the table entry with k>>5 added to its exponent field (k << 47 in the 64-bit pattern,
+  // which touches the high word only)
+  const double tab = __longlong_as_double(static_cast<long long>(__ldg(&kExp2fTable[ki & 31])));
+  const double s = __hiloint2double(__double2hiint(tab) + static_cast<int>(static_cast<unsigned>(ki) << 15), __double2loint(tab));
   const double q = fma(kC0, r, kC1);
   const double r2 = __dmul_rn(r, r);
   double y = fma(kC2, r, 1.0);
   y = fma(q, r2, y);
   y = __dmul_rn(y, s);
-  const float f = static_cast<float>(y);
-  return (x == x) ? f : x;
+  return static_cast<float>(y);
 }
 
 // 2^(j/16), j = 0..15: one 128-byte line, so a warp's 32 lookups are a single L1 transaction.
@@ -108,15 +111,17 @@ __device__ __forceinline__ double rcp_newton(double d) {
   return fma(r0, fma(-d, r0, 1.0), r0);
 }
 
-// Correctly rounded 1/y for a float y >= 1 (or +inf): hardware seed (within 1 ulp) and one fma
-// correction, r1 = r0 + r0*(1 - y*r0).  Bit-identical to __frcp_rn on this domain (checked through
-// Sigmoid over all 2^32 inputs) at a fraction of its cost.  y = inf gives r0 = 0 and a NaN residual.
+// Correctly rounded 1/y for a float y >= 1 (or +inf, or NaN): hardware seed (within 1 ulp) and one
+// fma correction, r1 = r0 + r0*(1 - y*r0).  Bit-identical to __frcp_rn on this domain (checked through
+// Sigmoid over all 2^32 inputs) at a fraction of its cost.  The flush-to-zero seed has no denormal
+// handling code around it; the few arguments whose reciprocal is denormal (y > 2^125, infinity
+// included) take the IEEE instruction.  A NaN runs through the arithmetic.
 __device__ __forceinline__ float rcp_correct(float y) {
+  if (y > 0x1p125f) return __frcp_rn(y);
   float r0;
-  asm("rcp.approx.f32 %0, %1;" : "=f"(r0) : "f"(y));
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0) : "f"(y));
   const float e = fmaf(-y, r0, 1.0f);
-  const float r1 = fmaf(r0, e, r0);
-  return (e == e) ? r1 : r0;
+  return fmaf(r0, e, r0);
 }
 
 // tanh(x) = 1 - 2/(e^{2|x|} + 1) in double, rounded once; for |x| < 2^-12 the float result is x

@@ -272,7 +272,18 @@ rownorm_smem_rows_kernel(const float* x, float* y, int64_t rows, int units, floa
       const float4 q = buf[u];
       float o[4] = {div_exact(__fsub_rn(q.x, mean), d, rcp, d_ok), div_exact(__fsub_rn(q.y, mean), d, rcp, d_ok),
                     div_exact(__fsub_rn(q.z, mean), d, rcp, d_ok), div_exact(__fsub_rn(q.w, mean), d, rcp, d_ok)};
-      if (aff.mode != kAffineNone) {
+      if (aff.mode == kAffineChannel) {
+        // long rows: the four lanes of a float4 almost always share a channel - one index, one scale, one bias
+        const uint32_t k0 = affine_index(aff, base, static_cast<uint32_t>(4 * u)), k3 = affine_index(aff, base, static_cast<uint32_t>(4 * u + 3));
+        if (k0 == k3) {
+          const float sc = __ldg(aff.scale + k0), bs = __ldg(aff.bias + k0);
+#pragma unroll
+          for (int e = 0; e < 4; ++e) o[e] = __fadd_rn(__fmul_rn(o[e], sc), bs);
+        } else {
+#pragma unroll
+          for (int e = 0; e < 4; ++e) o[e] = affine_apply(aff, o[e], affine_index(aff, base, static_cast<uint32_t>(4 * u + e)));
+        }
+      } else if (aff.mode != kAffineNone) {
 #pragma unroll
         for (int e = 0; e < 4; ++e) o[e] = affine_apply(aff, o[e], affine_index(aff, base, static_cast<uint32_t>(4 * u + e)));
       }

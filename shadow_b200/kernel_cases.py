@@ -99,8 +99,15 @@ def _cases(torch, F):
     case("reduce_sum_spatial", "redA_rows_kernel", reduce(1, (2, 3), 256 * 512))
     case("reduce_max_spatial", "redA_rows_kernel", reduce(2, (2, 3), 256 * 512))
     case("reduce_prod_spatial", "redA_rows_kernel", reduce(0, (2, 3), 256 * 512, 0.99))
-    case("reduce_sum_channel", "redC_kernel", reduce(1, (1,), 256 * 196))
-    case("reduce_max_channel", "redC_kernel", reduce(2, (1,), 256 * 196))
+    def reduce_channel(code):
+        def make():
+            x = normal((512, 512, 14, 14))          # enough planes for the fixed-column walk
+            r = torch.empty(512 * 196, device=dev)
+            return (lambda: F.reduce(x, code, (1,), out=r)), 4 * (x.numel() + 512 * 196)
+        return make
+
+    case("reduce_sum_channel", "redC_kernel", reduce_channel(1))
+    case("reduce_max_channel", "redC_kernel", reduce_channel(2))
     case("reduce_sum_batch_spatial", "redB_kernel", reduce(1, (0, 2, 3), 512))
     case("reduce_sum_all", "redA_block_kernel", reduce(1, (), 1))
 
@@ -112,14 +119,14 @@ def _cases(torch, F):
         return make
 
     case("softmax_rows", "softmax_rows_kernel", softmax((6144, 4096), 3.0, -1))
-    case("softmax_strided_c4b", "softmax_col", softmax((512, 1000, 7, 7), 1.0, 1))
-    case("softmax_strided_wide", "softmax_col", softmax((5, 21, 512, 512), 1.0, 1))
+    case("softmax_strided_c4b", "softmax_colvec_kernel", softmax((512, 1000, 7, 7), 1.0, 1))
+    case("softmax_strided_wide", "softmax_colreg_kernel", softmax((5, 21, 512, 512), 1.0, 1))
 
     def normalize():
         x = normal((32, 512, 38, 38))
         y = torch.empty_like(x)
         return (lambda: F.normalize(x, 1, 2.0, 1e-12, out=y)), 8 * x.numel()
-    case("normalize_l2_channel", "normalize_col", normalize)
+    case("normalize_l2_channel", "normalize_colvec_kernel", normalize)
 
     def layer_norm():
         x = normal((32768, 768))
@@ -127,6 +134,25 @@ def _cases(torch, F):
         y = torch.empty_like(x)
         return (lambda: F.layer_norm(x, [768], g, bt, 1e-5, out=y)), 8 * x.numel()
     case("layer_norm_rows", "rownorm_rows_kernel", layer_norm)
+
+    def group_norm():
+        x = normal((128, 64, 56, 56))
+        g, bt = normal((64,)), normal((64,))
+        y = torch.empty_like(x)
+        return (lambda: F.group_norm(x, 8, g, bt, 1e-5, out=y)), 8 * x.numel()
+    case("group_norm_100kb_rows", "rownorm_smem_rows_kernel", group_norm)
+
+    def permute():
+        x = normal((32, 256, 56, 56))
+        y = torch.empty((32, 56, 56, 256), device=dev)
+        return (lambda: F.permute(x, [0, 2, 3, 1], out=y)), 8 * x.numel()
+    case("permute_nchw_nhwc", "permute_tile4_kernel", permute)
+
+    def pad():
+        x = normal((64, 160, 56, 56))
+        y = torch.empty((64, 160, 58, 58), device=dev)
+        return (lambda: F.pad(x, [1, 1, 1, 1], 0.0, out=y)), 4 * (x.numel() + y.numel())
+    case("pad_border_1", "pad_vec_kernel", pad)
     return table
 
 
