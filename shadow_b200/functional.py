@@ -115,17 +115,28 @@ def scale(x: torch.Tensor, axis: int = 1, scale: Optional[torch.Tensor] = None,
 
 
 class ReduceScratch:
-    """Grow-only device scratch, the analogue of Workspace::GrowTempBuffer for Python callers."""
+    """Grow-only device scratch, the analogue of Workspace::GrowTempBuffer for Python callers: one
+    buffer per (device, stream), because kernels of two streams may run at the same time and a
+    reduction's partials must not be shared between them.  A buffer that is outgrown is handed back
+    to torch's allocator only after the stream that used it has been told so (record_stream), so its
+    memory cannot be reused while a kernel of that stream may still write it.  A CUDA graph captures the
+    buffer's address: do not outgrow the buffer of a stream between capture and replay."""
 
     def __init__(self):
-        self.buf: Optional[torch.Tensor] = None
+        self.bufs = {}
 
     def get(self, nbytes: int, device) -> int:
         if nbytes <= 0:
             return 0
-        if self.buf is None or self.buf.numel() < nbytes or self.buf.device != device:
-            self.buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
-        return self.buf.data_ptr()
+        stream = torch.cuda.current_stream(device)
+        key = (torch.device(device).index, stream.cuda_stream)
+        buf = self.bufs.get(key)
+        if buf is None or buf.numel() < nbytes:
+            if buf is not None:
+                buf.record_stream(stream)
+            buf = torch.empty(nbytes, dtype=torch.uint8, device=device)
+            self.bufs[key] = buf
+        return buf.data_ptr()
 
 
 _scratch = ReduceScratch()
