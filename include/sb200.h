@@ -280,6 +280,11 @@ int sb200_axpy(const float* alpha, const float* x, const float* y, float* out, i
  * (shadow/operators/kernels/softmax.hpp:10-12, softmax.cu:9-70); the reference's `val` scratch of
  * outer*inner floats and its four launches are not needed. */
 int sb200_softmax(const float* x, float* y, int64_t outer, int64_t dim, int64_t inner, void* stream);
+/* How many blocks of the resident-plane Softmax kernel (planes of about 100..200 KB kept in shared memory
+ * and filled by bulk asynchronous copies) have ever given up a bounded wait for their own copies on the
+ * current device: 0 on a healthy run; -1 if the counter cannot be read.  Synchronises the device.  A
+ * diagnostic of this implementation; no counterpart in the reference. */
+long long sb200_softmax_ring_timeouts(void);
 
 #ifdef __cplusplus
 }

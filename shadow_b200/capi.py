@@ -56,6 +56,7 @@ def lib() -> C.CDLL:
             "sb200_reduce_finalize": (i32, [vp, vp, i64, i32, i64, vp]),
             "sb200_reduce_combine": (i32, [vp, i64, i64, vp, i64, i32, i64, vp]),
             "sb200_softmax": (i32, [vp, vp, i64, i64, i64, vp]),
+            "sb200_softmax_ring_timeouts": (C.c_longlong, []),
             "sb200_eltwise": (i32, [C.POINTER(vp), i32, C.POINTER(f32), vp, i64, i32, vp]),
             "sb200_axpy": (i32, [vp, vp, vp, vp, i64, i64, vp]),
             "sb200_batch_norm": (i32, [vp, vp, i64, vp, vp, i64, i64, f32, f32, vp]),
@@ -79,7 +80,7 @@ def lib() -> C.CDLL:
 EXPORTED = ["sb200_status_string", "sb200_last_cuda_error", "sb200_device_sm_count", "sb200_launch_count",
             "sb200_fill", "sb200_unary", "sb200_activate", "sb200_prelu", "sb200_binary_scalar",
             "sb200_binary", "sb200_binary_broadcast", "sb200_scale_bias", "sb200_reduce_scratch_bytes",
-            "sb200_reduce", "sb200_reduce_static", "sb200_reduce_partial", "sb200_reduce_finalize", "sb200_reduce_combine", "sb200_softmax", "sb200_eltwise", "sb200_axpy", "sb200_batch_norm", "sb200_normalize", "sb200_ssd_normalize", "sb200_row_norm",
+            "sb200_reduce", "sb200_reduce_static", "sb200_reduce_partial", "sb200_reduce_finalize", "sb200_reduce_combine", "sb200_softmax", "sb200_softmax_ring_timeouts", "sb200_eltwise", "sb200_axpy", "sb200_batch_norm", "sb200_normalize", "sb200_ssd_normalize", "sb200_row_norm",
             "sb200_concat", "sb200_slice", "sb200_permute", "sb200_gather", "sb200_pad", "sb200_pooling"]
 
 

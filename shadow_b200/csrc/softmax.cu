@@ -462,6 +462,210 @@ softmax_colreg_kernel(const float* x, float* y, const __grid_constant__ ColWalk 
   }
 }
 
+// ---- strided softmax with the plane resident in shared memory, planes pipelined through it -------
+// For planes of about 100..200 KB (too long a column for a block's registers, e.g. [1000,7,7]): ONE
+// persistent block per SM keeps the whole plane in shared memory, cut into chunks of 5 * tact float4
+// (tact = k periods of the fixed-column walk, so thread t owns float4 t, t + tact, ... of every chunk
+// and its four lanes stay on four columns).  The chunks are brought in by bulk asynchronous copies
+// (cp.async.bulk global -> shared, completion counted on one mbarrier per chunk; no multicast, no
+// registers involved), so the tensor is read from DRAM once and never re-read through the L2:
+//   pass 1 takes the chunks in order as they land (running sums against integer references,
+//          lanes_take), the column references and sums meet through shared memory;
+//   pass 2 reads chunk c from shared memory, writes its outputs with 128-bit stores and, after a
+//          block barrier, hands the chunk's memory to the copy of chunk c of the block's NEXT plane:
+//          the next plane streams in while this one streams out, and its pass 1 finds all but the
+//          last chunks already there.
+// Every wait on an mbarrier is bounded: a wait that runs out (it never should: the copies were
+// issued by this block) raises a flag that sb200_softmax_ring_timeouts() reports, and the block
+// stops after giving its outstanding copies one more bounded wait.
+__device__ unsigned int g_ring_timeouts = 0;
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait: false when the phase did not complete within about half a second (2^30 SM clocks).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
+  if (mbar_try_wait(bar, parity)) return true;
+  const long long start = clock64();
+  while (!mbar_try_wait(bar, parity))
+    if (clock64() - start > (1ll << 30)) return false;
+  return true;
+}
+__device__ __forceinline__ void bulk_copy_g2s(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(src), "r"(bytes), "r"(bar) : "memory");
+}
+
+constexpr int kRingM = 5;   // float4 per thread and chunk
+
+struct RingGeo {
+  int64_t outer, plane4;   // planes; float4 per plane
+  int tact;                // working threads; a chunk holds kRingM * tact float4 (thread t owns float4 t, t + tact, ...)
+  int chunks;              // chunks per plane (the last one may be partial)
+  int R, ncols;            // partial rows per column held by the block (k * rows per period); columns (inner)
+  FastDiv32 div_inner;
+  ColWalk merge;           // what colwalk_merge needs: one plane, R partial rows of ncols columns
+};
+
+template <int T>
+__global__ void __launch_bounds__(T, 1)
+softmax_ring_kernel(const float* x, float* y, const __grid_constant__ RingGeo g) {
+  extern __shared__ float4 sm_dyn[];
+  float4* ring = sm_dyn;                                                    // [chunks][kRingM * tact]
+  float* sm_c = reinterpret_cast<float*>(ring + static_cast<size_t>(g.chunks) * kRingM * g.tact);   // [4 * tact]
+  float* sm_l = sm_c + 4 * g.tact;                                          // [4 * tact]
+  uint64_t* bars = reinterpret_cast<uint64_t*>(sm_l + 4 * g.tact);          // [chunks]
+  __shared__ int give_up;
+  const int t = threadIdx.x;
+  const uint32_t ring_addr = static_cast<uint32_t>(__cvta_generic_to_shared(ring));
+  const uint32_t bar_addr = static_cast<uint32_t>(__cvta_generic_to_shared(bars));
+  const int chunk4 = kRingM * g.tact;
+  const uint32_t chunk_bytes = static_cast<uint32_t>(chunk4) * 16u;
+  auto bytes_of = [&](int c) {   // the last chunk of a plane may be short
+    const int64_t left = g.plane4 - static_cast<int64_t>(c) * chunk4;
+    return left >= chunk4 ? chunk_bytes : static_cast<uint32_t>(left) * 16u;
+  };
+  auto fetch = [&](int64_t plane, int c) {   // one thread: announce the bytes, start the copy
+    const uint32_t bar = bar_addr + 8u * static_cast<uint32_t>(c), bytes = bytes_of(c);
+    mbar_expect_tx(bar, bytes);
+    bulk_copy_g2s(ring_addr + static_cast<uint32_t>(c) * chunk_bytes,
+                  reinterpret_cast<const float4*>(x) + plane * g.plane4 + static_cast<int64_t>(c) * chunk4, bytes, bar);
+  };
+  if (t == 0) {
+    give_up = 0;
+    for (int c = 0; c < g.chunks; ++c) mbar_init(bar_addr + 8u * static_cast<uint32_t>(c), 1);
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncthreads();
+  if (t == 0 && blockIdx.x < g.outer)
+    for (int c = 0; c < g.chunks; ++c) fetch(blockIdx.x, c);
+  // this thread's place in the column bookkeeping (flat layout, one plane per block)
+  const bool worker = t < g.tact;
+  uint32_t row_unused, rem0;
+  g.div_inner.divmod(static_cast<uint32_t>(4 * (worker ? t : 0)), row_unused, rem0);
+  int col[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    col[e] = static_cast<int>(rem0) + e;
+    if (col[e] >= g.ncols) col[e] -= g.ncols;
+  }
+  const ColWalk& q = g.merge;
+  uint32_t parity = 0;
+  bool failed = false;
+  for (int64_t plane = blockIdx.x; plane < g.outer; plane += gridDim.x, parity ^= 1u) {
+    // ---- pass 1: chunks in order, as they land
+    LaneSum s[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) s[e].init();
+    for (int c = 0; c < g.chunks && !failed; ++c) {
+      if (!mbar_wait(bar_addr + 8u * static_cast<uint32_t>(c), parity)) { failed = true; break; }
+      float4 v[kRingM];
+#pragma unroll
+      for (int u = 0; u < kRingM; ++u) {
+        const int j = u * g.tact + t;   // float4 inside the chunk
+        v[u] = (worker && static_cast<int64_t>(c) * chunk4 + j < g.plane4)
+                   ? ring[static_cast<size_t>(c) * chunk4 + j]
+                   : make_float4(-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F);   // absent: 2^x of -inf is 0
+      }
+      if (worker) lanes_take<kRingM>(s, v);
+    }
+    if (failed) give_up = 1;   // (every thread that saw it writes the same value)
+    __syncthreads();
+    if (give_up) break;
+    // ---- column references and sums through shared memory (as in softmax_colvec_kernel)
+    if (worker) *reinterpret_cast<float4*>(sm_c + 4 * t) = make_float4(s[0].c, s[1].c, s[2].c, s[3].c);
+    __syncthreads();
+    colwalk_merge(q, sm_c, OpMaxF(), -3.0e38f);
+    __syncthreads();
+    float cref[4];
+    if (worker) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        cref[e] = sm_c[col[e]];
+        sm_l[4 * t + e] = __fmul_rn(s[e].l, pow2_int(__fsub_rn(s[e].c, cref[e])));
+      }
+    }
+    __syncthreads();
+    colwalk_merge(q, sm_l, OpAddF(), 0.f);
+    __syncthreads();
+    float inv[4], k[4];
+    if (worker) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        inv[e] = __fmul_rn(__frcp_rn(sm_l[col[e]]), 0x1p-24f);   // takes the numerators' bias back
+        k[e] = __fsub_rn(kNumeratorBias, cref[e]);
+      }
+    }
+    // ---- pass 2: out of shared memory; each chunk's memory goes to the next plane as soon as it is done
+    const int64_t next = plane + gridDim.x;
+    float4* yp = reinterpret_cast<float4*>(y) + plane * g.plane4;
+    for (int c = 0; c < g.chunks; ++c) {
+      if (worker) {
+        float4 v[kRingM];
+#pragma unroll
+        for (int u = 0; u < kRingM; ++u) v[u] = ring[static_cast<size_t>(c) * chunk4 + u * g.tact + t];   // (stale bytes past the plane's end are not stored)
+#pragma unroll
+        for (int u = 0; u < kRingM; ++u) {
+          const int64_t i4 = static_cast<int64_t>(c) * chunk4 + u * g.tact + t;
+          if (i4 < g.plane4)
+            st_stream(yp + i4, make_float4(__fmul_rn(ex2_ftz(__fmaf_rn(v[u].x, kLog2eF, k[0])), inv[0]), __fmul_rn(ex2_ftz(__fmaf_rn(v[u].y, kLog2eF, k[1])), inv[1]),
+                                           __fmul_rn(ex2_ftz(__fmaf_rn(v[u].z, kLog2eF, k[2])), inv[2]), __fmul_rn(ex2_ftz(__fmaf_rn(v[u].w, kLog2eF, k[3])), inv[3])));
+        }
+      }
+      if (next < g.outer) {
+        __syncthreads();   // every thread has read chunk c
+        if (t == 0) {
+          asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // order the reads before the copy that overwrites them
+          fetch(next, c);
+        }
+      }
+    }
+  }
+  if (give_up) {
+    // copies of this block may still be in flight: give each one more bounded wait, then report
+    if (t == 0) {
+      for (int c = 0; c < g.chunks; ++c) mbar_wait(bar_addr + 8u * static_cast<uint32_t>(c), parity);
+      atomicAdd(&g_ring_timeouts, 1u);
+    }
+  }
+}
+
+// Plans the resident-plane kernel; false when it does not apply.
+bool plan_ring(const void* x, const void* y, int64_t outer, int64_t dim, int64_t inner, RingGeo* g, size_t* smem) {
+  if (!aligned16(x) || !aligned16(y) || (dim * inner) % 4 != 0 || inner < 2) return false;
+  const int64_t plane4 = dim * inner / 4;
+  const int64_t g4 = (inner % 4 == 0) ? 4 : ((inner % 2 == 0) ? 2 : 1);
+  const int64_t p = inner / g4;
+  const int rp = static_cast<int>(4 / g4);
+  if (p > 512 || plane4 * 16 < 96 * 1024 || outer < 2ll * sm_count()) return false;
+  const int64_t k = 512 / p;
+  const int64_t tact = k * p;
+  const int64_t chunks = (plane4 + kRingM * tact - 1) / (kRingM * tact);
+  const size_t bytes = static_cast<size_t>(chunks) * kRingM * tact * 16 + 2 * 4 * tact * sizeof(float) + static_cast<size_t>(chunks) * 8;
+  if (bytes > 226 * 1024 || chunks > 4096) return false;
+  g->outer = outer, g->plane4 = plane4, g->tact = static_cast<int>(tact), g->chunks = static_cast<int>(chunks);
+  g->R = static_cast<int>(k) * rp, g->ncols = static_cast<int>(inner);
+  g->div_inner = FastDiv32(static_cast<uint32_t>(inner));
+  g->merge = ColWalk{};
+  g->merge.tiled = 0, g->merge.P = 1, g->merge.tact = g->tact, g->merge.ncols = g->ncols, g->merge.R = g->R;
+  g->merge.lpc_shift = g->R >= 8 ? 3 : (g->R >= 4 ? 2 : (g->R >= 2 ? 1 : 0));
+  g->merge.div_ncols = FastDiv32(static_cast<uint32_t>(inner));
+  *smem = bytes;
+  return true;
+}
+
 template <int NV>
 void launch_colreg(const float* x, float* y, const ColWalk& cw, size_t smem, cudaStream_t s) {
   softmax_colreg_kernel<NV><<<cw.grid, cw.threads, smem, s>>>(x, y, cw);
@@ -491,6 +695,12 @@ bool pick_rows(const float* x, float* y, int64_t rows, int units, cudaStream_t s
 }  // namespace sb200
 
 using namespace sb200;
+
+extern "C" long long sb200_softmax_ring_timeouts(void) {
+  unsigned int n = 0;
+  if (cudaMemcpyFromSymbol(&n, g_ring_timeouts, sizeof(n)) != cudaSuccess) return -1;
+  return static_cast<long long>(n);
+}
 
 extern "C" int sb200_softmax(const float* x, float* y, int64_t outer, int64_t dim, int64_t inner,
                              void* stream) {
@@ -526,6 +736,19 @@ extern "C" int sb200_softmax(const float* x, float* y, int64_t outer, int64_t di
     else if (most <= 8) launch_colreg<8>(x, y, cw, smem, s);
     else launch_colreg<12>(x, y, cw, smem, s);
     return after_launch("sb200_softmax");
+  }
+  {
+    RingGeo rg;
+    size_t ring_smem = 0;
+    if (plan_ring(x, y, outer, dim, inner, &rg, &ring_smem)) {
+      static bool attr_set = false;   // racing first calls set the same value
+      if (!attr_set) {
+        cudaFuncSetAttribute(softmax_ring_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
+        attr_set = true;
+      }
+      softmax_ring_kernel<512><<<stream_grid(outer, 1), 512, ring_smem, s>>>(x, y, rg);
+      return after_launch("sb200_softmax");
+    }
   }
   if (plan_colwalk(x, y, outer, dim, inner, &cw)) {
     softmax_colvec_kernel<6><<<cw.grid, cw.threads, 2 * colwalk_smem(cw, sizeof(float)), s>>>(x, y, cw);

@@ -119,7 +119,8 @@ def _cases(torch, F):
         return make
 
     case("softmax_rows", "softmax_rows_kernel", softmax((6144, 4096), 3.0, -1))
-    case("softmax_strided_c4b", "softmax_colvec_kernel", softmax((512, 1000, 7, 7), 1.0, 1))
+    case("softmax_strided_c4b", "softmax_ring_kernel", softmax((512, 1000, 7, 7), 1.0, 1))
+    case("softmax_strided_c4b_few_planes", "softmax_colvec_kernel", softmax((280, 1000, 7, 7), 1.0, 1))
     case("softmax_strided_wide", "softmax_colreg_kernel", softmax((5, 21, 512, 512), 1.0, 1))
 
     def normalize():

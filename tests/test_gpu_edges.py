@@ -276,3 +276,23 @@ def test_pad_vector_stores_cross_row_boundaries():
         torch.cuda.synchronize()
         want = orc.pad(x, list(pads), value)
         assert orc.bit_equal(got.cpu().numpy(), want), (shape, pads)
+
+
+@pytest.mark.parametrize("shape", [(300, 1000, 7, 7), (310, 600, 9, 9), (300, 2500, 10), (297, 500, 14, 7), (600, 1002, 6, 4)],
+                         ids=lambda s: "x".join(str(d) for d in s))
+def test_softmax_with_the_plane_resident_in_shared_memory(shape):
+    """Planes of 96..200 KB with enough of them to pipeline: the persistent kernel that keeps a plane in
+    shared memory and streams the next one in by bulk asynchronous copies.  Ragged inner (49, 81, 10,
+    98, 24), a partial last chunk, several planes per block; none of its bounded waits may run out."""
+    from shadow_b200 import capi
+    from shadow_b200 import functional as F
+    torch = _torch()
+    x = cases.normal(7300 + shape[1], shape, 0.0, 3.0)
+    x[1, 5, 2] = -np.inf
+    x[2, :, 1] = 80.0          # a column of equal large values
+    got = F.softmax(torch.from_numpy(x).cuda(), 1)
+    torch.cuda.synchronize()
+    assert capi.lib().sb200_softmax_ring_timeouts() == 0
+    case = {"name": "softmax_resident", "op": "Softmax", "args": {"axis": 1}, "inputs": [x]}
+    want = cases.run_port(case)
+    cases.assert_parity(case, got.cpu().numpy(), want)
