@@ -460,10 +460,13 @@ def run_b200_arm(args):
         json_out = os.fdopen(os.dup(1), "w")
         os.dup2(2, 1)
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
-        # communicator set-up lines (rank count, transport) go to stderr; stdout stays the one JSON line
-        os.environ.setdefault("NCCL_DEBUG", "INFO")
+        # NCCL's communicator set-up lines (rank count, transport) are wanted in the log: INFO level for the INIT
+        # subsystem.  NCCL writes them to the process's stdout, which points at stderr for this run (above), so
+        # stdout proper stays the one JSON line.
+        if os.environ.get("NCCL_DEBUG", "").upper() not in ("INFO", "TRACE"):
+            os.environ["NCCL_DEBUG"] = "INFO"
         os.environ.setdefault("NCCL_DEBUG_SUBSYS", "INIT")
-        os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")
+        os.environ.pop("NCCL_DEBUG_FILE", None)
         # a rank that stalls in a collective must not keep 8 GPUs busy: the whole run takes well
         # under a minute, so after 3 minutes the process ends itself
         safety = threading.Timer(180.0, os._exit, args=(3,))
