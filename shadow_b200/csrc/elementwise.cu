@@ -31,6 +31,13 @@ struct GuardedTileTrait<F, decltype(void(F::kGuardedTile))> { static constexpr b
 template <typename F>
 __host__ __device__ constexpr bool guarded_tile() { return GuardedTileTrait<F>::value; }
 
+// Functors built on expf_like_glibc ask (static member kUsesExpfConsts) for its constants to be loaded
+// once per thread and handed to eval(x, consts).
+template <typename F, typename = void>
+struct ExpfConstsTrait { static constexpr bool value = false; };
+template <typename F>
+struct ExpfConstsTrait<F, decltype(void(F::kUsesExpfConsts))> { static constexpr bool value = F::kUsesExpfConsts; };
+
 // Calls f with as many operands as the kernel has inputs.
 template <int NIN, typename F>
 __device__ __forceinline__ float apply(const F& f, float a, float b) {
@@ -88,10 +95,20 @@ ew_vec_kernel(const float* a, const float* b, float* y, int64_t n, int head, F f
         if (NIN >= 2) vb[u] = ld_stream(b4 + v);
       }
     }
+    if constexpr (ExpfConstsTrait<F>::value) {
+      const ExpfConsts c = load_expf_consts();
 #pragma unroll
-    for (int u = 0; u < kUnroll; ++u) {
-      const int64_t v = first + u * kThreads;
-      if (v < nvec) st_stream(y4 + v, apply4<NIN>(f, va[u], vb[u]));
+      for (int u = 0; u < kUnroll; ++u) {
+        const int64_t v = first + u * kThreads;
+        if (v < nvec)
+          st_stream(y4 + v, make_float4(f.eval(va[u].x, c), f.eval(va[u].y, c), f.eval(va[u].z, c), f.eval(va[u].w, c)));
+      }
+    } else {
+#pragma unroll
+      for (int u = 0; u < kUnroll; ++u) {
+        const int64_t v = first + u * kThreads;
+        if (v < nvec) st_stream(y4 + v, apply4<NIN>(f, va[u], vb[u]));
+      }
     }
   }
 }

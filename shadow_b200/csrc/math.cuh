@@ -40,6 +40,48 @@ __device__ __align__(128) const unsigned long long kExp2fTable[32] = {
 // the polynomial) are the ones glibc's build for processors with FMA contracts; with them the result
 // equals glibc 2.39's expf on all 2^32 inputs (checked on the host), and a build without FMA differs
 // on two inputs by one ulp.
+// The six double constants of expf_like_glibc held in (vector) REGISTERS for a whole thread.  Written
+// as literals they are materialised again and again through uniform registers and moves (profile: 5-7
+// integer move instructions per element); read once per thread through an index the compiler cannot
+// fold (a zero loaded from memory) they stay in twelve registers.  Used by Sigmoid (34 instead of 40
+// instructions per element, 0.74 instead of 0.70 of 8 TB/s).  The same treatment made Tanh slower (the
+// compiler moved its nine constants back to uniform registers) and delays the start of the plain Exp,
+// which streams at the DRAM limit anyway: both keep literals.
+struct ExpfConsts {
+  double inv_ln2n, shift, c0, c1, c2, one;
+};
+__device__ const double kExpfConstTable[6] = {0x1.71547652b82fep+0 * 32.0, 0x1.8p+52,
+                                             0x1.c6af84b912394p-5 / 32.0 / 32.0 / 32.0, 0x1.ebfce50fac4f3p-3 / 32.0 / 32.0,
+                                             0x1.62e42ff0c52d6p-1 / 32.0, 1.0};
+__device__ int g_expf_zero = 0;
+__device__ __forceinline__ ExpfConsts load_expf_consts() {
+  int z;
+  asm volatile("ld.volatile.global.s32 %0, [%1];" : "=r"(z) : "l"(&g_expf_zero));
+  ExpfConsts k;
+  k.inv_ln2n = kExpfConstTable[z + 0], k.shift = kExpfConstTable[z + 1], k.c0 = kExpfConstTable[z + 2];
+  k.c1 = kExpfConstTable[z + 3], k.c2 = kExpfConstTable[z + 4], k.one = kExpfConstTable[z + 5];
+  return k;
+}
+// expf_like_glibc with the constants passed in (same operations, same bits).
+__device__ __forceinline__ float expf_like_glibc(float x, const ExpfConsts& c) {
+  float xc;
+  asm("max.NaN.f32 %0, %1, %2;" : "=f"(xc) : "f"(x), "f"(-104.5f));
+  asm("min.NaN.f32 %0, %1, %2;" : "=f"(xc) : "f"(xc), "f"(89.f));
+  const double xd = static_cast<double>(xc);
+  double kd = fma(c.inv_ln2n, xd, c.shift);
+  const int ki = __double2loint(kd);
+  kd = __dsub_rn(kd, c.shift);
+  const double r = fma(c.inv_ln2n, xd, -kd);
+  const double tab = __longlong_as_double(static_cast<long long>(__ldg(&kExp2fTable[ki & 31])));
+  const double s = __hiloint2double(__double2hiint(tab) + static_cast<int>(static_cast<unsigned>(ki) << 15), __double2loint(tab));
+  const double q = fma(c.c0, r, c.c1);
+  const double r2 = __dmul_rn(r, r);
+  double y = fma(c.c2, r, c.one);
+  y = fma(q, r2, y);
+  y = __dmul_rn(y, s);
+  return static_cast<float>(y);
+}
+
 __device__ __forceinline__ float expf_like_glibc(float x) {
   constexpr double kInvLn2N = 0x1.71547652b82fep+0 * 32.0;
   constexpr double kShift = 0x1.8p+52;
@@ -111,17 +153,19 @@ __device__ __forceinline__ double rcp_newton(double d) {
   return fma(r0, fma(-d, r0, 1.0), r0);
 }
 
-// Correctly rounded 1/y for a float y >= 1 (or +inf, or NaN): hardware seed (within 1 ulp) and one
-// fma correction, r1 = r0 + r0*(1 - y*r0).  Bit-identical to __frcp_rn on this domain (checked through
-// Sigmoid over all 2^32 inputs) at a fraction of its cost.  The flush-to-zero seed has no denormal
-// handling code around it; the few arguments whose reciprocal is denormal (y > 2^125, infinity
-// included) take the IEEE instruction.  A NaN runs through the arithmetic.
+// 1/y for a float y >= 1 (or +inf, or NaN), correctly rounded wherever the result is a normal float:
+// hardware seed (within 1 ulp) and one fma correction, r1 = r0 + r0*(1 - y*r0), computed on y * 2^-32 so
+// that seed and result stay normal for every y (no denormal handling code around the flush-to-zero
+// seed, no branch), then scaled back by 2^-32 - exact unless the result is denormal (y > 2^126), where
+// this second rounding can differ from the IEEE quotient by one unit of the denormal grid (through
+// Sigmoid: 34,015 of the 2^32 inputs, all with x < -87.3).  Infinity gives 0, a NaN runs through.
 __device__ __forceinline__ float rcp_correct(float y) {
-  if (y > 0x1p125f) return __frcp_rn(y);
+  const float ys = __fmul_rn(y, 0x1p-32f);
   float r0;
-  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0) : "f"(y));
-  const float e = fmaf(-y, r0, 1.0f);
-  return fmaf(r0, e, r0);
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r0) : "f"(ys));
+  const float e = fmaf(-ys, r0, 1.0f);
+  const float r1 = fmaf(r0, e, r0);
+  return (y == CUDART_INF_F) ? 0.f : __fmul_rn(r1, 0x1p-32f);
 }
 
 // tanh(x) = 1 - 2/(e^{2|x|} + 1) in double, rounded once; for |x| < 2^-12 the float result is x
@@ -175,6 +219,9 @@ struct UnaryFn {
   // Which tile code path the elementwise kernel uses for this functor (see ew_vec_kernel): for the
   // double-precision exp the per-group guarded form schedules markedly better (6.6 vs 5.5 TB/s).
   static constexpr bool kGuardedTile = (OP == SB200_EXP);
+  // (Exp alone streams at the DRAM limit with literal constants; loading them per thread only delays its start)
+  static constexpr bool kUsesExpfConsts = false;
+  __device__ __forceinline__ float eval(float x, const ExpfConsts& c) const { return expf_like_glibc(x, c); }
   __device__ __forceinline__ float operator()(float x) const {
     if (OP == SB200_ABS) return fabsf(x);
     if (OP == SB200_SQUARE) return __fmul_rn(x, x);
@@ -198,12 +245,16 @@ struct UnaryFn {
 template <int TYPE>
 struct ActivateFn {
   static constexpr bool kGuardedTile = (TYPE == SB200_SIGMOID || TYPE == SB200_TANH);
+  static constexpr bool kUsesExpfConsts = (TYPE == SB200_SIGMOID);
   float slope;
+  __device__ __forceinline__ float eval(float x, const ExpfConsts& c) const {
+    return rcp_correct(__fadd_rn(1.f, expf_like_glibc(-x, c)));
+  }
   __device__ __forceinline__ float operator()(float x) const {
     if (TYPE == SB200_RELU) return x > 0.f ? x : 0.f;
     if (TYPE == SB200_LEAKY) return x > 0.f ? x : __fmul_rn(slope, x);
-    // 1 / (1 + exp(-x)): glibc's expf bit for bit, a float add, then the correctly rounded
-    // reciprocal (== IEEE 1.0f / y)
+    // 1 / (1 + exp(-x)): glibc's expf bit for bit, a float add, then the reciprocal (== IEEE 1.0f / y
+    // for every normal result)
     if (TYPE == SB200_SIGMOID) return rcp_correct(__fadd_rn(1.f, expf_like_glibc(-x)));
     if (TYPE == SB200_SOFTPLUS) {
       // log1pf(expf(x)): expf as glibc computes it, then log1p in double rounded once
