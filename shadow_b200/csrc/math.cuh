@@ -196,6 +196,38 @@ __device__ __forceinline__ float div_exact(float x, float d, float rcp, bool d_o
   return __fdiv_rn(x, d);
 }
 
+// Four quotients at once with ONE decision for the group: when all four dividends are zero or lie in
+// [2^-60, 2^60] and all divisors are fine, the three-instruction step runs for all of them; otherwise
+// each goes through div_exact on its own.  (A zero dividend is safe in the fast step: q0 = +-0, the
+// residual is 0, the result +-0 with the dividend's sign.)  One divergence region per float4 instead
+// of one per element: about three instructions per element less in the normalisation kernels.
+__device__ __forceinline__ bool div_fast_ok(float x) {
+  const uint32_t ax = __float_as_uint(x) & 0x7fffffffu;
+  const uint32_t lo = (127u - 60u) << 23, hi = (127u + 60u) << 23;
+  return (ax - lo) <= (hi - lo) || ax == 0u;
+}
+__device__ __forceinline__ void div_exact4(float (&x)[4], const float (&d)[4], const float (&rcp)[4], const bool (&d_ok)[4]) {
+  const bool fast = d_ok[0] && d_ok[1] && d_ok[2] && d_ok[3] && div_fast_ok(x[0]) && div_fast_ok(x[1]) && div_fast_ok(x[2]) &&
+                    div_fast_ok(x[3]);
+  if (fast) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float q0 = __fmul_rn(x[e], rcp[e]);
+      const float r = __fmaf_rn(-d[e], q0, x[e]);
+      x[e] = __fmaf_rn(r, rcp[e], q0);
+    }
+  } else {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) x[e] = div_exact(x[e], d[e], rcp[e], d_ok[e]);
+  }
+}
+// The same with one divisor for the four.
+__device__ __forceinline__ void div_exact4(float (&x)[4], float d, float rcp, bool d_ok) {
+  const float dd[4] = {d, d, d, d}, rr[4] = {rcp, rcp, rcp, rcp};
+  const bool oo[4] = {d_ok, d_ok, d_ok, d_ok};
+  div_exact4(x, dd, rr, oo);
+}
+
 // ---- functors -----------------------------------------------------------------------------------
 // std::max(a, b) == (a < b) ? b : a and std::min(a, b) == (b < a) ? b : a.
 __device__ __forceinline__ float std_max(float a, float b) { return (a < b) ? b : a; }

@@ -180,8 +180,8 @@ normalize_colvec_kernel(const float* x, float* y, const __grid_constant__ ColWal
 #pragma unroll
   for (int e = 0; e < 4; ++e) row[e] = L.row0 + ((!q.tiled && L.rem0 + e >= q.ncols) ? 1 : 0);
   auto out4 = [&](const float4& v, int k) {
-    float o[4] = {div_exact(v.x, d[0], rcp[0], ok[0]), div_exact(v.y, d[1], rcp[1], ok[1]),
-                  div_exact(v.z, d[2], rcp[2], ok[2]), div_exact(v.w, d[3], rcp[3], ok[3])};
+    float o[4] = {v.x, v.y, v.z, v.w};
+    div_exact4(o, d, rcp, ok);
     if (SCALE == kScaleShared) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) o[e] = __fmul_rn(o[e], shared_scale);
@@ -280,9 +280,10 @@ normalize_rows_kernel(const float* x, float* y, int64_t rows, int units_per_row,
     const int u = t + i * TPR;
     if (live && u < units_per_row) {
       float o[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+      if (MODE != kSsdSpatial) div_exact4(o, d, rcp, d_ok);
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        o[e] = (MODE == kSsdSpatial) ? __fmul_rn(o[e], factor) : div_exact(o[e], d, rcp, d_ok);
+        if (MODE == kSsdSpatial) o[e] = __fmul_rn(o[e], factor);
         if (SCALE == kScaleShared) o[e] = __fmul_rn(o[e], shared_scale);
         if (SCALE == kScaleChannel) o[e] = __fmul_rn(o[e], __ldg(ssd.scale + ssd.div_spatial.div(static_cast<uint32_t>(4 * u + e))));
       }

@@ -125,8 +125,14 @@ rownorm_rows_kernel(const float* x, float* y, int64_t rows, int units_per_row, f
     const int u = t + i * TPR;
     if (live && u < units_per_row) {
       float o[W];
+      if constexpr (W == 4) {
 #pragma unroll
-      for (int e = 0; e < W; ++e) o[e] = div_exact(v[i][e], d, rcp, d_ok);
+        for (int e = 0; e < W; ++e) o[e] = v[i][e];
+        div_exact4(o, d, rcp, d_ok);
+      } else {
+#pragma unroll
+        for (int e = 0; e < W; ++e) o[e] = div_exact(v[i][e], d, rcp, d_ok);
+      }
       if (vec_affine) {
         const float4 sc = __ldg(reinterpret_cast<const float4*>(aff.scale) + u), bs = __ldg(reinterpret_cast<const float4*>(aff.bias) + u);
         o[0] = __fadd_rn(__fmul_rn(o[0], sc.x), bs.x);
@@ -270,8 +276,8 @@ rownorm_smem_rows_kernel(const float* x, float* y, int64_t rows, int units, floa
     const uint32_t base = channel_base(aff, row);
     for (int u = threadIdx.x; u < units; u += T) {
       const float4 q = buf[u];
-      float o[4] = {div_exact(__fsub_rn(q.x, mean), d, rcp, d_ok), div_exact(__fsub_rn(q.y, mean), d, rcp, d_ok),
-                    div_exact(__fsub_rn(q.z, mean), d, rcp, d_ok), div_exact(__fsub_rn(q.w, mean), d, rcp, d_ok)};
+      float o[4] = {__fsub_rn(q.x, mean), __fsub_rn(q.y, mean), __fsub_rn(q.z, mean), __fsub_rn(q.w, mean)};
+      div_exact4(o, d, rcp, d_ok);
       if (aff.mode == kAffineChannel) {
         // long rows: the four lanes of a float4 almost always share a channel - one index, one scale, one bias
         const uint32_t k0 = affine_index(aff, base, static_cast<uint32_t>(4 * u)), k3 = affine_index(aff, base, static_cast<uint32_t>(4 * u + 3));
