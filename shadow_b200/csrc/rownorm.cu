@@ -153,8 +153,8 @@ rownorm_rows_kernel(const float* x, float* y, int64_t rows, int units_per_row, f
 // read come from L2 (the grid is sized so that the rows in flight fit there).  Used for rows that
 // would need a 1024-thread block in the register kernel (one resident block per SM, no overlap
 // of one row's load with another's arithmetic) and for rows too long for registers at all.
-template <bool VEC>
-__global__ void __launch_bounds__(256)
+template <bool VEC, int T>
+__global__ void __launch_bounds__(T)
 rownorm_long_rows_kernel(const float* x, float* y, int64_t rows, int64_t inner, float alpha, float eps,
                          const __grid_constant__ Affine aff) {
   constexpr int W = VEC ? 4 : 1;
@@ -174,28 +174,28 @@ rownorm_long_rows_kernel(const float* x, float* y, int64_t rows, int64_t inner, 
     const float* xr = x + row * inner;
     float* yr = y + row * inner;
     double acc = 0.0;
-    for (int64_t u0 = threadIdx.x; u0 < units; u0 += 256 * kB) {
+    for (int64_t u0 = threadIdx.x; u0 < units; u0 += T * kB) {
       float v[kB][W];
 #pragma unroll
       for (int k = 0; k < kB; ++k)
-        if (u0 + k * 256 < units) load(xr, u0 + k * 256, v[k]);
+        if (u0 + k * T < units) load(xr, u0 + k * T, v[k]);
 #pragma unroll
       for (int k = 0; k < kB; ++k)
-        if (u0 + k * 256 < units) {
+        if (u0 + k * T < units) {
 #pragma unroll
           for (int e = 0; e < W; ++e) acc += static_cast<double>(__fmul_rn(alpha, v[k][e]));
         }
     }
     const float mean = static_cast<float>(block_reduce(acc, OpAddD(), 0.0, red));
     acc = 0.0;
-    for (int64_t u0 = threadIdx.x; u0 < units; u0 += 256 * kB) {
+    for (int64_t u0 = threadIdx.x; u0 < units; u0 += T * kB) {
       float v[kB][W];
 #pragma unroll
       for (int k = 0; k < kB; ++k)
-        if (u0 + k * 256 < units) load(xr, u0 + k * 256, v[k]);
+        if (u0 + k * T < units) load(xr, u0 + k * T, v[k]);
 #pragma unroll
       for (int k = 0; k < kB; ++k)
-        if (u0 + k * 256 < units) {
+        if (u0 + k * T < units) {
 #pragma unroll
           for (int e = 0; e < W; ++e) {
             const float c = __fsub_rn(v[k][e], mean);
@@ -208,20 +208,26 @@ rownorm_long_rows_kernel(const float* x, float* y, int64_t rows, int64_t inner, 
     const bool d_ok = (d >= 0x1p-60f) && (d <= 0x1p60f);
     const float rcp = __frcp_rn(d);
     const uint32_t base = channel_base(aff, row);
-    for (int64_t u0 = threadIdx.x; u0 < units; u0 += 256 * kB) {
+    for (int64_t u0 = threadIdx.x; u0 < units; u0 += T * kB) {
       float v[kB][W];
 #pragma unroll
       for (int k = 0; k < kB; ++k)
-        if (u0 + k * 256 < units) load(xr, u0 + k * 256, v[k]);
+        if (u0 + k * T < units) load(xr, u0 + k * T, v[k]);
 #pragma unroll
       for (int k = 0; k < kB; ++k) {
-        const int64_t u = u0 + k * 256;
+        const int64_t u = u0 + k * T;
         if (u < units) {
           float o[W];
 #pragma unroll
-          for (int e = 0; e < W; ++e) {
-            o[e] = div_exact(__fsub_rn(v[k][e], mean), d, rcp, d_ok);
-            if (aff.mode != kAffineNone) o[e] = affine_apply(aff, o[e], affine_index(aff, base, static_cast<uint32_t>(u * W + e)));
+          for (int e = 0; e < W; ++e) o[e] = __fsub_rn(v[k][e], mean);
+          if constexpr (W == 4) {
+            div_exact4(o, d, rcp, d_ok);
+          } else {
+            o[0] = div_exact(o[0], d, rcp, d_ok);
+          }
+          if (aff.mode != kAffineNone) {
+#pragma unroll
+            for (int e = 0; e < W; ++e) o[e] = affine_apply(aff, o[e], affine_index(aff, base, static_cast<uint32_t>(u * W + e)));
           }
           if (VEC) st_stream(reinterpret_cast<float4*>(yr) + u, make_float4(o[0], o[W > 1 ? 1 : 0], o[W > 2 ? 2 : 0], o[W > 3 ? 3 : 0]));
           else st_stream(yr + u, o[0]);
@@ -371,8 +377,15 @@ extern "C" int sb200_row_norm(const float* x, float* y, int64_t rows, int64_t in
     int64_t per_sm = (48ll << 20) / (inner * 4) / sm_count();
     per_sm = per_sm < 1 ? 1 : (per_sm > 8 ? 8 : per_sm);
     const unsigned grid = stream_grid(rows, static_cast<int>(per_sm));
-    if (vec) rownorm_long_rows_kernel<true><<<grid, 256, 0, s>>>(x, y, rows, inner, alpha, eps, aff);
-    else rownorm_long_rows_kernel<false><<<grid, 256, 0, s>>>(x, y, rows, inner, alpha, eps, aff);
+    // rows this long leave room for few blocks (their re-reads must stay in L2): large blocks keep the SM busy
+    if (inner >= 32768) {
+      if (vec) rownorm_long_rows_kernel<true, 1024><<<grid, 1024, 0, s>>>(x, y, rows, inner, alpha, eps, aff);
+      else rownorm_long_rows_kernel<false, 1024><<<grid, 1024, 0, s>>>(x, y, rows, inner, alpha, eps, aff);
+    } else if (vec) {
+      rownorm_long_rows_kernel<true, 256><<<grid, 256, 0, s>>>(x, y, rows, inner, alpha, eps, aff);
+    } else {
+      rownorm_long_rows_kernel<false, 256><<<grid, 256, 0, s>>>(x, y, rows, inner, alpha, eps, aff);
+    }
   }
   return after_launch("sb200_row_norm");
 }
