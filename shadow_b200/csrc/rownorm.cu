@@ -320,7 +320,7 @@ bool pick_rows(const float* x, float* y, int64_t rows, int units, float alpha, f
 #define SB200_TRY(TPR, NV) \
   if (units <= TPR * NV) { launch_rows<TPR, NV, VEC>(x, y, rows, units, alpha, eps, aff, s); return true; }
   SB200_TRY(32, 1) SB200_TRY(32, 2) SB200_TRY(32, 4)
-  SB200_TRY(64, 4) SB200_TRY(128, 4) SB200_TRY(256, 4) SB200_TRY(512, 4)
+  SB200_TRY(64, 4) SB200_TRY(128, 4) SB200_TRY(128, 6) SB200_TRY(128, 7) SB200_TRY(256, 4) SB200_TRY(256, 6) SB200_TRY(512, 4)
 #undef SB200_TRY
   return false;
 }
