@@ -120,16 +120,16 @@ __device__ __align__(128) const double kExp2Sixteenths[16] = {
 // classic scheme): x = k*(ln2/16) + r with k = round(x*16/ln2), |r| <= ln2/32, then
 // e^x = 2^(k>>4) * 2^((k&15)/16) * e^r with e^r by its degree-4 Taylor polynomial
 // (r^5/120 < 4.1e-11).  k is found by adding the 1.5*2^52 rounding constant in double (no
-// conversion instruction: the conversion unit is the scarce pipe of these kernels); the reduction
-// runs in double with ln2/16 split so that k*hi is exact.
+// conversion instruction); the reduction is one fused multiply-add with ln2/16 in double.
 __device__ __forceinline__ double exp_core(float x) {
   const double xd = static_cast<double>(x);
   const double kRound = 6755399441055744.0;                 // 1.5 * 2^52: adding it rounds to an integer
   const double t = fma(xd, 23.083120654223414, kRound);     // x * 16/ln2, integer part in the low word
   const int ki = __double2loint(t);                         // k as a signed integer (|k| < 2^12)
   const double kd = t - kRound;
-  double r = fma(kd, -0.043321698773070239, xd);
-  r = fma(kd, -1.1926343307941173e-11, r);
+  // one-step reduction: the rounding of ln2/16 to double moves r by at most 2^9 * 5e-18, far below the
+  // 4e-11 of the polynomial
+  const double r = fma(kd, -0.043321698784996581, xd);
   double p = fma(r, 4.16666666666666666667e-02, 1.66666666666666666667e-01);
   p = fma(p, r, 0.5);
   p = fma(p, r, 1.0);
@@ -144,8 +144,7 @@ __device__ __forceinline__ double exp_core(float x) {
 // goes double -> float -> double by bit manipulation (truncation is fine for a seed), because
 // each cvt instruction costs a slot of the conversion unit, the busiest pipe of the tanh kernel.
 __device__ __forceinline__ double rcp_newton(double d) {
-  const unsigned hi = static_cast<unsigned>(__double2hiint(d)), lo = static_cast<unsigned>(__double2loint(d));
-  const float df = __uint_as_float(((hi - 0x38000000u) << 3) | (lo >> 29));   // d truncated to float
+  const float df = __double2float_rz(d);   // (the kernel is bound by instruction issue: one conversion beats four integer operations)
   float seed;
   asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(seed) : "f"(df));
   const unsigned sb = __float_as_uint(seed);                                   // positive, normal
