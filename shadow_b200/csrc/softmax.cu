@@ -467,7 +467,7 @@ softmax_colreg_kernel(const float* x, float* y, const __grid_constant__ ColWalk 
 // persistent block per SM keeps the whole plane in shared memory, cut into chunks of 5 * tact float4
 // (tact = k periods of the fixed-column walk, so thread t owns float4 t, t + tact, ... of every chunk
 // and its four lanes stay on four columns).  The chunks are brought in by bulk asynchronous copies
-// (cp.async.bulk global -> shared, completion counted on one mbarrier per chunk; no multicast, no
+// (cp.async.bulk global -> shared, one block's own memory only, completion counted on one mbarrier per chunk; no
 // registers involved), so the tensor is read from DRAM once and never re-read through the L2:
 //   pass 1 takes the chunks in order as they land (running sums against integer references,
 //          lanes_take), the column references and sums meet through shared memory;
