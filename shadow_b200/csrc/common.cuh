@@ -112,6 +112,20 @@ struct OpMulD { __device__ __forceinline__ double operator()(double a, double b)
 struct OpMaxF { __device__ __forceinline__ float operator()(float a, float b) const { return (a < b) ? b : a; } };
 struct OpMinF { __device__ __forceinline__ float operator()(float a, float b) const { return (b < a) ? b : a; } };
 
+// ---- opting a kernel into more than 48 KB of dynamic shared memory -----------------------------------
+// The attribute belongs to the (kernel, device) pair, and a process may drive several devices (one
+// Network per device): `done` is one bit per device ordinal, kept by the caller per kernel
+// instantiation.  Racing first calls set the same value.
+template <typename Kernel>
+inline void allow_dynamic_smem(Kernel kernel, int bytes, unsigned long long* done) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) dev = 63;   // ordinals past 63 share a bit: set every time
+  const unsigned long long bit = 1ull << dev;
+  if ((*done & bit) && dev != 63) return;
+  cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+  *done |= bit;
+}
+
 // ---- asynchronous 16-byte copies global -> shared (no register staging) ---------------------------
 __device__ __forceinline__ void cp_async16(uint32_t smem_addr, const void* gptr) {
   asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_addr), "l"(gptr) : "memory");

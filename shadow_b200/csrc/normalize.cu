@@ -318,11 +318,8 @@ void launch_colvec(const float* x, float* y, const ColWalk& cw, float p, float e
   constexpr int U = 4, NB = 2;
   size_t smem = colwalk_smem(cw, sizeof(double));
   if (smem < colwalk_ring_bytes(cw, U, NB)) smem = colwalk_ring_bytes(cw, U, NB);
-  static bool attr_set = false;   // per instantiation; racing first calls set the same value
-  if (!attr_set) {
-    cudaFuncSetAttribute(normalize_colvec_kernel<MODE, SCALE, U, NB>, cudaFuncAttributeMaxDynamicSharedMemorySize, 1024 * U * NB * 16);
-    attr_set = true;
-  }
+  static unsigned long long attr_done = 0;   // per instantiation, one bit per device
+  allow_dynamic_smem(normalize_colvec_kernel<MODE, SCALE, U, NB>, 1024 * U * NB * 16, &attr_done);
   normalize_colvec_kernel<MODE, SCALE, U, NB><<<cw.grid, cw.threads, smem, s>>>(x, y, cw, p, eps, ssd);
 }
 

@@ -661,11 +661,8 @@ void launch_stage1(const Plan& P, const float* x, float* y, double* part, cudaSt
     constexpr int U = 2, NB = 3;
     size_t smem = colwalk_smem(P.cw, sizeof(typename RedOp<OP>::Acc));
     if (smem < colwalk_ring_bytes(P.cw, U, NB)) smem = colwalk_ring_bytes(P.cw, U, NB);
-    static bool attr_set = false;   // per instantiation; racing first calls set the same value
-    if (!attr_set) {
-      cudaFuncSetAttribute(redC_kernel<OP, U, NB, TO_PART>, cudaFuncAttributeMaxDynamicSharedMemorySize, 512 * U * NB * 16);
-      attr_set = true;
-    }
+    static unsigned long long attr_done = 0;   // per instantiation, one bit per device
+    allow_dynamic_smem(redC_kernel<OP, U, NB, TO_PART>, 512 * U * NB * 16, &attr_done);
     redC_kernel<OP, U, NB, TO_PART><<<P.cw.grid, P.cw.threads, smem, s>>>(x, y, part, P.cw, P.n_out, P.b.count);
   } else if (P.family == kFamB) {
     dim3 grid(static_cast<unsigned>(P.b.nbx * P.b.K0), static_cast<unsigned>(P.splits));

@@ -360,12 +360,9 @@ extern "C" int sb200_row_norm(const float* x, float* y, int64_t rows, int64_t in
   if (!done && vec && inner * 4 <= 224 * 1024) {
     // the row fits the shared memory of a block
     const size_t bytes = static_cast<size_t>(inner) * 4;
-    static bool attr_set = false;   // racing first calls set the same values
-    if (!attr_set) {
-      cudaFuncSetAttribute(rownorm_smem_rows_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
-      cudaFuncSetAttribute(rownorm_smem_rows_kernel<1024>, cudaFuncAttributeMaxDynamicSharedMemorySize, 224 * 1024);
-      attr_set = true;
-    }
+    static unsigned long long attr_done_512 = 0, attr_done_1024 = 0;   // one bit per device
+    allow_dynamic_smem(rownorm_smem_rows_kernel<512>, 110 * 1024, &attr_done_512);
+    allow_dynamic_smem(rownorm_smem_rows_kernel<1024>, 224 * 1024, &attr_done_1024);
     if (bytes <= 110 * 1024)
       rownorm_smem_rows_kernel<512><<<stream_grid(rows, 2), 512, bytes, s>>>(x, y, rows, static_cast<int>(inner / 4), alpha, eps, aff);
     else

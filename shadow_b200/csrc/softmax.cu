@@ -741,11 +741,8 @@ extern "C" int sb200_softmax(const float* x, float* y, int64_t outer, int64_t di
     RingGeo rg;
     size_t ring_smem = 0;
     if (plan_ring(x, y, outer, dim, inner, &rg, &ring_smem)) {
-      static bool attr_set = false;   // racing first calls set the same value
-      if (!attr_set) {
-        cudaFuncSetAttribute(softmax_ring_kernel<512>, cudaFuncAttributeMaxDynamicSharedMemorySize, 226 * 1024);
-        attr_set = true;
-      }
+      static unsigned long long attr_done = 0;   // one bit per device
+      allow_dynamic_smem(softmax_ring_kernel<512>, 226 * 1024, &attr_done);
       softmax_ring_kernel<512><<<stream_grid(outer, 1), 512, ring_smem, s>>>(x, y, rg);
       return after_launch("sb200_softmax");
     }

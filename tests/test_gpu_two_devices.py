@@ -1,0 +1,43 @@
+"""One process driving two devices (the reference's multi-device model is one Network per device_id,
+shadow/core/context.cu:10-15): per-device state of the kernel library - the opt-in to large dynamic
+shared memory, the cached multiprocessor count, the built-in reduction scratch - must be set up on
+each device it is used on.  Skipped on a machine with one GPU."""
+import numpy as np
+import pytest
+
+import cases
+
+pytestmark = pytest.mark.gpu
+
+
+def test_kernels_with_per_device_state_run_on_a_second_device():
+    import torch
+    from shadow_b200 import capi
+    from shadow_b200 import functional as F
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    x_soft = cases.normal(8100, (300, 1000, 7, 7), 0.0, 2.0)       # resident-plane Softmax (226 KB of shared memory)
+    x_gn = cases.normal(8101, (40, 8, 56, 56))                     # GroupNorm over 100 KB rows staged in shared memory
+    x_red = cases.normal(8102, (600, 64, 14, 14))                  # inner-kept Reduce with its copy ring
+    want_soft = cases.run_port({"name": "s", "op": "Softmax", "args": {"axis": 1}, "inputs": [x_soft]})
+    want_gn = cases.run_port({"name": "g", "op": "GroupNorm", "args": {"group": 1, "eps": 1e-5}, "inputs": [x_gn]})
+    want_red = cases.run_port({"name": "r", "op": "Reduce", "args": {"operation": 1, "axes": [1], "keep_dims": True}, "inputs": [x_red]})
+    for dev in (0, 1, 0):
+        with torch.cuda.device(dev):
+            d = torch.device("cuda", dev)
+            got_soft = F.softmax(torch.from_numpy(x_soft).to(d), 1)
+            got_gn = F.group_norm(torch.from_numpy(x_gn).to(d), 1, None, None, 1e-5)
+            got_red = F.reduce(torch.from_numpy(x_red).to(d), 1, [1], keep_dims=True)
+            lib = capi.lib()
+            y = torch.empty(1, device=d)
+            big = torch.from_numpy(cases.normal(8103, (8, 1024, 1024))).to(d)
+            capi.check(lib.sb200_reduce_static(big.data_ptr(), capi.ints(big.shape), 3, capi.ints([0, 1, 2]), 3, 1, y.data_ptr(),
+                                               torch.cuda.current_stream().cuda_stream), "sb200_reduce_static")
+            torch.cuda.synchronize()
+            assert lib.sb200_softmax_ring_timeouts() == 0
+            cases.assert_parity({"name": "s", "op": "Softmax", "args": {"axis": 1}, "inputs": [x_soft]}, got_soft.cpu().numpy(), want_soft)
+            cases.assert_parity({"name": "g", "op": "GroupNorm", "args": {"group": 1, "eps": 1e-5}, "inputs": [x_gn]},
+                                got_gn.cpu().numpy().reshape(want_gn.shape), want_gn)
+            cases.assert_parity({"name": "r", "op": "Reduce", "args": {"operation": 1, "axes": [1], "keep_dims": True}, "inputs": [x_red]},
+                                got_red.cpu().numpy().reshape(want_red.shape), want_red)
+            assert np.isclose(float(y.item()), float(np.sum(big.cpu().numpy().astype(np.float64))), rtol=1e-5, atol=1e-2)
