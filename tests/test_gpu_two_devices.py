@@ -41,3 +41,32 @@ def test_kernels_with_per_device_state_run_on_a_second_device():
             cases.assert_parity({"name": "r", "op": "Reduce", "args": {"operation": 1, "axes": [1], "keep_dims": True}, "inputs": [x_red]},
                                 got_red.cpu().numpy().reshape(want_red.shape), want_red)
             assert np.isclose(float(y.item()), float(np.sum(big.cpu().numpy().astype(np.float64))), rtol=1e-5, atol=1e-2)
+
+
+def test_cpp_host_with_one_thread_per_device_uses_the_c_entry_points(tmp_path):
+    """tests/support/comm_two_threads.cpp: no Python in the data path - a C++ program whose two host threads
+    each own a device, shard a tensor, and finish a Sum and a Max over all axes with one
+    sb200_sharded_reduce_finish call."""
+    import os
+    import shutil
+    import subprocess
+    import torch
+    from shadow_b200 import build as sbuild
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    if sbuild.build_comm() is None:
+        pytest.skip("no NCCL on this machine")
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    lib_dir = os.path.join(root, "shadow_b200", "lib")
+    nvcc = shutil.which("nvcc") or "/usr/local/cuda/bin/nvcc"
+    cuda_home = os.path.dirname(os.path.dirname(nvcc))
+    exe = str(tmp_path / "comm_two_threads")
+    build = subprocess.run(["g++", "-O1", "-std=c++17", "-o", exe, os.path.join(root, "tests", "support", "comm_two_threads.cpp"),
+                            "-I" + os.path.join(root, "include"), "-I" + os.path.join(cuda_home, "include"),
+                            "-L" + lib_dir, "-lsb200_nccl", "-lsb200", "-Wl,-rpath," + lib_dir,
+                            "-L" + os.path.join(cuda_home, "lib64"), "-lcudart", "-lpthread"], capture_output=True, text=True)
+    assert build.returncode == 0, build.stderr
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    run = subprocess.run([exe, "2"], capture_output=True, text=True, timeout=180, env=env)
+    assert run.returncode == 0, run.stdout + run.stderr
+    assert any(line.startswith("ok: 2 ranks") for line in run.stdout.splitlines()), run.stdout   # (NCCL may print its version first)
