@@ -607,6 +607,20 @@ def run_b200_arm(args):
         want_sum, want_max = float(np.float32(acc)), float(np.float32(host[:, 1].max()))
         results_check = {"sum_from_rank_partials": want_sum, "max_from_rank_partials": want_max,
                          "matches": bool(want_sum == float(s.item()) and want_max == float(m.item()))}
+        if rank == 0:
+            # and against the whole (unsharded) tensor on the host: float products as the operator forms them,
+            # summed in double, slice by slice (a few seconds of numpy on rank 0, outside every timed region)
+            a_full, b_full = make_inputs(A_SHAPE, B_SHAPE)
+            host_sum, host_max = 0.0, -np.inf
+            for n in range(A_SHAPE[0]):
+                o = a_full[n] * b_full[0]            # [1,2048,2048] x [16,1,2048] -> [16,2048,2048] float32
+                host_sum += float(np.sum(o, dtype=np.float64))
+                host_max = max(host_max, float(o.max()))
+            tol = 1e-5 * np.log2(numel(O_SHAPE))
+            results_check.update({"host_double_sum": host_sum, "host_max": host_max,
+                                  "agrees_with_unsharded_host": bool(abs(float(s.item()) - host_sum) <= tol * abs(host_sum)
+                                                                     and float(m.item()) == host_max)})
+            del a_full, b_full, o
 
     # ---- per-operator durations: the same steps launched directly with CUDA events between the
     # operators (events cannot be read inside a graph replay)
