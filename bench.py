@@ -354,6 +354,21 @@ def per_op_sweep(torch, F, device, peak):
     del a, b
     yp = torch.empty(256, 160, 58, 58, device=device)
     bench("pad_1_1_1_1[256,160,56,56]", lambda: F.pad(y, [1, 1, 1, 1], 0.0, out=yp), 4 * (y.numel() + yp.numel()))
+    del yp
+    idx = torch.arange(0, 160, 2, device=device, dtype=torch.int32)
+    yg = torch.empty(256, 80, 56, 56, device=device)
+    bench("gather_axis1_every_2nd[256,160,56,56]", lambda: F.gather(y, idx, 1, out=yg), 8 * yg.numel())
+    del y, yg
+    x = torch.randn(256, 64, 112, 112, device=device)
+    y = torch.empty(256, 64, 56, 56, device=device)
+    bench("pooling_max_k2_s2[256,64,112,112]", lambda: F.pooling(x, 0, [2], [2], [0], out=y), 4 * (x.numel() + y.numel()))
+    bench("pooling_max_k3_s2_p1[256,64,112,112]", lambda: F.pooling(x, 0, [3], [2], [1], full_pooling=False, out=y),
+          4 * (x.numel() + y.numel()))
+    bench("pooling_avg_k2_s2[256,64,112,112]", lambda: F.pooling(x, 1, [2], [2], [0], out=y), 4 * (x.numel() + y.numel()))
+    del x, y
+    x = torch.randn(1024, 2048, 7, 7, device=device)
+    y = torch.empty(1024, 2048, 1, 1, device=device)
+    bench("pooling_avg_global[1024,2048,7,7]", lambda: F.pooling(x, 1, global_pooling=True, out=y), 4 * (x.numel() + y.numel()))
     return rows
 
 

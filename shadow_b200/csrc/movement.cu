@@ -276,6 +276,33 @@ gather_kernel(const float* __restrict__ x, const int* __restrict__ indexes, floa
   y[i] = (gi >= 0 && gi < gather_dim) ? __ldg(x + (o * gather_dim + gi) * inner + col) : 0.f;
 }
 
+// The same with 128-bit accesses (inner a multiple of 4, 16-byte aligned bases): a thread moves kGatherU
+// float4, all loads issued before the first store.  count4 = outer * num_indexes * inner / 4 < 2^32.
+constexpr int kGatherU = 4;
+__global__ void __launch_bounds__(kThreads)
+gather_vec_kernel(const float4* __restrict__ x, const int* __restrict__ indexes, float4* y, uint32_t count4, uint32_t num_indexes,
+                  int64_t gather_dim, uint32_t inner4, FastDiv32 div_inner4, FastDiv32 div_num) {
+  const int64_t first = static_cast<int64_t>(blockIdx.x) * (kThreads * kGatherU) + threadIdx.x;
+  float4 v[kGatherU];
+#pragma unroll
+  for (int u = 0; u < kGatherU; ++u) {
+    const int64_t i = first + u * kThreads;
+    if (i < count4) {
+      uint32_t r, col, o, which;
+      div_inner4.divmod(static_cast<uint32_t>(i), r, col);
+      div_num.divmod(r, o, which);
+      const int64_t gi = __ldg(indexes + which);
+      v[u] = make_float4(0.f, 0.f, 0.f, 0.f);   // an index outside [0, gather_dim) yields 0, as in the scalar kernel
+      if (gi >= 0 && gi < gather_dim) v[u] = ld_stream(x + (static_cast<int64_t>(o) * gather_dim + gi) * inner4 + col);
+    }
+  }
+#pragma unroll
+  for (int u = 0; u < kGatherU; ++u) {
+    const int64_t i = first + u * kThreads;
+    if (i < count4) st_stream(y + i, v[u]);
+  }
+}
+
 // A thread owns up to kPadRun consecutive columns of one output row: one index decode per thread
 // (by high multiplies: rows < 2^32 is checked by the caller), then plain coalesced 4-byte accesses.
 constexpr int kPadRun = 4;
@@ -477,6 +504,14 @@ int sb200_gather(const float* x, const int* indexes, int64_t num_indexes, int64_
     return SB200_ERR_BAD_ARGUMENT;
   if (outer * num_indexes > (1ll << 40) / inner || outer * gather_dim > (1ll << 40) / inner) return SB200_ERR_UNSUPPORTED;
   const int64_t count = outer * num_indexes * inner;
+  if ((inner & 3) == 0 && aligned16(x) && aligned16(y) && count / 4 < (1ll << 32) && num_indexes < (1ll << 32)) {
+    const int64_t count4 = count / 4, per_block = kThreads * kGatherU;
+    gather_vec_kernel<<<static_cast<unsigned>((count4 + per_block - 1) / per_block), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(
+        reinterpret_cast<const float4*>(x), indexes, reinterpret_cast<float4*>(y), static_cast<uint32_t>(count4),
+        static_cast<uint32_t>(num_indexes), gather_dim, static_cast<uint32_t>(inner / 4),
+        FastDiv32(static_cast<uint32_t>(inner / 4)), FastDiv32(static_cast<uint32_t>(num_indexes)));
+    return after_launch("sb200_gather");
+  }
   const int64_t blocks = (count + kThreads - 1) / kThreads;
   if (blocks >= (1ll << 31)) return SB200_ERR_UNSUPPORTED;
   const FastDiv32 div_inner(static_cast<uint32_t>(inner < (1ll << 32) ? inner : 1));

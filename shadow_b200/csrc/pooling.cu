@@ -4,8 +4,13 @@
 // min(start + kernel, in + pad); the average divides by the size of that window BEFORE it is
 // clipped to the tensor (padding counts), the maximum starts from the lowest float.
 //   small windows (<= 64 elements, the usual 2x2 / 3x3 case): one thread per output walks its
-//       window in the reference's order (d, then h, then w), so the float sum is bit-identical;
-//       neighbouring threads read neighbouring windows, the overlap is served by L1/L2;
+//       window in the reference's order (d, then h, then w), so the float sum is bit-identical.
+//       2-D: the input rows a block needs are ONE contiguous range of the tensor (a band of rows of
+//       one plane, or several whole planes when planes are small); the block brings it into shared
+//       memory with 16-byte asynchronous copies (coalesced, no register staging) and the windows
+//       are read from there, so global memory sees 128-bit accesses only and every output store is
+//       coalesced (pool_smem_kernel).  3-D, bands wider than the shared-memory budget and
+//       misaligned bases: windows read through L1/L2 (pool_thread_kernel);
 //   large windows (global pooling): one warp per output, lanes stride over the window and merge
 //       by shuffles; the sum is accumulated in double (the reference adds floats one by one, so
 //       the average matches it to the reduction tolerance, the maximum exactly).
@@ -76,6 +81,161 @@ pool_thread_kernel(const float* __restrict__ x, float* y, uint32_t count, const 
   y[i] = AVG ? __fdiv_rn(sum_val, static_cast<float>(w.pool_size)) : max_val;
 }
 
+// 2-D pooling from a shared-memory copy of the block's input range.
+// Block b = (group, band): planes [group*G, group*G + g) and output rows [band*TH, band*TH + rows) of
+// them (G > 1 only with whole planes: NB == 1, TH == out_h).  Its input is the contiguous float range
+// [in_start, in_end) of x; the copy starts at in_start rounded down to a multiple of 4 floats.
+struct PoolTile {
+  int G, TH, NB;          // planes per block, output rows per band, bands per plane
+  int64_t planes;
+  int64_t total_in;       // planes * in_h * in_w
+};
+
+// KH x KW > 0: the window extents as compile-time constants (must equal g.k_h, g.k_w) - windows that
+// lie inside the tensor take an unrolled path without bounds checks; KH == 0: run-time loops.
+template <bool AVG, int KH, int KW>
+__global__ void __launch_bounds__(kThreads)
+pool_smem_kernel(const float* __restrict__ x, float* y, const __grid_constant__ PoolGeom g, const __grid_constant__ PoolTile q) {
+  extern __shared__ __align__(16) float pool_sm[];
+  const int t = threadIdx.x;
+  const int64_t group = blockIdx.x / q.NB;
+  const int band = static_cast<int>(blockIdx.x - group * q.NB);
+  const int64_t p0 = group * q.G;
+  const int n_planes = static_cast<int>((q.planes - p0) < q.G ? (q.planes - p0) : q.G);
+  const int oh0 = band * q.TH;
+  const int rows = (q.G > 1) ? n_planes * g.out_h : min(q.TH, g.out_h - oh0);
+  const int plane_in = g.in_h * g.in_w;   // fits an int: a block's input fits shared memory or is one band of a plane < 2^31
+  int h_lo = 0, h_hi = g.in_h;
+  if (q.G == 1) {
+    h_lo = max(oh0 * g.s_h - g.p_h, 0);
+    h_hi = min(min((oh0 + rows - 1) * g.s_h - g.p_h + g.k_h, g.in_h + g.p_h), g.in_h);
+    h_hi = max(h_hi, h_lo);
+  }
+  const int64_t in_start = p0 * plane_in + static_cast<int64_t>(h_lo) * g.in_w;
+  const int64_t in_end = (q.G > 1) ? (p0 + n_planes) * plane_in : p0 * plane_in + static_cast<int64_t>(h_hi) * g.in_w;
+  const int64_t a0 = in_start & ~static_cast<int64_t>(3);
+  const int shift = static_cast<int>(in_start - a0);
+  // whole float4 that lie inside the tensor; what is left of the range (at most 3 floats) by scalar loads
+  int64_t vec_end = (in_end + 3) & ~static_cast<int64_t>(3);
+  const int64_t tensor_vec_end = q.total_in & ~static_cast<int64_t>(3);
+  if (vec_end > tensor_vec_end) vec_end = tensor_vec_end;
+  const int n_vec = vec_end > a0 ? static_cast<int>((vec_end - a0) >> 2) : 0;
+  const uint32_t sm_addr = static_cast<uint32_t>(__cvta_generic_to_shared(pool_sm));
+  const float4* src = reinterpret_cast<const float4*>(x + a0);
+  for (int j = t; j < n_vec; j += kThreads) cp_async16(sm_addr + 16u * j, src + j);
+  cp_async_commit();
+  const int n_in = static_cast<int>(in_end - a0);
+  for (int i = 4 * n_vec + t; i < n_in; i += kThreads) pool_sm[i] = __ldg(x + a0 + i);
+  cp_async_wait<0>();
+  __syncthreads();
+
+  const int n_out = rows * g.out_w;
+  float* yb = y + (p0 * g.out_h + oh0) * static_cast<int64_t>(g.out_w);
+  // local output o = row * out_w + ow, walked with a stride of kThreads without a division per output
+  uint32_t row, ow;
+  g.div_w.divmod(static_cast<uint32_t>(t), row, ow);
+  const uint32_t d_row = g.div_w.div(kThreads), d_ow = kThreads - d_row * g.out_w;
+  const int origin = shift - h_lo * g.in_w;   // index in pool_sm of element (row 0, column 0) of the block's first plane
+  const int in_w = g.in_w, in_h = g.in_h;
+  for (int o = t; o < n_out; o += kThreads) {
+    uint32_t pl = 0, oh = static_cast<uint32_t>(oh0) + row;
+    if (q.G > 1) g.div_h.divmod(row, pl, oh);
+    const int hs = static_cast<int>(oh) * g.s_h - g.p_h, ws = static_cast<int>(ow) * g.s_w - g.p_w;
+    const int off = origin + static_cast<int>(pl) * plane_in;
+    float max_val = -FLT_MAX, sum_val = 0.f;
+    int pool_size;
+    if (KH > 0 && hs >= 0 && hs + KH <= in_h && ws >= 0 && ws + KW <= in_w) {
+      const float* rp = pool_sm + (off + hs * in_w + ws);
+      float v[KH > 0 ? KH * KW : 1];
+#pragma unroll
+      for (int i = 0; i < KH; ++i)
+#pragma unroll
+        for (int j = 0; j < KW; ++j) v[i * KW + j] = rp[i * in_w + j];
+#pragma unroll
+      for (int e = 0; e < KH * KW; ++e) {
+        if (AVG) sum_val = __fadd_rn(sum_val, v[e]);
+        else max_val = std_max(max_val, v[e]);
+      }
+      pool_size = KH * KW;
+    } else if (KH > 0) {
+      // a window that hangs over an edge: the same unrolled walk with one predicate per row and per column
+      // (an element outside the tensor is skipped; windows never reach beyond the padding's far side
+      // without also leaving the tensor, so "inside the tensor" is the only test the elements need)
+      const int rbase = off + hs * in_w + ws;
+      bool col_ok[KW > 0 ? KW : 1];
+#pragma unroll
+      for (int j = 0; j < KW; ++j) col_ok[j] = static_cast<unsigned>(ws + j) < static_cast<unsigned>(in_w);
+#pragma unroll
+      for (int i = 0; i < KH; ++i) {
+        const bool row_ok = static_cast<unsigned>(hs + i) < static_cast<unsigned>(in_h);
+#pragma unroll
+        for (int j = 0; j < KW; ++j) {
+          if (row_ok && col_ok[j]) {
+            const float v = pool_sm[rbase + i * in_w + j];
+            if (AVG) sum_val = __fadd_rn(sum_val, v);
+            else max_val = std_max(max_val, v);
+          }
+        }
+      }
+      pool_size = (min(hs + KH, in_h + g.p_h) - hs) * (min(ws + KW, in_w + g.p_w) - ws);
+    } else {
+      const int he = min(hs + g.k_h, in_h + g.p_h), we = min(ws + g.k_w, in_w + g.p_w);
+      const int h0 = max(hs, 0), h1 = min(he, in_h), w0 = max(ws, 0), w1 = min(we, in_w);
+      for (int ph = h0; ph < h1; ++ph) {
+        const int ro = off + ph * in_w;
+        for (int pw = w0; pw < w1; ++pw) {
+          const float v = pool_sm[ro + pw];
+          if (AVG) sum_val = __fadd_rn(sum_val, v);
+          else max_val = std_max(max_val, v);
+        }
+      }
+      pool_size = (he - hs) * (we - ws);
+    }
+    st_stream(yb + o, AVG ? __fdiv_rn(sum_val, static_cast<float>(pool_size)) : max_val);
+    ow += d_ow;
+    row += d_row;
+    if (ow >= static_cast<uint32_t>(g.out_w)) ow -= g.out_w, ++row;
+  }
+}
+
+// Shared-memory budget of one pool_smem_kernel block: eight 256-thread blocks per SM keep 190 KB in flight.
+constexpr int kPoolSmemBudget = 24 * 1024;
+constexpr int kPoolSmemMax = 47 * 1024;
+
+// Chooses planes per block or rows per band; false when one output row's input does not fit.
+inline bool plan_pool_tile(const PoolGeom& g, int64_t planes, PoolTile& q, int& smem_bytes) {
+  const int64_t plane_bytes = static_cast<int64_t>(g.in_h) * g.in_w * 4;
+  if (plane_bytes >= (1ll << 32)) return false;   // the kernel indexes a plane with an int
+  q.planes = planes;
+  q.total_in = planes * g.in_h * g.in_w;
+  int64_t in_floats;
+  if (plane_bytes * 2 <= kPoolSmemBudget) {
+    q.G = static_cast<int>(kPoolSmemBudget / plane_bytes);
+    if (q.G > planes) q.G = static_cast<int>(planes);
+    q.NB = 1, q.TH = g.out_h;
+    in_floats = static_cast<int64_t>(q.G) * g.in_h * g.in_w;
+    if (static_cast<int64_t>(q.G) * g.out_h * g.out_w >= (1ll << 30)) return false;
+  } else {
+    q.G = 1;
+    const int64_t row_bytes = static_cast<int64_t>(g.in_w) * 4;
+    // input rows of a band of th output rows: (th - 1) * s_h + k_h
+    int64_t th = (kPoolSmemBudget / row_bytes - g.k_h) / g.s_h + 1;
+    if (kPoolSmemBudget / row_bytes < g.k_h) th = 1;
+    if (th > g.out_h) th = g.out_h;
+    q.NB = static_cast<int>((g.out_h + th - 1) / th);
+    q.TH = (g.out_h + q.NB - 1) / q.NB;
+    q.NB = (g.out_h + q.TH - 1) / q.TH;
+    int64_t in_rows = static_cast<int64_t>(q.TH - 1) * g.s_h + g.k_h;
+    if (in_rows > g.in_h) in_rows = g.in_h;
+    in_floats = in_rows * g.in_w;
+  }
+  const int64_t bytes = (in_floats + 8) * 4;
+  if (bytes > kPoolSmemMax) return false;
+  smem_bytes = static_cast<int>(bytes);
+  const int64_t blocks = ((planes + q.G - 1) / q.G) * q.NB;
+  return blocks < (1ll << 31);
+}
+
 template <bool AVG>
 __global__ void __launch_bounds__(kThreads)
 pool_warp_kernel(const float* __restrict__ x, float* y, uint32_t count, const __grid_constant__ PoolGeom g) {
@@ -137,7 +297,22 @@ extern "C" int sb200_pooling(const float* x, float* y, int64_t planes, const int
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int64_t window = static_cast<int64_t>(kernel[0]) * kernel[1] * kernel[2];
   const uint32_t n = static_cast<uint32_t>(count);
-  if (window <= 64) {
+  PoolTile q;
+  int smem_bytes = 0;
+  if (window <= 64 && g.in_d == 1 && g.out_d == 1 && g.k_d == 1 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 &&
+      plan_pool_tile(g, planes, q, smem_bytes)) {
+    const unsigned blocks = static_cast<unsigned>(((planes + q.G - 1) / q.G) * q.NB);
+    const bool avg = pool_type == 1;
+#define SB200_POOL(KH, KW)                                                                                     \
+  do {                                                                                                         \
+    if (avg) pool_smem_kernel<true, KH, KW><<<blocks, kThreads, smem_bytes, s>>>(x, y, g, q);                  \
+    else pool_smem_kernel<false, KH, KW><<<blocks, kThreads, smem_bytes, s>>>(x, y, g, q);                     \
+  } while (0)
+    if (g.k_h == 2 && g.k_w == 2) SB200_POOL(2, 2);
+    else if (g.k_h == 3 && g.k_w == 3) SB200_POOL(3, 3);
+    else SB200_POOL(0, 0);
+#undef SB200_POOL
+  } else if (window <= 64) {
     const unsigned blocks = static_cast<unsigned>((count + kThreads - 1) / kThreads);
     if (pool_type == 1) pool_thread_kernel<true><<<blocks, kThreads, 0, s>>>(x, y, n, g);
     else pool_thread_kernel<false><<<blocks, kThreads, 0, s>>>(x, y, n, g);

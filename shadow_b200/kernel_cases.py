@@ -154,6 +154,28 @@ def _cases(torch, F):
         y = torch.empty((64, 160, 58, 58), device=dev)
         return (lambda: F.pad(x, [1, 1, 1, 1], 0.0, out=y)), 4 * (x.numel() + y.numel())
     case("pad_border_1", "pad_vec_kernel", pad)
+
+    def gather():
+        x = normal((64, 160, 56, 56))
+        idx = torch.arange(0, 160, 2, device=dev, dtype=torch.int32)
+        y = torch.empty((64, 80, 56, 56), device=dev)
+        return (lambda: F.gather(x, idx, 1, out=y)), 8 * y.numel()
+    case("gather_every_2nd_channel", "gather_vec_kernel", gather)
+
+    def pooling(pool, kernel, stride, pad, full):
+        def make():
+            x = normal((64, 64, 112, 112))
+            y = torch.empty((64, 64, 56, 56), device=dev)
+            return (lambda: F.pooling(x, pool, [kernel], [stride], [pad], full_pooling=full, out=y)), 4 * (x.numel() + y.numel())
+        return make
+    case("pooling_max_k2_s2", "pool_smem_kernel", pooling(0, 2, 2, 0, True))
+    case("pooling_max_k3_s2_p1", "pool_smem_kernel", pooling(0, 3, 2, 1, False))
+
+    def pooling_global():
+        x = normal((512, 2048, 7, 7))
+        y = torch.empty((512, 2048, 1, 1), device=dev)
+        return (lambda: F.pooling(x, 1, global_pooling=True, out=y)), 4 * (x.numel() + y.numel())
+    case("pooling_avg_global_7x7", "pool_smem_kernel", pooling_global)
     return table
 
 

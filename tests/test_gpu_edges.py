@@ -296,3 +296,55 @@ def test_softmax_with_the_plane_resident_in_shared_memory(shape):
     case = {"name": "softmax_resident", "op": "Softmax", "args": {"axis": 1}, "inputs": [x]}
     want = cases.run_port(case)
     cases.assert_parity(case, got.cpu().numpy(), want)
+
+
+POOL_GEOMETRIES = [
+    # shape, pool, kernel, stride, pad, global, full
+    ((3, 5, 70, 66), 0, [3], [2], [1], False, False),      # bands of rows of one plane, halo rows shared by two bands
+    ((3, 5, 70, 66), 1, [3], [2], [1], False, True),       # ceil sizing: the last windows hang over the padded edge
+    ((2, 3, 61, 63), 1, [2], [2], [0], False, True),       # odd extents: clipped windows at the bottom and the right
+    ((2, 3, 61, 63), 0, [2, 3], [2, 1], [0, 1], False, False),
+    ((41, 50, 7, 7), 1, [], [1], [0], True, True),         # many small planes per block, input count not a multiple of 4
+    ((7, 33, 6, 10), 1, [3], [1], [1], False, True),       # planes per block does not divide the plane count
+    ((7, 33, 6, 10), 0, [3], [1], [1], False, True),
+    ((1, 2, 3, 1500), 0, [2], [1], [0], False, True),      # rows wider than a block's thread count
+    ((1, 1, 2, 4000), 1, [2, 4], [1, 3], [0, 2], False, True),   # one output row per band at the larger shared-memory size
+    ((2, 2, 40, 40), 0, [2], [3], [0], False, True),       # stride above the kernel: rows that no window reads
+    ((1, 1, 1, 1), 1, [1], [1], [0], False, True),
+]
+
+
+@pytest.mark.parametrize("geometry", POOL_GEOMETRIES, ids=lambda g: "x".join(str(d) for d in g[0]) + ("_avg" if g[1] else "_max"))
+@pytest.mark.parametrize("offset", [0, 1])
+def test_pooling_from_shared_memory_rows(geometry, offset):
+    """2-D pooling with the block's input range staged in shared memory (offset 0), and the same
+    geometries from a base that is not 16-byte aligned (offset 1: windows read through the caches).
+    Small windows add floats in the reference's order, so every result is bit-exact."""
+    from shadow_b200 import functional as F
+    shape, pool, kernel, stride, pad, global_pooling, full = geometry
+    x = cases.normal(7400 + shape[2] + shape[3], shape)
+    xv, _ = _view(x, offset)
+    want = orc.pooling(x, pool, kernel, stride, pad, global_pooling, full)
+    yv, ybuf = _view(np.zeros(want.shape, np.float32), 0)
+    got = F.pooling(xv, pool, kernel, stride, pad, global_pooling, full, out=yv)
+    _torch().cuda.synchronize()
+    assert orc.bit_equal(got.cpu().numpy(), want)
+    assert _guards_intact(ybuf, 0, want.size)
+
+
+@pytest.mark.parametrize("offset", [0, 2])
+def test_gather_with_vector_rows(offset):
+    """Gather whose inner extent is a multiple of 4: 128-bit moves from an aligned base, the 4-byte kernel
+    from a base that is not; repeated and out-of-order indexes, more float4 than one block moves."""
+    from shadow_b200 import functional as F
+    torch = _torch()
+    for shape, axis, idx in (((3, 10, 4, 8), 1, [9, 0, 0, 5, 3]), ((6, 40, 36), 0, [5, 5, 1]), ((2, 7, 1028), 1, [6, 0, 3, 3, 1, 2]),
+                             ((5, 12), 0, [4, 0])):
+        x = cases.normal(7500 + shape[1], shape)
+        xv, _ = _view(x, offset)
+        want = np.take(x, idx, axis=axis)
+        yv, ybuf = _view(np.zeros(want.shape, np.float32), offset)
+        got = F.gather(xv, torch.tensor(idx, dtype=torch.int32, device="cuda"), axis, out=yv)
+        torch.cuda.synchronize()
+        assert orc.bit_equal(got.cpu().numpy(), want), (shape, axis)
+        assert _guards_intact(ybuf, offset, want.size)
