@@ -81,19 +81,29 @@ pool_thread_kernel(const float* __restrict__ x, float* y, uint32_t count, const 
   y[i] = AVG ? __fdiv_rn(sum_val, static_cast<float>(w.pool_size)) : max_val;
 }
 
-// 2-D pooling from a shared-memory copy of the block's input range.
+// 2-D pooling from a shared-memory copy of the block's input.
 // Block b = (group, band): planes [group*G, group*G + g) and output rows [band*TH, band*TH + rows) of
-// them (G > 1 only with whole planes: NB == 1, TH == out_h).  Its input is the contiguous float range
-// [in_start, in_end) of x; the copy starts at in_start rounded down to a multiple of 4 floats.
+// them (G > 1 only with whole planes: NB == 1, TH == out_h).  Three layouts of the copy:
+//   kPoolFlat      the contiguous float range [in_start, in_end) of x as it lies in memory (the copy starts at
+//                  in_start rounded down to a multiple of 4 floats); windows that leave the tensor are clipped;
+//   kPoolFlatFree  the same when no window of the geometry leaves the tensor: no clipping code at all;
+//   kPoolPadded    one band of one plane (G == 1, in_w a multiple of 4) laid out WITH its padding: tile rows
+//                  of `pitch` floats, the tensor's columns starting at column `lead`, everything else holding
+//                  the neutral value (lowest float for max; +0 for the average, which leaves a float sum
+//                  unchanged bit for bit: the running sum starts at +0 and never becomes -0) - so every
+//                  window, also one over an edge, is the same unrolled walk without a test.
+enum { kPoolFlat = 0, kPoolFlatFree = 1, kPoolPadded = 2 };
 struct PoolTile {
   int G, TH, NB;          // planes per block, output rows per band, bands per plane
+  int pitch, lead;        // kPoolPadded: floats per tile row, tile column of tensor column 0 (both multiples of 4)
+  FastDiv32 div_w4;       // by in_w / 4
   int64_t planes;
   int64_t total_in;       // planes * in_h * in_w
 };
 
-// KH x KW > 0: the window extents as compile-time constants (must equal g.k_h, g.k_w) - windows that
-// lie inside the tensor take an unrolled path without bounds checks; KH == 0: run-time loops.
-template <bool AVG, int KH, int KW>
+// KH x KW > 0: the window extents as compile-time constants (must equal g.k_h, g.k_w): an unrolled walk
+// with all loads ahead of the arithmetic; KH == 0: run-time loops.
+template <bool AVG, int KH, int KW, int MODE>
 __global__ void __launch_bounds__(kThreads)
 pool_smem_kernel(const float* __restrict__ x, float* y, const __grid_constant__ PoolGeom g, const __grid_constant__ PoolTile q) {
   extern __shared__ __align__(16) float pool_sm[];
@@ -104,28 +114,50 @@ pool_smem_kernel(const float* __restrict__ x, float* y, const __grid_constant__ 
   const int n_planes = static_cast<int>((q.planes - p0) < q.G ? (q.planes - p0) : q.G);
   const int oh0 = band * q.TH;
   const int rows = (q.G > 1) ? n_planes * g.out_h : min(q.TH, g.out_h - oh0);
-  const int plane_in = g.in_h * g.in_w;   // fits an int: a block's input fits shared memory or is one band of a plane < 2^31
-  int h_lo = 0, h_hi = g.in_h;
-  if (q.G == 1) {
-    h_lo = max(oh0 * g.s_h - g.p_h, 0);
-    h_hi = min(min((oh0 + rows - 1) * g.s_h - g.p_h + g.k_h, g.in_h + g.p_h), g.in_h);
-    h_hi = max(h_hi, h_lo);
-  }
-  const int64_t in_start = p0 * plane_in + static_cast<int64_t>(h_lo) * g.in_w;
-  const int64_t in_end = (q.G > 1) ? (p0 + n_planes) * plane_in : p0 * plane_in + static_cast<int64_t>(h_hi) * g.in_w;
-  const int64_t a0 = in_start & ~static_cast<int64_t>(3);
-  const int shift = static_cast<int>(in_start - a0);
-  // whole float4 that lie inside the tensor; what is left of the range (at most 3 floats) by scalar loads
-  int64_t vec_end = (in_end + 3) & ~static_cast<int64_t>(3);
-  const int64_t tensor_vec_end = q.total_in & ~static_cast<int64_t>(3);
-  if (vec_end > tensor_vec_end) vec_end = tensor_vec_end;
-  const int n_vec = vec_end > a0 ? static_cast<int>((vec_end - a0) >> 2) : 0;
+  const int plane_in = g.in_h * g.in_w;   // fits an int (checked by the planner)
+  const int in_w = g.in_w, in_h = g.in_h;
   const uint32_t sm_addr = static_cast<uint32_t>(__cvta_generic_to_shared(pool_sm));
-  const float4* src = reinterpret_cast<const float4*>(x + a0);
-  for (int j = t; j < n_vec; j += kThreads) cp_async16(sm_addr + 16u * j, src + j);
-  cp_async_commit();
-  const int n_in = static_cast<int>(in_end - a0);
-  for (int i = 4 * n_vec + t; i < n_in; i += kThreads) pool_sm[i] = __ldg(x + a0 + i);
+  int origin;      // kPoolFlat*: index in pool_sm of element (0, 0) of the block's first plane
+  if (MODE == kPoolPadded) {
+    const int tile_rows = (rows - 1) * g.s_h + g.k_h, h_first = oh0 * g.s_h - g.p_h;
+    const float neutral = AVG ? 0.f : -FLT_MAX;
+    const float4 fill = make_float4(neutral, neutral, neutral, neutral);
+    const int n_fill = (tile_rows * q.pitch) >> 2;
+    for (int j = t; j < n_fill; j += kThreads) reinterpret_cast<float4*>(pool_sm)[j] = fill;
+    __syncthreads();
+    const int hr0 = max(h_first, 0), hr1 = min(h_first + tile_rows, in_h);
+    const int w4 = in_w >> 2, n_vec = max(hr1 - hr0, 0) * w4;
+    const float4* src = reinterpret_cast<const float4*>(x + p0 * plane_in + static_cast<int64_t>(hr0) * in_w);
+    const uint32_t dst0 = sm_addr + 4u * static_cast<uint32_t>((hr0 - h_first) * q.pitch + q.lead);
+    for (int j = t; j < n_vec; j += kThreads) {
+      uint32_t r, c4;
+      q.div_w4.divmod(static_cast<uint32_t>(j), r, c4);
+      cp_async16(dst0 + 4u * (r * q.pitch) + 16u * c4, src + j);
+    }
+    cp_async_commit();
+    origin = 0;
+  } else {
+    int h_lo = 0, h_hi = in_h;
+    if (q.G == 1) {
+      h_lo = max(oh0 * g.s_h - g.p_h, 0);
+      h_hi = min(min((oh0 + rows - 1) * g.s_h - g.p_h + g.k_h, in_h + g.p_h), in_h);
+      h_hi = max(h_hi, h_lo);
+    }
+    const int64_t in_start = p0 * plane_in + static_cast<int64_t>(h_lo) * in_w;
+    const int64_t in_end = (q.G > 1) ? (p0 + n_planes) * plane_in : p0 * plane_in + static_cast<int64_t>(h_hi) * in_w;
+    const int64_t a0 = in_start & ~static_cast<int64_t>(3);
+    // whole float4 that lie inside the tensor; what is left of the range (at most 3 floats) by scalar loads
+    int64_t vec_end = (in_end + 3) & ~static_cast<int64_t>(3);
+    const int64_t tensor_vec_end = q.total_in & ~static_cast<int64_t>(3);
+    if (vec_end > tensor_vec_end) vec_end = tensor_vec_end;
+    const int n_vec = vec_end > a0 ? static_cast<int>((vec_end - a0) >> 2) : 0;
+    const float4* src = reinterpret_cast<const float4*>(x + a0);
+    for (int j = t; j < n_vec; j += kThreads) cp_async16(sm_addr + 16u * j, src + j);
+    cp_async_commit();
+    const int n_in = static_cast<int>(in_end - a0);
+    for (int i = 4 * n_vec + t; i < n_in; i += kThreads) pool_sm[i] = __ldg(x + a0 + i);
+    origin = static_cast<int>(in_start - a0) - h_lo * in_w;
+  }
   cp_async_wait<0>();
   __syncthreads();
 
@@ -135,32 +167,33 @@ pool_smem_kernel(const float* __restrict__ x, float* y, const __grid_constant__ 
   uint32_t row, ow;
   g.div_w.divmod(static_cast<uint32_t>(t), row, ow);
   const uint32_t d_row = g.div_w.div(kThreads), d_ow = kThreads - d_row * g.out_w;
-  const int origin = shift - h_lo * g.in_w;   // index in pool_sm of element (row 0, column 0) of the block's first plane
-  const int in_w = g.in_w, in_h = g.in_h;
+  // row stride of the copy, and what to add to hs * stride + ws to reach the window's first element
+  const int stride = (MODE == kPoolPadded) ? q.pitch : in_w;
+  const int first = (MODE == kPoolPadded) ? (g.p_h - oh0 * g.s_h) * q.pitch + q.lead : origin;
   for (int o = t; o < n_out; o += kThreads) {
     uint32_t pl = 0, oh = static_cast<uint32_t>(oh0) + row;
     if (q.G > 1) g.div_h.divmod(row, pl, oh);
     const int hs = static_cast<int>(oh) * g.s_h - g.p_h, ws = static_cast<int>(ow) * g.s_w - g.p_w;
-    const int off = origin + static_cast<int>(pl) * plane_in;
+    const int off = first + static_cast<int>(pl) * plane_in;
     float max_val = -FLT_MAX, sum_val = 0.f;
-    int pool_size;
-    if (KH > 0 && hs >= 0 && hs + KH <= in_h && ws >= 0 && ws + KW <= in_w) {
-      const float* rp = pool_sm + (off + hs * in_w + ws);
+    int pool_size = KH * KW;
+    const bool whole = MODE != kPoolFlat || (hs >= 0 && hs + KH <= in_h && ws >= 0 && ws + KW <= in_w);
+    if (MODE != kPoolFlatFree && AVG) pool_size = (min(hs + g.k_h, in_h + g.p_h) - hs) * (min(ws + g.k_w, in_w + g.p_w) - ws);
+    if (KH > 0 && whole) {
+      const float* rp = pool_sm + (off + hs * stride + ws);
       float v[KH > 0 ? KH * KW : 1];
 #pragma unroll
       for (int i = 0; i < KH; ++i)
 #pragma unroll
-        for (int j = 0; j < KW; ++j) v[i * KW + j] = rp[i * in_w + j];
+        for (int j = 0; j < KW; ++j) v[i * KW + j] = rp[i * stride + j];
 #pragma unroll
       for (int e = 0; e < KH * KW; ++e) {
         if (AVG) sum_val = __fadd_rn(sum_val, v[e]);
         else max_val = std_max(max_val, v[e]);
       }
-      pool_size = KH * KW;
     } else if (KH > 0) {
-      // a window that hangs over an edge: the same unrolled walk with one predicate per row and per column
-      // (an element outside the tensor is skipped; windows never reach beyond the padding's far side
-      // without also leaving the tensor, so "inside the tensor" is the only test the elements need)
+      // kPoolFlat, a window over an edge: the same unrolled walk with one predicate per row and per column
+      // (an element is taken exactly when it lies inside the tensor)
       const int rbase = off + hs * in_w + ws;
       bool col_ok[KW > 0 ? KW : 1];
 #pragma unroll
@@ -177,19 +210,18 @@ pool_smem_kernel(const float* __restrict__ x, float* y, const __grid_constant__ 
           }
         }
       }
-      pool_size = (min(hs + KH, in_h + g.p_h) - hs) * (min(ws + KW, in_w + g.p_w) - ws);
     } else {
-      const int he = min(hs + g.k_h, in_h + g.p_h), we = min(ws + g.k_w, in_w + g.p_w);
-      const int h0 = max(hs, 0), h1 = min(he, in_h), w0 = max(ws, 0), w1 = min(we, in_w);
+      int h0 = hs, h1 = hs + g.k_h, w0 = ws, w1 = ws + g.k_w;
+      if (MODE == kPoolFlat) h0 = max(h0, 0), h1 = min(h1, in_h), w0 = max(w0, 0), w1 = min(w1, in_w);
+      if (MODE == kPoolFlatFree) pool_size = g.k_h * g.k_w;
       for (int ph = h0; ph < h1; ++ph) {
-        const int ro = off + ph * in_w;
+        const int ro = off + ph * stride;
         for (int pw = w0; pw < w1; ++pw) {
           const float v = pool_sm[ro + pw];
           if (AVG) sum_val = __fadd_rn(sum_val, v);
           else max_val = std_max(max_val, v);
         }
       }
-      pool_size = (he - hs) * (we - ws);
     }
     st_stream(yb + o, AVG ? __fdiv_rn(sum_val, static_cast<float>(pool_size)) : max_val);
     ow += d_ow;
@@ -202,22 +234,38 @@ pool_smem_kernel(const float* __restrict__ x, float* y, const __grid_constant__ 
 constexpr int kPoolSmemBudget = 24 * 1024;
 constexpr int kPoolSmemMax = 47 * 1024;
 
-// Chooses planes per block or rows per band; false when one output row's input does not fit.
-inline bool plan_pool_tile(const PoolGeom& g, int64_t planes, PoolTile& q, int& smem_bytes) {
+// Chooses the layout and planes per block or rows per band; false when one output row's input does not fit.
+inline bool plan_pool_tile(const PoolGeom& g, int64_t planes, PoolTile& q, int& mode, int& smem_bytes) {
   const int64_t plane_bytes = static_cast<int64_t>(g.in_h) * g.in_w * 4;
   if (plane_bytes >= (1ll << 32)) return false;   // the kernel indexes a plane with an int
   q.planes = planes;
   q.total_in = planes * g.in_h * g.in_w;
-  int64_t in_floats;
+  q.pitch = q.lead = 0;
+  q.div_w4 = FastDiv32(static_cast<uint32_t>(g.in_w / 4 > 0 ? g.in_w / 4 : 1));
+  // exclusive end, in tensor coordinates, of the last window along each axis before clipping
+  const int64_t reach_h = static_cast<int64_t>(g.out_h - 1) * g.s_h - g.p_h + g.k_h;
+  const int64_t reach_w = static_cast<int64_t>(g.out_w - 1) * g.s_w - g.p_w + g.k_w;
+  const bool all_inside = g.p_h == 0 && g.p_w == 0 && reach_h <= g.in_h && reach_w <= g.in_w;
+  mode = all_inside ? kPoolFlatFree : kPoolFlat;
+  int64_t bytes;
   if (plane_bytes * 2 <= kPoolSmemBudget) {
     q.G = static_cast<int>(kPoolSmemBudget / plane_bytes);
     if (q.G > planes) q.G = static_cast<int>(planes);
     q.NB = 1, q.TH = g.out_h;
-    in_floats = static_cast<int64_t>(q.G) * g.in_h * g.in_w;
     if (static_cast<int64_t>(q.G) * g.out_h * g.out_w >= (1ll << 30)) return false;
+    bytes = (static_cast<int64_t>(q.G) * g.in_h * g.in_w + 8) * 4;
   } else {
     q.G = 1;
-    const int64_t row_bytes = static_cast<int64_t>(g.in_w) * 4;
+    int64_t row_floats = g.in_w;
+    if (!all_inside && (g.in_w & 3) == 0) {
+      mode = kPoolPadded;
+      q.lead = (g.p_w + 3) & ~3;
+      const int64_t pitch = (q.lead + (reach_w > g.in_w ? reach_w : g.in_w) + 3) & ~static_cast<int64_t>(3);
+      if (pitch >= (1 << 20)) return false;
+      q.pitch = static_cast<int>(pitch);
+      row_floats = pitch;
+    }
+    const int64_t row_bytes = row_floats * 4;
     // input rows of a band of th output rows: (th - 1) * s_h + k_h
     int64_t th = (kPoolSmemBudget / row_bytes - g.k_h) / g.s_h + 1;
     if (kPoolSmemBudget / row_bytes < g.k_h) th = 1;
@@ -226,10 +274,9 @@ inline bool plan_pool_tile(const PoolGeom& g, int64_t planes, PoolTile& q, int& 
     q.TH = (g.out_h + q.NB - 1) / q.NB;
     q.NB = (g.out_h + q.TH - 1) / q.TH;
     int64_t in_rows = static_cast<int64_t>(q.TH - 1) * g.s_h + g.k_h;
-    if (in_rows > g.in_h) in_rows = g.in_h;
-    in_floats = in_rows * g.in_w;
+    if (mode != kPoolPadded && in_rows > g.in_h) in_rows = g.in_h;
+    bytes = (in_rows * row_floats + 8) * 4;
   }
-  const int64_t bytes = (in_floats + 8) * 4;
   if (bytes > kPoolSmemMax) return false;
   smem_bytes = static_cast<int>(bytes);
   const int64_t blocks = ((planes + q.G - 1) / q.G) * q.NB;
@@ -298,20 +345,27 @@ extern "C" int sb200_pooling(const float* x, float* y, int64_t planes, const int
   const int64_t window = static_cast<int64_t>(kernel[0]) * kernel[1] * kernel[2];
   const uint32_t n = static_cast<uint32_t>(count);
   PoolTile q;
-  int smem_bytes = 0;
+  int smem_bytes = 0, mode = kPoolFlat;
   if (window <= 64 && g.in_d == 1 && g.out_d == 1 && g.k_d == 1 && (reinterpret_cast<uintptr_t>(x) & 15u) == 0 &&
-      plan_pool_tile(g, planes, q, smem_bytes)) {
+      plan_pool_tile(g, planes, q, mode, smem_bytes)) {
     const unsigned blocks = static_cast<unsigned>(((planes + q.G - 1) / q.G) * q.NB);
     const bool avg = pool_type == 1;
+#define SB200_POOL_M(KH, KW, MODE)                                                                             \
+  do {                                                                                                         \
+    if (avg) pool_smem_kernel<true, KH, KW, MODE><<<blocks, kThreads, smem_bytes, s>>>(x, y, g, q);            \
+    else pool_smem_kernel<false, KH, KW, MODE><<<blocks, kThreads, smem_bytes, s>>>(x, y, g, q);               \
+  } while (0)
 #define SB200_POOL(KH, KW)                                                                                     \
   do {                                                                                                         \
-    if (avg) pool_smem_kernel<true, KH, KW><<<blocks, kThreads, smem_bytes, s>>>(x, y, g, q);                  \
-    else pool_smem_kernel<false, KH, KW><<<blocks, kThreads, smem_bytes, s>>>(x, y, g, q);                     \
+    if (mode == kPoolPadded) SB200_POOL_M(KH, KW, kPoolPadded);                                                \
+    else if (mode == kPoolFlatFree) SB200_POOL_M(KH, KW, kPoolFlatFree);                                       \
+    else SB200_POOL_M(KH, KW, kPoolFlat);                                                                      \
   } while (0)
     if (g.k_h == 2 && g.k_w == 2) SB200_POOL(2, 2);
     else if (g.k_h == 3 && g.k_w == 3) SB200_POOL(3, 3);
     else SB200_POOL(0, 0);
 #undef SB200_POOL
+#undef SB200_POOL_M
   } else if (window <= 64) {
     const unsigned blocks = static_cast<unsigned>((count + kThreads - 1) / kThreads);
     if (pool_type == 1) pool_thread_kernel<true><<<blocks, kThreads, 0, s>>>(x, y, n, g);

@@ -311,6 +311,16 @@ POOL_GEOMETRIES = [
     ((1, 1, 2, 4000), 1, [2, 4], [1, 3], [0, 2], False, True),   # one output row per band at the larger shared-memory size
     ((2, 2, 40, 40), 0, [2], [3], [0], False, True),       # stride above the kernel: rows that no window reads
     ((1, 1, 1, 1), 1, [1], [1], [0], False, True),
+    # planes above 12 KB whose width is a multiple of 4, with padding or overhang: the copy is laid out with its padding
+    ((2, 3, 72, 64), 0, [3], [2], [1], False, False),
+    ((2, 3, 72, 64), 1, [3], [2], [1], False, True),
+    ((1, 2, 100, 68), 1, [2], [2], [1], False, True),
+    ((1, 2, 200, 64), 1, [3], [2], [1], False, True),      # three bands
+    ((1, 2, 200, 64), 0, [3], [2], [1], False, True),
+    ((1, 1, 150, 64), 0, [3], [1], [1], False, True),
+    ((1, 2, 80, 48), 1, [2, 5], [2, 3], [1, 2], False, True),   # run-time window loops over the padded copy
+    ((1, 2, 80, 48), 0, [2], [3], [0], False, True),       # no padding, but the last window hangs over the edge
+    ((2, 2, 64, 64), 1, [2], [2], [0], False, True),       # every window inside the tensor
 ]
 
 
