@@ -97,6 +97,7 @@ struct PoolTile {
   int G, TH, NB;          // planes per block, output rows per band, bands per plane
   int pitch, lead;        // kPoolPadded: floats per tile row, tile column of tensor column 0 (both multiples of 4)
   FastDiv32 div_w4;       // by in_w / 4
+  FastDiv32 div_nb;       // by NB
   int64_t planes;
   int64_t total_in;       // planes * in_h * in_w
 };
@@ -108,9 +109,10 @@ __global__ void __launch_bounds__(kThreads)
 pool_smem_kernel(const float* __restrict__ x, float* y, const __grid_constant__ PoolGeom g, const __grid_constant__ PoolTile q) {
   extern __shared__ __align__(16) float pool_sm[];
   const int t = threadIdx.x;
-  const int64_t group = blockIdx.x / q.NB;
-  const int band = static_cast<int>(blockIdx.x - group * q.NB);
-  const int64_t p0 = group * q.G;
+  uint32_t group, band_u;
+  q.div_nb.divmod(blockIdx.x, group, band_u);
+  const int band = static_cast<int>(band_u);
+  const int64_t p0 = static_cast<int64_t>(group) * q.G;
   const int n_planes = static_cast<int>((q.planes - p0) < q.G ? (q.planes - p0) : q.G);
   const int oh0 = band * q.TH;
   const int rows = (q.G > 1) ? n_planes * g.out_h : min(q.TH, g.out_h - oh0);
@@ -122,11 +124,19 @@ pool_smem_kernel(const float* __restrict__ x, float* y, const __grid_constant__ 
     const int tile_rows = (rows - 1) * g.s_h + g.k_h, h_first = oh0 * g.s_h - g.p_h;
     const float neutral = AVG ? 0.f : -FLT_MAX;
     const float4 fill = make_float4(neutral, neutral, neutral, neutral);
-    const int n_fill = (tile_rows * q.pitch) >> 2;
-    for (int j = t; j < n_fill; j += kThreads) reinterpret_cast<float4*>(pool_sm)[j] = fill;
-    __syncthreads();
-    const int hr0 = max(h_first, 0), hr1 = min(h_first + tile_rows, in_h);
-    const int w4 = in_w >> 2, n_vec = max(hr1 - hr0, 0) * w4;
+    const int hr0 = max(h_first, 0), hr1 = max(min(h_first + tile_rows, in_h), hr0);
+    // neutral values where the copy below does not write: tile rows above and below the tensor's rows, and the
+    // columns left and right of the tensor's columns in the rows between (disjoint from the copy: no barrier)
+    float4* sm4 = reinterpret_cast<float4*>(pool_sm);
+    const int pitch4 = q.pitch >> 2, top4 = (hr0 - h_first) * pitch4, mid_end4 = (hr1 - h_first) * pitch4;
+    for (int j = t; j < top4; j += kThreads) sm4[j] = fill;
+    for (int j = mid_end4 + t; j < tile_rows * pitch4; j += kThreads) sm4[j] = fill;
+    const int left4 = q.lead >> 2, right0 = left4 + (in_w >> 2), side4 = left4 + (pitch4 - right0);
+    for (int j = t; j < (hr1 - hr0) * side4; j += kThreads) {   // a few cells per row: most threads skip this loop
+      const int r = j / side4, b = j - r * side4;
+      sm4[top4 + r * pitch4 + (b < left4 ? b : right0 + (b - left4))] = fill;
+    }
+    const int w4 = in_w >> 2, n_vec = (hr1 - hr0) * w4;
     const float4* src = reinterpret_cast<const float4*>(x + p0 * plane_in + static_cast<int64_t>(hr0) * in_w);
     const uint32_t dst0 = sm_addr + 4u * static_cast<uint32_t>((hr0 - h_first) * q.pitch + q.lead);
     for (int j = t; j < n_vec; j += kThreads) {
@@ -278,6 +288,7 @@ inline bool plan_pool_tile(const PoolGeom& g, int64_t planes, PoolTile& q, int& 
     bytes = (in_rows * row_floats + 8) * 4;
   }
   if (bytes > kPoolSmemMax) return false;
+  q.div_nb = FastDiv32(static_cast<uint32_t>(q.NB));
   smem_bytes = static_cast<int>(bytes);
   const int64_t blocks = ((planes + q.G - 1) / q.G) * q.NB;
   return blocks < (1ll << 31);
