@@ -321,6 +321,9 @@ POOL_GEOMETRIES = [
     ((1, 2, 80, 48), 1, [2, 5], [2, 3], [1, 2], False, True),   # run-time window loops over the padded copy
     ((1, 2, 80, 48), 0, [2], [3], [0], False, True),       # no padding, but the last window hangs over the edge
     ((2, 2, 64, 64), 1, [2], [2], [0], False, True),       # every window inside the tensor
+    ((1, 1, 3, 6000), 0, [3], [1], [1], False, True),      # one band needs 72 KB of shared memory (opted into per device)
+    ((1, 1, 3, 9000), 1, [3], [1], [1], False, True),      # and this one more than a block may have: windows through the caches
+    ((300, 2, 7, 7), 1, [], [1], [0], True, True),         # whole passes of 256 one-output planes, then a short last block
 ]
 
 
