@@ -259,12 +259,14 @@ struct UnaryFn {
     if (OP == SB200_SQRT) return __fsqrt_rn(x);
     if (OP == SB200_LOG) return logf(x);   // within 1 ulp of glibc's logf on every input
     if (OP == SB200_EXP) return expf_like_glibc(x);
-    if (OP == SB200_SIN) return static_cast<float>(sin(static_cast<double>(x)));
-    if (OP == SB200_COS) return static_cast<float>(cos(static_cast<double>(x)));
+    if (OP == SB200_SIN) return sinf(x);
+    if (OP == SB200_COS) return cosf(x);
+    // (CUDA's tanf is 3 ulp from glibc's on 55,858 of the 2^32 inputs - above the bar - so Tan stays in double;
+    // the float sin / cos / asin / acos / atan are within 2 ulp of glibc's on every input)
     if (OP == SB200_TAN) return static_cast<float>(tan(static_cast<double>(x)));
-    if (OP == SB200_ASIN) return static_cast<float>(asin(static_cast<double>(x)));
-    if (OP == SB200_ACOS) return static_cast<float>(acos(static_cast<double>(x)));
-    if (OP == SB200_ATAN) return static_cast<float>(atan(static_cast<double>(x)));
+    if (OP == SB200_ASIN) return asinf(x);
+    if (OP == SB200_ACOS) return acosf(x);
+    if (OP == SB200_ATAN) return atanf(x);
     if (OP == SB200_FLOOR) return floorf(x);
     if (OP == SB200_CEIL) return ceilf(x);
     if (OP == SB200_NEG) return -x;
@@ -288,9 +290,9 @@ struct ActivateFn {
     // for every normal result)
     if (TYPE == SB200_SIGMOID) return rcp_correct(__fadd_rn(1.f, expf_like_glibc(-x)));
     if (TYPE == SB200_SOFTPLUS) {
-      // log1pf(expf(x)): expf as glibc computes it, then log1p in double rounded once
-      float e = expf_like_glibc(x);
-      return static_cast<float>(log1p(static_cast<double>(e)));
+      // log1pf(expf(x)): expf as glibc computes it, then CUDA's float log1pf (documented to stay within 1 ulp of
+      // the true value, as glibc's does: at most 2 ulp between the two, checked on every float input)
+      return log1pf(expf_like_glibc(x));
     }
     if (TYPE == SB200_TANH) return tanh_accurate(x);
     if (TYPE == SB200_RELU6) return x < 0.f ? 0.f : (x > 6.f ? 6.f : x);

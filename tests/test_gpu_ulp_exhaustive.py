@@ -1,8 +1,8 @@
 """Every float bit pattern through the transcendental operators of the library as built.
 
-Exp and Log (`sb200_unary`), Sigmoid, SoftPlus and Tanh (`sb200_activate`) are run on the GPU over all
-2^32 float inputs (64 launches of 2^26 elements each) and compared on the host with the reference's
-own CPU arithmetic - glibc's expf / logf / tanhf and the compositions 1/(1+expf(-x)) and
+Exp, Log and the six trigonometric codes (`sb200_unary`), Sigmoid, SoftPlus and Tanh (`sb200_activate`) are run on
+the GPU over all 2^32 float inputs (64 launches of 2^26 elements each) and compared on the host with the reference's
+own CPU arithmetic - glibc's expf / logf / tanhf / sinf ... atanf and the compositions 1/(1+expf(-x)) and
 log1pf(expf(x)) of shadow/operators/kernels/activate.cpp:15-26 and shadow/core/blas.cpp:143-167 -
 evaluated by the oracle's C helper on all host threads.  The bar is the one the operators are built
 to: at most 2 ulp from the reference on EVERY input, NaN for NaN, no zero of the wrong sign.
@@ -35,6 +35,12 @@ FUNCTIONS = [
     ("Tanh", 4, ("activate", 5), 2),
     ("Reciprocal", 5, ("unary", 14), 0),
     ("Sqrt", 6, ("unary", 2), 0),
+    ("Sin", 7, ("unary", 5), 2),
+    ("Cos", 8, ("unary", 6), 2),
+    ("Tan", 9, ("unary", 7), 2),
+    ("Asin", 10, ("unary", 8), 2),
+    ("Acos", 11, ("unary", 9), 2),
+    ("Atan", 12, ("unary", 10), 2),
 ]
 
 
