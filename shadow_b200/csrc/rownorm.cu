@@ -72,6 +72,13 @@ __device__ __forceinline__ double row_sum(double v, double* red) {
   }
 }
 
+// The four terms of one float4, added as floats (pairwise) before they join the double accumulator: one
+// conversion and one double addition per float4 instead of four of each.  Each pre-sum is off by at most 2^-24
+// of its own size, far inside the tolerance a different addition order already needs (a float ulp of the mean).
+__device__ __forceinline__ double sum4_terms(float a, float b, float c, float d) {
+  return static_cast<double>(__fadd_rn(__fadd_rn(a, b), __fadd_rn(c, d)));
+}
+
 // Rows in registers.  VEC: units are float4 (inner % 4 == 0, aligned), else single floats.
 template <int TPR, int NV, bool VEC, int BLOCK>
 __global__ void __launch_bounds__(BLOCK)
@@ -96,8 +103,12 @@ rownorm_rows_kernel(const float* x, float* y, int64_t rows, int units_per_row, f
       } else {
         v[i][0] = ld_stream(x + row_off + u);
       }
+      if constexpr (W == 4) {
+        acc += sum4_terms(__fmul_rn(alpha, v[i][0]), __fmul_rn(alpha, v[i][1]), __fmul_rn(alpha, v[i][2]), __fmul_rn(alpha, v[i][3]));
+      } else {
 #pragma unroll
-      for (int e = 0; e < W; ++e) acc += static_cast<double>(__fmul_rn(alpha, v[i][e]));
+        for (int e = 0; e < W; ++e) acc += static_cast<double>(__fmul_rn(alpha, v[i][e]));
+      }
     }
   }
   const float mean = static_cast<float>(row_sum<TPR>(acc, red));
@@ -107,9 +118,13 @@ rownorm_rows_kernel(const float* x, float* y, int64_t rows, int units_per_row, f
     const int u = t + i * TPR;
     if (live && u < units_per_row) {
 #pragma unroll
-      for (int e = 0; e < W; ++e) {
-        v[i][e] = __fsub_rn(v[i][e], mean);
-        acc += static_cast<double>(__fmul_rn(alpha, __fmul_rn(v[i][e], v[i][e])));
+      for (int e = 0; e < W; ++e) v[i][e] = __fsub_rn(v[i][e], mean);
+      if constexpr (W == 4) {
+        acc += sum4_terms(__fmul_rn(alpha, __fmul_rn(v[i][0], v[i][0])), __fmul_rn(alpha, __fmul_rn(v[i][1], v[i][1])),
+                          __fmul_rn(alpha, __fmul_rn(v[i][2], v[i][2])), __fmul_rn(alpha, __fmul_rn(v[i][3], v[i][3])));
+      } else {
+#pragma unroll
+        for (int e = 0; e < W; ++e) acc += static_cast<double>(__fmul_rn(alpha, __fmul_rn(v[i][e], v[i][e])));
       }
     }
   }
@@ -264,16 +279,15 @@ rownorm_smem_rows_kernel(const float* x, float* y, int64_t rows, int units, floa
     double acc = 0.0;
     for (int u = threadIdx.x; u < units; u += T) {
       const float4 q = buf[u];
-      acc += static_cast<double>(__fmul_rn(alpha, q.x)), acc += static_cast<double>(__fmul_rn(alpha, q.y));
-      acc += static_cast<double>(__fmul_rn(alpha, q.z)), acc += static_cast<double>(__fmul_rn(alpha, q.w));
+      acc += sum4_terms(__fmul_rn(alpha, q.x), __fmul_rn(alpha, q.y), __fmul_rn(alpha, q.z), __fmul_rn(alpha, q.w));
     }
     const float mean = static_cast<float>(block_reduce(acc, OpAddD(), 0.0, red));
     acc = 0.0;
     for (int u = threadIdx.x; u < units; u += T) {
       const float4 q = buf[u];
       const float c0 = __fsub_rn(q.x, mean), c1 = __fsub_rn(q.y, mean), c2 = __fsub_rn(q.z, mean), c3 = __fsub_rn(q.w, mean);
-      acc += static_cast<double>(__fmul_rn(alpha, __fmul_rn(c0, c0))), acc += static_cast<double>(__fmul_rn(alpha, __fmul_rn(c1, c1)));
-      acc += static_cast<double>(__fmul_rn(alpha, __fmul_rn(c2, c2))), acc += static_cast<double>(__fmul_rn(alpha, __fmul_rn(c3, c3)));
+      acc += sum4_terms(__fmul_rn(alpha, __fmul_rn(c0, c0)), __fmul_rn(alpha, __fmul_rn(c1, c1)),
+                        __fmul_rn(alpha, __fmul_rn(c2, c2)), __fmul_rn(alpha, __fmul_rn(c3, c3)));
     }
     const float var = static_cast<float>(block_reduce(acc, OpAddD(), 0.0, red));
     const float d = __fsqrt_rn(__fadd_rn(var, eps));
