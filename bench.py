@@ -282,6 +282,13 @@ def per_op_sweep(torch, F, device, peak):
     for name, code in (("Add", 0), ("Mul", 2), ("Max", 5)):
         bench("binary_broadcast_%s[512,64,56,56]+[1,64,1,1]" % name, lambda: F.binary(a, b, code, out=y), 8 * n + 256)
     bench("binary_same_Add[512,64,56,56]", lambda: F.binary(a, c, 0, out=y), 12 * n)
+    bench("binary_scalar_Mul[512,64,56,56]", lambda: F.binary_scalar(a, 1.5, 2, out=y), 8 * n)
+    a.uniform_(0.5, 2.0)
+    c.uniform_(0.5, 2.0)
+    bench("binary_same_Div[512,64,56,56]", lambda: F.binary(a, c, 3, out=y), 12 * n)
+    bench("binary_same_Pow[512,64,56,56]", lambda: F.binary(a, c, 4, out=y), 12 * n)
+    a.uniform_(-1.0, 1.0)
+    c.uniform_(-1.0, 1.0)
     bench("eltwise_Sum_3_inputs[512,64,56,56]", lambda: F.eltwise([a, c, a], 1, [0.5, 0.25, 2.0], out=y), 16 * n)
     bench("eltwise_Max_2_inputs[512,64,56,56]", lambda: F.eltwise([a, c], 2, out=y), 12 * n)
     alpha = torch.randn(512, 64, device=device)
@@ -290,10 +297,18 @@ def per_op_sweep(torch, F, device, peak):
     c2 = (512, 256, 28, 28)
     x, y = torch.empty(c2, device=device).normal_(0, 2), torch.empty(c2, device=device)
     n = x.numel()
-    for name, code in (("Relu", 1), ("Leaky", 2), ("Sigmoid", 3), ("Tanh", 5)):
+    for name, code in (("Relu", 1), ("Leaky", 2), ("Sigmoid", 3), ("SoftPlus", 4), ("Tanh", 5), ("Relu6", 6), ("HardSwish", 7),
+                       ("Gelu", 8)):
         bench("activate_%s[512,256,28,28]" % name, lambda: F.activate(x, code, 0.1, out=y), 8 * n)
+    slopes = torch.rand(256, device=device) * 0.3
+    bench("activate_PRelu[512,256,28,28]", lambda: F.activate(x, 0, 0.1, slopes, out=y), 8 * n + 4 * 256)
     x.uniform_(-10, 10)
     bench("unary_Exp[512,256,28,28]", lambda: F.unary(x, 4, out=y), 8 * n)
+    for name, code in (("Abs", 0), ("Sin", 5), ("Cos", 6), ("Tan", 7), ("Atan", 10), ("Floor", 11), ("Reciprocal", 14)):
+        bench("unary_%s[512,256,28,28]" % name, lambda: F.unary(x, code, out=y), 8 * n)
+    x.uniform_(-1, 1)
+    for name, code in (("Asin", 8), ("Acos", 9)):
+        bench("unary_%s[512,256,28,28]" % name, lambda: F.unary(x, code, out=y), 8 * n)
     x.uniform_(0.01, 10)
     bench("unary_Log[512,256,28,28]", lambda: F.unary(x, 3, out=y), 8 * n)
     bench("unary_Sqrt[512,256,28,28]", lambda: F.unary(x, 2, out=y), 8 * n)
@@ -307,8 +322,10 @@ def per_op_sweep(torch, F, device, peak):
         r = torch.empty(outs, device=device)
         for name, code in (("Sum", 1), ("Avg", 4), ("Max", 2), ("Min", 3)):
             bench("reduce_%s%s[1024,512,14,14]" % (name, list(axes)), lambda: F.reduce(x, code, axes, out=r), 4 * (n + outs))
-    x.uniform_(0.99, 1.01)
     r = torch.empty(1024 * 512, device=device)
+    for name, code in (("L1", 5), ("L2", 6)):
+        bench("reduce_%s[2, 3][1024,512,14,14]" % name, lambda: F.reduce(x, code, (2, 3), out=r), 4 * (n + 1024 * 512))
+    x.uniform_(0.99, 1.01)
     bench("reduce_Prod[2, 3][1024,512,14,14]", lambda: F.reduce(x, 0, (2, 3), out=r), 4 * (n + 1024 * 512))
     del x
     x, y = torch.empty(16384, 4096, device=device).normal_(0, 3), torch.empty(16384, 4096, device=device)
