@@ -64,18 +64,15 @@ def _scan_slice(lib, code, base, stride, got):
     return list(hist), list(stats), [over[i] for i in range(min(n_over.value, 64))], n_over.value
 
 
-@pytest.mark.parametrize("name,code,how,bar", FUNCTIONS, ids=[f[0] for f in FUNCTIONS])
-def test_every_float_within_the_bar(name, code, how, bar):
+def _device_results(how, threads):
+    """Runs one function over every float bit pattern (every 61st on a small host) and yields, launch
+    by launch, (first bit pattern, stride, results on the host)."""
     import torch
     from shadow_b200 import functional as F
-    lib = _scan_lib()
-    threads = os.cpu_count() or 1
     full = threads >= 8
     dev = torch.device("cuda", 0)
     out_dev = torch.empty(CHUNK, dtype=torch.float32, device=dev)
     host = torch.empty(CHUNK, dtype=torch.float32).pin_memory()
-    hist, worst, wrong_sign, over, n_over = [0] * 5, (0, 0), 0, [], 0
-    pool = ThreadPoolExecutor(max_workers=threads)
     stride = 1 if full else 61
     per = CHUNK * stride            # bit patterns covered per launch
     for base in range(0, 1 << 32, per):
@@ -90,7 +87,29 @@ def test_every_float_within_the_bar(name, code, how, bar):
             F.activate(x, how[1], 0.1, out=y)
         host[:count].copy_(y)
         torch.cuda.synchronize()
-        got = host[:count].numpy()
+        yield base, stride, host[:count].numpy()
+
+
+def _expected_total(threads):
+    return (1 << 32) if threads >= 8 else len(range(0, 1 << 32, 61))
+
+
+def _report(line):
+    print(line)
+    table = os.environ.get("SB200_ULP_TABLE")
+    if table:
+        with open(table, "a") as fh:
+            fh.write(line + "\n")
+
+
+@pytest.mark.parametrize("name,code,how,bar", FUNCTIONS, ids=[f[0] for f in FUNCTIONS])
+def test_every_float_within_the_bar(name, code, how, bar):
+    lib = _scan_lib()
+    threads = os.cpu_count() or 1
+    hist, worst, wrong_sign, over, n_over = [0] * 5, (0, 0), 0, [], 0
+    pool = ThreadPoolExecutor(max_workers=threads)
+    for base, stride, got in _device_results(how, threads):
+        count = got.size
         share = (count + threads - 1) // threads
         jobs = [pool.submit(_scan_slice, lib, code, base + lo * stride, stride, got[lo:lo + share])
                 for lo in range(0, count, share)]
@@ -103,14 +122,46 @@ def test_every_float_within_the_bar(name, code, how, bar):
             over, n_over = (over + o)[:64], n_over + n
     pool.shutdown()
     total = sum(hist)
-    line = "%-10s inputs %d  0ulp %d  1ulp %d  2ulp %d  3ulp %d  >=4ulp %d  max %d at 0x%08x  wrong-sign zeros %d" % (
-        name, total, hist[0], hist[1], hist[2], hist[3], hist[4], worst[0], worst[1], wrong_sign)
-    print(line)
-    table = os.environ.get("SB200_ULP_TABLE")
-    if table:
-        with open(table, "a") as fh:
-            fh.write(line + "\n")
-    assert total == ((1 << 32) if full else len(range(0, 1 << 32, stride)))
+    _report("%-10s inputs %d  0ulp %d  1ulp %d  2ulp %d  3ulp %d  >=4ulp %d  max %d at 0x%08x  wrong-sign zeros %d" % (
+        name, total, hist[0], hist[1], hist[2], hist[3], hist[4], worst[0], worst[1], wrong_sign))
+    assert total == _expected_total(threads)
     assert worst[0] <= bar, "%s: %d inputs above %d ulp, first ones %s" % (
         name, n_over if bar == 2 else total - hist[0], bar, ["0x%08x" % b for b in over[:16]])
     assert wrong_sign == 0, "%s: %d zeros of the wrong sign" % (name, wrong_sign)
+
+
+def _gelu_slice(lib, base, stride, got):
+    hist = (C.c_uint64 * 5)()
+    stats = (C.c_int64 * 3)()
+    rc = lib.orc_gelu_scan(C.c_uint32(base & 0xFFFFFFFF), C.c_uint32(stride), got.size, got.ctypes.data_as(C.POINTER(C.c_float)),
+                           hist, stats)
+    assert rc == 0
+    return list(hist), list(stats)
+
+
+def test_gelu_on_every_float():
+    """Gelu = 0.5f*x*(1 + erff(0.707107f*x)) (shadow/operators/kernels/activate.cpp:25-26).  For x << 0 the sum
+    1 + erf cancels, so a one-ulp difference in erf is magnified in the result; the bar is therefore 2 ulp of
+    the result plus one ulp of erf (2^-24) times |x/2|, and it has to hold on every input."""
+    lib = _scan_lib()
+    lib.orc_gelu_scan.restype = C.c_int
+    lib.orc_gelu_scan.argtypes = [C.c_uint32, C.c_uint32, C.c_int64, C.POINTER(C.c_float), C.POINTER(C.c_uint64), C.POINTER(C.c_int64)]
+    threads = os.cpu_count() or 1
+    hist, outside, first, wrong_sign = [0] * 5, 0, None, 0
+    pool = ThreadPoolExecutor(max_workers=threads)
+    for base, stride, got in _device_results(("activate", 8), threads):
+        share = (got.size + threads - 1) // threads
+        jobs = [pool.submit(_gelu_slice, lib, base + lo * stride, stride, got[lo:lo + share]) for lo in range(0, got.size, share)]
+        for h, st in [j.result() for j in jobs]:
+            hist = [a + c for a, c in zip(hist, h)]
+            if st[0] and first is None:
+                first = st[1]
+            outside += st[0]
+            wrong_sign += st[2]
+    pool.shutdown()
+    total = sum(hist)
+    _report("%-10s inputs %d  0ulp %d  1ulp %d  2ulp %d  3ulp %d  >=4ulp %d  outside 2 ulp + |x/2|*2^-24: %d  wrong-sign zeros %d" % (
+        "Gelu", total, hist[0], hist[1], hist[2], hist[3], hist[4], outside, wrong_sign))
+    assert total == _expected_total(threads)
+    assert outside == 0, "Gelu: %d inputs outside the bar, the first one 0x%08x" % (outside, first or 0)
+    assert wrong_sign == 0
