@@ -362,6 +362,62 @@ pad_vec_kernel(const float* __restrict__ x, float* y, int64_t total, int in_h, i
   }
 }
 
+// Pad with non-negative paddings and an input width that is a multiple of 4: a block builds a band of
+// consecutive output rows (planes follow each other, so a band may span planes) in shared memory - filled with
+// the value, then overwritten by the input rows that fall into it, which are ONE contiguous range of x read as
+// aligned float4 - and writes it out as aligned float4 of the flat output.  No per-element index arithmetic:
+// two multiply-high divisions per input float4, none per output float4.
+struct PadBand {
+  int rows_per_block;
+  uint32_t total_rows;        // planes * out_h
+  FastDiv32 div_w4, div_in_h, div_out_h;
+};
+
+__global__ void __launch_bounds__(kThreads)
+pad_smem_kernel(const float* __restrict__ x, float* y, int in_h, int in_w, int out_h, int out_w, int top, int left,
+                float value, const __grid_constant__ PadBand q) {
+  extern __shared__ __align__(16) float pad_tile[];
+  const int t = threadIdx.x;
+  const uint32_t r0 = blockIdx.x * static_cast<uint32_t>(q.rows_per_block);
+  const int rows = static_cast<int>(min(static_cast<uint32_t>(q.rows_per_block), q.total_rows - r0));
+  const int64_t o_start = static_cast<int64_t>(r0) * out_w;
+  const int64_t a0 = o_start & ~static_cast<int64_t>(3);
+  const int lead = static_cast<int>(o_start - a0);
+  const int n_tile = lead + rows * out_w;
+  float4* tile4 = reinterpret_cast<float4*>(pad_tile);
+  const float4 fill = make_float4(value, value, value, value);
+  for (int j = t; j < (n_tile + 3) >> 2; j += kThreads) tile4[j] = fill;
+  __syncthreads();
+  // input rows (flattened over planes) that lie before output row r: whole planes, plus the rows of r's plane above it
+  auto input_rows_before = [&](uint32_t r) {
+    uint32_t plane, oh;
+    q.div_out_h.divmod(r, plane, oh);
+    return plane * static_cast<uint32_t>(in_h) + static_cast<uint32_t>(min(max(static_cast<int>(oh) - top, 0), in_h));
+  };
+  const uint32_t i0 = input_rows_before(r0), i1 = input_rows_before(r0 + rows);
+  const int w4 = in_w >> 2, n4 = static_cast<int>(i1 - i0) * w4;
+  const float4* src = reinterpret_cast<const float4*>(x) + static_cast<int64_t>(i0) * w4;
+#pragma unroll 4
+  for (int j = t; j < n4; j += kThreads) {
+    const float4 v = ld_stream(src + j);
+    uint32_t irow, c4, plane, h;
+    q.div_w4.divmod(static_cast<uint32_t>(j), irow, c4);
+    q.div_in_h.divmod(i0 + irow, plane, h);
+    const int64_t out_row = static_cast<int64_t>(plane) * out_h + h + top;
+    float* dst = pad_tile + (static_cast<int>(out_row - r0) * out_w + lead + left + 4 * static_cast<int>(c4));
+    dst[0] = v.x, dst[1] = v.y, dst[2] = v.z, dst[3] = v.w;
+  }
+  __syncthreads();
+  // the band's floats are tile[lead, n_tile): aligned float4 in the middle, single floats where the first or
+  // the last float4 is shared with a neighbouring band
+  float4* y4 = reinterpret_cast<float4*>(y + a0);
+  const int head_end = min((lead + 3) & ~3, n_tile);
+  const int body_end = max(n_tile & ~3, head_end);
+  for (int j = (head_end >> 2) + t; j < (body_end >> 2); j += kThreads) st_stream(y4 + j, tile4[j]);
+  if (t < head_end - lead) y[a0 + lead + t] = pad_tile[lead + t];
+  if (t < n_tile - body_end) y[a0 + body_end + t] = pad_tile[body_end + t];
+}
+
 }  // namespace
 }  // namespace sb200
 
@@ -532,6 +588,22 @@ int sb200_pad(const float* x, float* y, int64_t planes, int in_h, int in_w, cons
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(y)) & 3u) return SB200_ERR_BAD_ARGUMENT;
   if (planes > (1ll << 40) / (out_h * out_w)) return SB200_ERR_UNSUPPORTED;
   const int64_t total = planes * out_h * out_w;
+  const int64_t rows_all = planes * out_h;
+  const int64_t band_rows = (24 * 1024) / (out_w * 4) > 0 ? (24 * 1024) / (out_w * 4) : 1;
+  if (paddings[0] >= 0 && paddings[1] >= 0 && paddings[2] >= 0 && paddings[3] >= 0 && (in_w & 3) == 0 && aligned16(x) &&
+      aligned16(y) && rows_all < (1ll << 31) && (band_rows * out_w + 8) * 4 <= 47 * 1024 && band_rows * out_w < (1ll << 24)) {
+    PadBand q;
+    q.rows_per_block = static_cast<int>(band_rows);
+    q.total_rows = static_cast<uint32_t>(rows_all);
+    q.div_w4 = FastDiv32(static_cast<uint32_t>(in_w / 4));
+    q.div_in_h = FastDiv32(static_cast<uint32_t>(in_h));
+    q.div_out_h = FastDiv32(static_cast<uint32_t>(out_h));
+    const int64_t blocks = (rows_all + band_rows - 1) / band_rows;
+    const int smem = static_cast<int>((band_rows * out_w + 8) * 4);
+    pad_smem_kernel<<<static_cast<unsigned>(blocks), kThreads, smem, static_cast<cudaStream_t>(stream)>>>(
+        x, y, in_h, in_w, static_cast<int>(out_h), static_cast<int>(out_w), paddings[0], paddings[2], value, q);
+    return after_launch("sb200_pad");
+  }
   if (aligned16(y) && total < (1ll << 32)) {
     const int64_t blocks4 = ((total + 3) / 4 + kThreads - 1) / kThreads;
     pad_vec_kernel<<<static_cast<unsigned>(blocks4), kThreads, 0, static_cast<cudaStream_t>(stream)>>>(

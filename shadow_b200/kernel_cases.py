@@ -50,6 +50,17 @@ def _cases(torch, F):
     case("activate_sigmoid", "ew_vec_kernel", activate(3))
     case("activate_tanh", "ew_vec_kernel", activate(5))
 
+    case("unary_sin", "ew_vec_kernel", unary(5, -10, 10))
+    case("unary_tan", "ew_vec_kernel", unary(7, -10, 10))
+    case("activate_softplus", "ew_vec_kernel", activate(4))
+    case("activate_gelu", "ew_vec_kernel", activate(8))
+
+    def binary_pow():
+        a, c = uniform(n_ew, 0.5, 2.0), uniform(n_ew, 0.5, 2.0)
+        y = torch.empty_like(a)
+        return (lambda: F.binary(a, c, 4, out=y)), 12 * a.numel()
+    case("binary_same_pow", "ew_vec_kernel", binary_pow)
+
     def binary_same():
         a, c = uniform(n_ew, -1, 1), uniform(n_ew, -1, 1)
         y = torch.empty_like(a)

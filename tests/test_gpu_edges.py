@@ -270,7 +270,11 @@ def test_pad_vector_stores_cross_row_boundaries():
     from shadow_b200 import functional as F
     torch = _torch()
     for shape, pads, value in (((3, 5, 56, 56), (1, 1, 1, 1), 0.0), ((2, 3, 4, 5), (2, 0, 1, 1), -7.5),
-                               ((4, 1, 6, 1), (0, 3, 1, 1), 2.0), ((2, 2, 9, 9), (-2, -1, -3, 0), 0.0), ((1, 1, 1, 1), (0, 0, 0, 0), 1.0)):
+                               ((4, 1, 6, 1), (0, 3, 1, 1), 2.0), ((2, 2, 9, 9), (-2, -1, -3, 0), 0.0), ((1, 1, 1, 1), (0, 0, 0, 0), 1.0),
+                               # input widths that are multiples of 4: bands of output rows assembled in shared memory
+                               ((2, 3, 8, 12), (0, 2, 3, 1), -1.0), ((1, 1, 4, 4), (0, 0, 0, 1), 9.0), ((300, 1, 1, 4), (1, 0, 0, 0), 0.5),
+                               ((1, 2, 3, 6000), (1, 1, 2, 2), 0.0), ((7, 9, 20, 16), (3, 0, 0, 5), 1.5), ((2, 1, 1, 4), (0, 0, 0, 0), 0.0),
+                               ((40, 16, 28, 28), (1, 2, 2, 1), 0.0)):
         x = cases.normal(7200 + shape[2], shape)
         got = F.pad(torch.from_numpy(x).cuda(), list(pads), value)
         torch.cuda.synchronize()
