@@ -212,6 +212,8 @@ permute_tile_kernel(const float* __restrict__ x, float* y, const __grid_constant
 // decoded once per block with multiply-high divisions.
 struct Tile4Geom {
   int A4, B4;                    // extents of a and b in float4
+  int TB4;                       // float4 of b per tile (<= 16; the block has 16 * TB4 threads): chosen to divide B4 when it can
+  FastDiv32 div_tb4;
   int64_t a_in_step4, b_out_step4;   // step of a in x and of b in y, in float4
   FastDiv32 div_tiles_b, div_tiles_a;
   int nbatch;
@@ -232,8 +234,10 @@ permute_tile4_kernel(const float4* __restrict__ x, float4* y, const __grid_const
     in_base += idx * g.batch_in_step4[d], out_base += idx * g.batch_out_step4[d];
   }
   {
-    const int b4l = threadIdx.x & 15, agl = threadIdx.x >> 4;   // position inside the tile
-    const int b4 = static_cast<int>(tb) * 16 + b4l, ag = static_cast<int>(ta) * 16 + agl;
+    uint32_t agl_u, b4l_u;                                      // position inside the tile
+    g.div_tb4.divmod(threadIdx.x, agl_u, b4l_u);
+    const int b4l = static_cast<int>(b4l_u), agl = static_cast<int>(agl_u);
+    const int b4 = static_cast<int>(tb) * g.TB4 + b4l, ag = static_cast<int>(ta) * 16 + agl;
     if (b4 < g.B4 && ag < g.A4) {
       const float4* src = x + in_base + static_cast<int64_t>(4 * ag) * g.a_in_step4 + b4;
       const float4 r0 = ld_stream(src), r1 = ld_stream(src + g.a_in_step4), r2 = ld_stream(src + 2 * g.a_in_step4),
@@ -250,8 +254,8 @@ permute_tile4_kernel(const float4* __restrict__ x, float4* y, const __grid_const
   if (ag >= g.A4) return;
 #pragma unroll
   for (int k = 0; k < 4; ++k) {
-    const int bl = (threadIdx.x >> 4) + 16 * k;
-    const int b = static_cast<int>(tb) * 64 + bl;
+    const int bl = (threadIdx.x >> 4) + g.TB4 * k;              // threadIdx.x >> 4 runs over 0 .. TB4 - 1
+    const int b = static_cast<int>(tb) * (4 * g.TB4) + bl;
     if (b < 4 * g.B4) st_stream(y + out_base + static_cast<int64_t>(b) * g.b_out_step4 + ag, tile[bl][agl ^ ((bl >> 2) & 7)]);
   }
 }
@@ -501,12 +505,27 @@ int sb200_permute(const float* x, float* y, const int* in_shape, const int* orde
         Tile4Geom g;
         g.A4 = static_cast<int>(ext[nd - 1] / 4), g.B4 = static_cast<int>(ext[jb] / 4);
         g.a_in_step4 = src_step[nd - 1] / 4, g.b_out_step4 = out_step[jb] / 4;
-        const int64_t tiles_a = (g.A4 + 15) / 16, tiles_b = (g.B4 + 15) / 16;
+        // tiles along b: as few as 16 float4 per tile allow, then of equal width (b = 56 floats: one tile of 14
+        // float4 and 224 threads instead of a 16-wide tile with two idle columns)
+        const int n_tiles_b = (g.B4 + 15) / 16;
+        g.TB4 = (g.B4 + n_tiles_b - 1) / n_tiles_b;
+        g.div_tb4 = FastDiv32(static_cast<uint32_t>(g.TB4));
+        const int64_t tiles_a = (g.A4 + 15) / 16, tiles_b = n_tiles_b;
         g.div_tiles_a = FastDiv32(static_cast<uint32_t>(tiles_a)), g.div_tiles_b = FastDiv32(static_cast<uint32_t>(tiles_b));
         g.nbatch = 0;
         int64_t blocks = tiles_a * tiles_b;
-        for (int j = 0; j < nd - 1; ++j) {
-          if (j == jb) continue;
+        int order[kMaxDims], n_order = 0;
+        for (int j = 0; j < nd - 1; ++j)
+          if (j != jb) order[n_order++] = j;
+        // batch dims by falling input step: over consecutive blocks the one with the SMALLEST input step varies
+        // fastest, so the blocks in flight together read neighbouring row segments of x (order 2,0,3,1 of
+        // [128,256,56,56]: 224-byte segments that are adjacent in memory; 0.75 -> 0.80 of 8 TB/s against the
+        // output's order) - writes stay whole 256-byte segments either way
+        for (int a1 = 0; a1 < n_order; ++a1)
+          for (int b1 = a1 + 1; b1 < n_order; ++b1)
+            if (src_step[order[b1]] > src_step[order[a1]]) { const int tmp = order[a1]; order[a1] = order[b1]; order[b1] = tmp; }
+        for (int o = 0; o < n_order; ++o) {
+          const int j = order[o];
           g.div_batch[g.nbatch] = FastDiv32(static_cast<uint32_t>(ext[j]));
           g.batch_in_step4[g.nbatch] = src_step[j] / 4, g.batch_out_step4[g.nbatch] = out_step[j] / 4;
           ++g.nbatch;
@@ -514,7 +533,7 @@ int sb200_permute(const float* x, float* y, const int* in_shape, const int* orde
         }
         for (int d = g.nbatch; d < kMaxDims; ++d) g.div_batch[d] = FastDiv32(1), g.batch_in_step4[d] = 0, g.batch_out_step4[d] = 0;
         if (blocks < (1ll << 31)) {
-          permute_tile4_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(reinterpret_cast<const float4*>(x),
+          permute_tile4_kernel<<<static_cast<unsigned>(blocks), 16 * g.TB4, 0, s>>>(reinterpret_cast<const float4*>(x),
                                                                              reinterpret_cast<float4*>(y), g);
           return after_launch("sb200_permute");
         }
