@@ -389,9 +389,6 @@ pad_smem_kernel(const float* __restrict__ x, float* y, int in_h, int in_w, int o
   const int lead = static_cast<int>(o_start - a0);
   const int n_tile = lead + rows * out_w;
   float4* tile4 = reinterpret_cast<float4*>(pad_tile);
-  const float4 fill = make_float4(value, value, value, value);
-  for (int j = t; j < (n_tile + 3) >> 2; j += kThreads) tile4[j] = fill;
-  __syncthreads();
   // input rows (flattened over planes) that lie before output row r: whole planes, plus the rows of r's plane above it
   auto input_rows_before = [&](uint32_t r) {
     uint32_t plane, oh;
@@ -401,15 +398,33 @@ pad_smem_kernel(const float* __restrict__ x, float* y, int in_h, int in_w, int o
   const uint32_t i0 = input_rows_before(r0), i1 = input_rows_before(r0 + rows);
   const int w4 = in_w >> 2, n4 = static_cast<int>(i1 - i0) * w4;
   const float4* src = reinterpret_cast<const float4*>(x) + static_cast<int64_t>(i0) * w4;
-#pragma unroll 4
-  for (int j = t; j < n4; j += kThreads) {
-    const float4 v = ld_stream(src + j);
-    uint32_t irow, c4, plane, h;
-    q.div_w4.divmod(static_cast<uint32_t>(j), irow, c4);
-    q.div_in_h.divmod(i0 + irow, plane, h);
-    const int64_t out_row = static_cast<int64_t>(plane) * out_h + h + top;
-    float* dst = pad_tile + (static_cast<int>(out_row - r0) * out_w + lead + left + 4 * static_cast<int>(c4));
-    dst[0] = v.x, dst[1] = v.y, dst[2] = v.z, dst[3] = v.w;
+  // The band's input (at most kPadU float4 per thread for the usual 24 KB band) is requested first, so that
+  // its way from DRAM overlaps the fill of the band; wider bands take further rounds.
+  constexpr int kPadU = 6;
+  for (int j0 = 0; j0 < n4 || j0 == 0; j0 += kPadU * kThreads) {
+    float4 v[kPadU];
+#pragma unroll
+    for (int u = 0; u < kPadU; ++u) {
+      const int j = j0 + u * kThreads + t;
+      if (j < n4) v[u] = ld_stream(src + j);
+    }
+    if (j0 == 0) {
+      const float4 fill = make_float4(value, value, value, value);
+      for (int j = t; j < (n_tile + 3) >> 2; j += kThreads) tile4[j] = fill;
+      __syncthreads();
+    }
+#pragma unroll
+    for (int u = 0; u < kPadU; ++u) {
+      const int j = j0 + u * kThreads + t;
+      if (j < n4) {
+        uint32_t irow, c4, plane, h;
+        q.div_w4.divmod(static_cast<uint32_t>(j), irow, c4);
+        q.div_in_h.divmod(i0 + irow, plane, h);
+        const int64_t out_row = static_cast<int64_t>(plane) * out_h + h + top;
+        float* dst = pad_tile + (static_cast<int>(out_row - r0) * out_w + lead + left + 4 * static_cast<int>(c4));
+        dst[0] = v[u].x, dst[1] = v[u].y, dst[2] = v[u].z, dst[3] = v[u].w;
+      }
+    }
   }
   __syncthreads();
   // the band's floats are tile[lead, n_tile): aligned float4 in the middle, single floats where the first or
