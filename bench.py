@@ -375,6 +375,10 @@ def per_op_sweep(torch, F, device, peak):
     idx = torch.arange(0, 160, 2, device=device, dtype=torch.int32)
     yg = torch.empty(256, 80, 56, 56, device=device)
     bench("gather_axis1_every_2nd[256,160,56,56]", lambda: F.gather(y, idx, 1, out=yg), 8 * yg.numel())
+    del yg
+    idx = torch.randperm(160, device=device).to(torch.int32)
+    yg = torch.empty(256, 160, 56, 56, device=device)
+    bench("gather_axis1_permuted[256,160,56,56]", lambda: F.gather(y, idx, 1, out=yg), 8 * yg.numel())
     del y, yg
     x = torch.randn(256, 64, 112, 112, device=device)
     y = torch.empty(256, 64, 56, 56, device=device)
