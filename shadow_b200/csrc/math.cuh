@@ -175,9 +175,9 @@ __device__ __forceinline__ float tanh_accurate(float x) {
   const float ax = fminf(fabsf(x), 10.f);         // beyond 10, 1 - 2e^{-2|x|} rounds to 1 (also for inf)
   const double e = exp_core(ax + ax);             // e^{2|x|} in [1, 4.9e8]
   const double t = fma(-2.0, rcp_newton(e + 1.0), 1.0);
-  float y = copysignf(static_cast<float>(t), x);
-  y = (fabsf(x) < 2.44140625e-4f) ? x : y;        // tiny arguments (and +-0) return x itself
-  return (x == x) ? y : x;                        // NaN
+  const float y = copysignf(static_cast<float>(t), x);
+  // tiny arguments (and +-0) return x itself, and so does a NaN: one test covers both
+  return (fabsf(x) >= 2.44140625e-4f) ? y : x;
 }
 
 // tan(x) rounded to float.  |x| < 2^20: x = k*(pi/2) + r in double (k by the 1.5*2^52 rounding constant, pi/2 as
