@@ -658,7 +658,7 @@ void launch_stage1(const Plan& P, const float* x, float* y, double* part, cudaSt
       else redA_block_kernel<OP, false, TO_PART><<<grid, kThreads, 0, s>>>(x, y, part, P.a);
     }
   } else if (P.family == kFamB && P.b_colwalk) {
-    constexpr int U = 2, NB = 3;
+    constexpr int U = 2, NB = 4;
     size_t smem = colwalk_smem(P.cw, sizeof(typename RedOp<OP>::Acc));
     if (smem < colwalk_ring_bytes(P.cw, U, NB)) smem = colwalk_ring_bytes(P.cw, U, NB);
     static unsigned long long attr_done = 0;   // per instantiation, one bit per device
