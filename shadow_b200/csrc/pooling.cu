@@ -386,6 +386,7 @@ extern "C" int sb200_pooling(const float* x, float* y, int64_t planes, const int
   } while (0)
     if (g.k_h == 2 && g.k_w == 2) SB200_POOL(2, 2);
     else if (g.k_h == 3 && g.k_w == 3) SB200_POOL(3, 3);
+    else if (g.k_h == 7 && g.k_w == 7) SB200_POOL(7, 7);   // global pooling of 7x7 planes
     else SB200_POOL(0, 0);
 #undef SB200_POOL
 #undef SB200_POOL_M
