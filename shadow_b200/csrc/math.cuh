@@ -121,7 +121,12 @@ __device__ __align__(128) const double kExp2Sixteenths[16] = {
 // e^x = 2^(k>>4) * 2^((k&15)/16) * e^r with e^r by its degree-4 Taylor polynomial
 // (r^5/120 < 4.1e-11).  k is found by adding the 1.5*2^52 rounding constant in double (no
 // conversion instruction); the reduction is one fused multiply-add with ln2/16 in double.
-__device__ __forceinline__ double exp_core(double xd) {
+// The two factors are returned separately so that a caller can fuse the last multiplication with what follows
+// (1 - e^x, (e^x + 1)/2): e^x = p * scale * 2^-bias_down, with scale an exact power-of-two multiple of the table entry.
+struct ExpParts {
+  double p, scale;
+};
+__device__ __forceinline__ ExpParts exp_parts(double xd, int bias_down) {
   const double kRound = 6755399441055744.0;                 // 1.5 * 2^52: adding it rounds to an integer
   const double t = fma(xd, 23.083120654223414, kRound);     // x * 16/ln2, integer part in the low word
   const int ki = __double2loint(t);                         // k as a signed integer (|k| < 2^12)
@@ -129,15 +134,20 @@ __device__ __forceinline__ double exp_core(double xd) {
   // one-step reduction: the rounding of ln2/16 to double moves r by at most 2^9 * 5e-18, far below the
   // 4e-11 of the polynomial
   const double r = fma(kd, -0.043321698784996581, xd);
-  double p = fma(r, 4.16666666666666666667e-02, 1.66666666666666666667e-01);
-  p = fma(p, r, 0.5);
-  p = fma(p, r, 1.0);
-  p = fma(p, r, 1.0);
-  const double v = p * __ldg(&kExp2Sixteenths[ki & 15]);  // in [1, 2.05)
-  // scale by 2^(k>>4) through the exponent field; k>>4 stays within [-152, 130]
-  return __hiloint2double(__double2hiint(v) + ((ki >> 4) << 20), __double2loint(v));
+  ExpParts e;
+  e.p = fma(r, 4.16666666666666666667e-02, 1.66666666666666666667e-01);
+  e.p = fma(e.p, r, 0.5);
+  e.p = fma(e.p, r, 1.0);
+  e.p = fma(e.p, r, 1.0);
+  // 2^(k>>4 - bias_down) * 2^((k&15)/16) through the table entry's exponent field; k>>4 stays within [-152, 130]
+  const double tab = __ldg(&kExp2Sixteenths[ki & 15]);      // in [1, 2)
+  e.scale = __hiloint2double(__double2hiint(tab) + (((ki >> 4) - bias_down) << 20), __double2loint(tab));
+  return e;
 }
-
+__device__ __forceinline__ double exp_core(double xd) {
+  const ExpParts e = exp_parts(xd, 0);
+  return e.p * e.scale;
+}
 __device__ __forceinline__ double exp_core(float x) { return exp_core(static_cast<double>(x)); }
 
 // 1/d for a positive double d whose float image and its reciprocal are normal floats (the callers'
@@ -170,11 +180,17 @@ __device__ __forceinline__ float rcp_correct(float y) {
 }
 
 // tanh(x) = 1 - 2/(e^{2|x|} + 1) in double, rounded once; for |x| < 2^-12 the float result is x
-// itself (tanh x = x - x^3/3 and the correction is below half an ulp).
+// itself (tanh x = x - x^3/3 and the correction is below half an ulp).  The exponential is exp_core's scheme
+// written out so that its last multiplication, the addition of 1 and a halving are ONE fused multiply-add:
+// wh = p * (table entry with the exponent k>>4 - 1) + 0.5 = (e^{2|x|} + 1) / 2, whose reciprocal is the
+// 2/(e^{2|x|} + 1) that is wanted (11 double-precision instructions in all, two fewer than through exp_core;
+// the results are the same bit for bit).
 __device__ __forceinline__ float tanh_accurate(float x) {
   const float ax = fminf(fabsf(x), 10.f);         // beyond 10, 1 - 2e^{-2|x|} rounds to 1 (also for inf)
-  const double e = exp_core(ax + ax);             // e^{2|x|} in [1, 4.9e8]
-  const double t = fma(-2.0, rcp_newton(e + 1.0), 1.0);
+  const ExpParts e = exp_parts(static_cast<double>(ax + ax), 1);   // e^{2|x|} / 2 = e.p * e.scale
+  const double wh = fma(e.p, e.scale, 0.5);        // (e^{2|x|} + 1) / 2 in [1, 2.5e8]
+  const double q = rcp_newton(wh);                 // 2 / (e^{2|x|} + 1)
+  const double t = 1.0 - q;
   const float y = copysignf(static_cast<float>(t), x);
   // tiny arguments (and +-0) return x itself, and so does a NaN: one test covers both
   return (fabsf(x) >= 2.44140625e-4f) ? y : x;
@@ -276,7 +292,8 @@ __device__ __forceinline__ float erf_accurate(float t) {
   q = fma(q, u, 0.11181143059940291);
   q = fma(q, u, 1.7356902054909418);
   q = fma(q, u, 2.6824706331264441);
-  const double e = 1.0 - exp_core(-(a * q));
+  const ExpParts ex = exp_parts(-(a * q), 0);
+  const double e = fma(-ex.p, ex.scale, 1.0);   // 1 - e^{-a q}: the product and the subtraction in one rounding
   const double r = (at < 1.220703125e-4f) ? a * 1.1283791670955126 : e;
   return copysignf(static_cast<float>(r), t);
 }
