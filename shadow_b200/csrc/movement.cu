@@ -516,6 +516,16 @@ int sb200_permute(const float* x, float* y, const int* in_shape, const int* orde
                  out_step[jb] % 4 == 0 && ext[nd - 1] / 4 < (1ll << 30) && ext[jb] / 4 < (1ll << 30);
       for (int j = 0; j < nd - 1 && vec; ++j)
         if (j != jb) vec = src_step[j] % 4 == 0 && out_step[j] % 4 == 0 && ext[j] < (1ll << 31);
+      int order[kMaxDims], n_order = 0;
+      for (int j = 0; j < nd - 1; ++j)
+        if (j != jb) order[n_order++] = j;
+      // batch dims by falling input step: over consecutive blocks the one with the SMALLEST input step varies
+      // fastest, so the blocks in flight together read neighbouring row segments of x (order 2,0,3,1 of
+      // [128,256,56,56]: 224-byte segments that are adjacent in memory; 0.75 -> 0.80 of 8 TB/s against the
+      // output's order) - writes stay whole 256-byte segments either way
+      for (int a1 = 0; a1 < n_order; ++a1)
+        for (int b1 = a1 + 1; b1 < n_order; ++b1)
+          if (src_step[order[b1]] > src_step[order[a1]]) { const int tmp = order[a1]; order[a1] = order[b1]; order[b1] = tmp; }
       if (vec) {
         Tile4Geom g;
         g.A4 = static_cast<int>(ext[nd - 1] / 4), g.B4 = static_cast<int>(ext[jb] / 4);
@@ -529,16 +539,6 @@ int sb200_permute(const float* x, float* y, const int* in_shape, const int* orde
         g.div_tiles_a = FastDiv32(static_cast<uint32_t>(tiles_a)), g.div_tiles_b = FastDiv32(static_cast<uint32_t>(tiles_b));
         g.nbatch = 0;
         int64_t blocks = tiles_a * tiles_b;
-        int order[kMaxDims], n_order = 0;
-        for (int j = 0; j < nd - 1; ++j)
-          if (j != jb) order[n_order++] = j;
-        // batch dims by falling input step: over consecutive blocks the one with the SMALLEST input step varies
-        // fastest, so the blocks in flight together read neighbouring row segments of x (order 2,0,3,1 of
-        // [128,256,56,56]: 224-byte segments that are adjacent in memory; 0.75 -> 0.80 of 8 TB/s against the
-        // output's order) - writes stay whole 256-byte segments either way
-        for (int a1 = 0; a1 < n_order; ++a1)
-          for (int b1 = a1 + 1; b1 < n_order; ++b1)
-            if (src_step[order[b1]] > src_step[order[a1]]) { const int tmp = order[a1]; order[a1] = order[b1]; order[b1] = tmp; }
         for (int o = 0; o < n_order; ++o) {
           const int j = order[o];
           g.div_batch[g.nbatch] = FastDiv32(static_cast<uint32_t>(ext[j]));
@@ -559,8 +559,8 @@ int sb200_permute(const float* x, float* y, const int* in_shape, const int* orde
       g.tiles_a = (g.A + 31) / 32, g.tiles_b = (g.Bn + 32 * kTilesB - 1) / (32 * kTilesB);
       g.nbatch = 0;
       int64_t blocks = g.tiles_a * g.tiles_b;
-      for (int j = 0; j < nd - 1; ++j) {
-        if (j == jb) continue;
+      for (int o = 0; o < n_order; ++o) {
+        const int j = order[o];
         g.batch_ext[g.nbatch] = ext[j], g.batch_in_step[g.nbatch] = src_step[j], g.batch_out_step[g.nbatch] = out_step[j];
         ++g.nbatch;
         blocks *= ext[j];
