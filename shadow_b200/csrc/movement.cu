@@ -168,22 +168,25 @@ struct TileGeom {
   int64_t tiles_a, tiles_b;    // tiles along a, groups of kTilesB tiles along b
   int nbatch;
   int64_t batch_ext[kMaxDims], batch_in_step[kMaxDims], batch_out_step[kMaxDims];
+  FastDiv32 div_tiles_b, div_tiles_a, div_batch[kMaxDims];   // the grid has fewer than 2^31 blocks: every factor fits 32 bits
 };
 
 __global__ void __launch_bounds__(256)
 permute_tile_kernel(const float* __restrict__ x, float* y, const __grid_constant__ TileGeom g) {
   __shared__ float tile[kTilesB][32][33];
-  int64_t rest = blockIdx.x;
-  const int64_t tb = rest % g.tiles_b; rest /= g.tiles_b;
-  const int64_t ta = rest % g.tiles_a; rest /= g.tiles_a;
+  // block index -> (batch indices, tile along a, tile along b) by multiply-high divisions (a 64-bit division
+  // costs about a hundred instructions, and a thread's useful work here is 32 loads and stores)
+  uint32_t rest = blockIdx.x, tb, ta;
+  g.div_tiles_b.divmod(rest, rest, tb);
+  g.div_tiles_a.divmod(rest, rest, ta);
   int64_t in_base = 0, out_base = 0;
   for (int d = g.nbatch - 1; d >= 0; --d) {
-    const int64_t idx = rest % g.batch_ext[d];
-    rest /= g.batch_ext[d];
+    uint32_t idx;
+    g.div_batch[d].divmod(rest, rest, idx);
     in_base += idx * g.batch_in_step[d], out_base += idx * g.batch_out_step[d];
   }
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-  const int64_t a0 = ta * 32, b0 = tb * 32 * kTilesB;
+  const int64_t a0 = static_cast<int64_t>(ta) * 32, b0 = static_cast<int64_t>(tb) * 32 * kTilesB;
 #pragma unroll
   for (int t = 0; t < kTilesB; ++t)
 #pragma unroll
@@ -562,10 +565,13 @@ int sb200_permute(const float* x, float* y, const int* in_shape, const int* orde
       for (int o = 0; o < n_order; ++o) {
         const int j = order[o];
         g.batch_ext[g.nbatch] = ext[j], g.batch_in_step[g.nbatch] = src_step[j], g.batch_out_step[g.nbatch] = out_step[j];
+        g.div_batch[g.nbatch] = FastDiv32(static_cast<uint32_t>(ext[j] < (1ll << 32) ? ext[j] : 1));
         ++g.nbatch;
         blocks *= ext[j];
       }
-      for (int d = g.nbatch; d < kMaxDims; ++d) g.batch_ext[d] = 1, g.batch_in_step[d] = 0, g.batch_out_step[d] = 0;
+      for (int d = g.nbatch; d < kMaxDims; ++d) g.batch_ext[d] = 1, g.batch_in_step[d] = 0, g.batch_out_step[d] = 0, g.div_batch[d] = FastDiv32(1);
+      g.div_tiles_a = FastDiv32(static_cast<uint32_t>(g.tiles_a < (1ll << 32) ? g.tiles_a : 1));
+      g.div_tiles_b = FastDiv32(static_cast<uint32_t>(g.tiles_b < (1ll << 32) ? g.tiles_b : 1));
       if (blocks < (1ll << 31)) {
         permute_tile_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(x, y, g);
         return after_launch("sb200_permute");
