@@ -171,9 +171,11 @@ struct TileGeom {
   FastDiv32 div_tiles_b, div_tiles_a, div_batch[kMaxDims];   // the grid has fewer than 2^31 blocks: every factor fits 32 bits
 };
 
+// TB = tiles along b per block: kTilesB, or fewer when b is short (b = 57: two tiles instead of four half-empty ones)
+template <int TB>
 __global__ void __launch_bounds__(256)
 permute_tile_kernel(const float* __restrict__ x, float* y, const __grid_constant__ TileGeom g) {
-  __shared__ float tile[kTilesB][32][33];
+  __shared__ float tile[TB][32][33];
   // block index -> (batch indices, tile along a, tile along b) by multiply-high divisions (a 64-bit division
   // costs about a hundred instructions, and a thread's useful work here is 32 loads and stores)
   uint32_t rest = blockIdx.x, tb, ta;
@@ -186,9 +188,9 @@ permute_tile_kernel(const float* __restrict__ x, float* y, const __grid_constant
     in_base += idx * g.batch_in_step[d], out_base += idx * g.batch_out_step[d];
   }
   const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;
-  const int64_t a0 = static_cast<int64_t>(ta) * 32, b0 = static_cast<int64_t>(tb) * 32 * kTilesB;
+  const int64_t a0 = static_cast<int64_t>(ta) * 32, b0 = static_cast<int64_t>(tb) * 32 * TB;
 #pragma unroll
-  for (int t = 0; t < kTilesB; ++t)
+  for (int t = 0; t < TB; ++t)
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const int64_t a = a0 + ty + k * 8, b = b0 + t * 32 + tx;
@@ -196,7 +198,7 @@ permute_tile_kernel(const float* __restrict__ x, float* y, const __grid_constant
     }
   __syncthreads();
 #pragma unroll
-  for (int t = 0; t < kTilesB; ++t)
+  for (int t = 0; t < TB; ++t)
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
       const int64_t b = b0 + t * 32 + ty + k * 8, a = a0 + tx;
@@ -559,7 +561,8 @@ int sb200_permute(const float* x, float* y, const int* in_shape, const int* orde
       TileGeom g;
       g.A = ext[nd - 1], g.Bn = ext[jb];
       g.a_in_step = src_step[nd - 1], g.b_out_step = out_step[jb];
-      g.tiles_a = (g.A + 31) / 32, g.tiles_b = (g.Bn + 32 * kTilesB - 1) / (32 * kTilesB);
+      const int tiles_per_block = g.Bn > 64 ? kTilesB : (g.Bn > 32 ? 2 : 1);
+      g.tiles_a = (g.A + 31) / 32, g.tiles_b = (g.Bn + 32 * tiles_per_block - 1) / (32 * tiles_per_block);
       g.nbatch = 0;
       int64_t blocks = g.tiles_a * g.tiles_b;
       for (int o = 0; o < n_order; ++o) {
@@ -573,7 +576,9 @@ int sb200_permute(const float* x, float* y, const int* in_shape, const int* orde
       g.div_tiles_a = FastDiv32(static_cast<uint32_t>(g.tiles_a < (1ll << 32) ? g.tiles_a : 1));
       g.div_tiles_b = FastDiv32(static_cast<uint32_t>(g.tiles_b < (1ll << 32) ? g.tiles_b : 1));
       if (blocks < (1ll << 31)) {
-        permute_tile_kernel<<<static_cast<unsigned>(blocks), 256, 0, s>>>(x, y, g);
+        if (tiles_per_block == kTilesB) permute_tile_kernel<kTilesB><<<static_cast<unsigned>(blocks), 256, 0, s>>>(x, y, g);
+        else if (tiles_per_block == 2) permute_tile_kernel<2><<<static_cast<unsigned>(blocks), 256, 0, s>>>(x, y, g);
+        else permute_tile_kernel<1><<<static_cast<unsigned>(blocks), 256, 0, s>>>(x, y, g);
         return after_launch("sb200_permute");
       }
     }
