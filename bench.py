@@ -89,8 +89,8 @@ class ClockSampler:
             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
     NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
-    def __init__(self, index: int, period_ms: int = 20):
-        self.index, self.period_ms = index, period_ms
+    def __init__(self, index: int, period_ms: int = 20, ready_wait_s: float = 15.0):
+        self.index, self.period_ms, self.ready_wait_s = index, period_ms, ready_wait_s
         self.proc, self.samples, self.reasons, self.max_mhz = None, [], set(), None
 
     def __enter__(self):
@@ -101,6 +101,17 @@ class ClockSampler:
                  "-lms", str(self.period_ms)], stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
         except Exception:
             self.proc = None
+        # wait for the child's first line: with eight of them starting at once on an 8-GPU box a child needs
+        # longer to come up than a short timed region lasts, and the region would go unsampled
+        self.first = ""
+        if self.proc is not None and self.ready_wait_s > 0:
+            import select
+            try:
+                ready, _, _ = select.select([self.proc.stdout], [], [], self.ready_wait_s)
+                if ready:
+                    self.first = self.proc.stdout.readline()
+            except Exception:
+                pass
         return self
 
     def __exit__(self, *exc):
@@ -108,10 +119,14 @@ class ClockSampler:
             return
         self.proc.terminate()
         try:
-            out, _ = self.proc.communicate(timeout=5)
+            self.proc.wait(timeout=5)
         except Exception:
             self.proc.kill()
+        try:
+            out = self.proc.stdout.read()      # through the same reader as the first line: nothing buffered is lost
+        except Exception:
             out = ""
+        # (the first line was taken before the barrier, with the GPU idle: it only shows that the child is up)
         for line in out.splitlines():
             parts = [p.strip() for p in line.split(",")]
             if len(parts) < 6:
@@ -592,6 +607,10 @@ def run_b200_arm(args):
         else:
             step()
 
+    # the clock sampler is a child process: it is started (and has reported once) BEFORE the barrier, so that
+    # nothing but the timed launches lies between the barrier and the timed region
+    clocks = ClockSampler(local_rank, ready_wait_s=0.0 if args.no_clocks else 15.0)
+    clocks.__enter__()
     if dist is not None:
         dist.barrier()
     torch.cuda.synchronize()
@@ -612,7 +631,7 @@ def run_b200_arm(args):
             ms = float(tmax.item())
         return ms
 
-    with ClockSampler(local_rank) as clocks:
+    try:
         ms_total = timed_block()          # the reported number: the first block of exactly --steps steps
         # The same block again, several times: a timed region of a few milliseconds yields no clock
         # samples and says nothing about run-to-run spread.  The count derives from the max-over-ranks
@@ -622,6 +641,8 @@ def run_b200_arm(args):
             n_more = int(min(200, max(4, 300.0 / max(ms_total, 1e-3))))
             for _ in range(n_more):
                 repeats.append(timed_block())
+    finally:
+        clocks.__exit__(None, None, None)
     extra = (len(repeats) - 1) * args.steps
     launches = (launches_per_step * args.steps) if graph is not None else (capi.launch_count() - launches_before) // len(repeats)
     if dist is not None:
